@@ -1,0 +1,150 @@
+"""Generates the golden fixtures in this folder from the reference itself.
+
+Run in a container where the reference tree is mounted:
+
+    make -C oracle            # builds oracle/_ref/philox_ref from the reference's philox.h
+    python tests/golden/make_golden.py [--reference /path/to/project_aether]
+
+Outputs (committed):
+  philox_kat.json     word 0 of the reference's Philox4x32-10 for several seeds/counters
+                      (from oracle/_ref/philox_ref, i.e. the reference header compiled as is)
+  replay_cases.npz    inputs and outputs of the reference's NumPy replay
+                      `radix_sort_reference.onesweep_reference` on the shapes its own test
+                      uses (tests/test_radix_sort.py:22-33), the look-back vector of
+                      tests/test_radix_sort.py:36-43, and `num_passes` values
+  triton_interp.npz   (only with --triton) keys / permutation / counts produced by the
+                      reference's two Triton kernels run by Triton's CPU interpreter on a
+                      small case, with the host code of fused_radix_sort.py:244-279
+
+The tests only read the fixtures; nothing at test time needs the reference tree.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+
+
+def philox_fixture():
+    exe = os.path.join(ROOT, 'oracle', '_ref', 'philox_ref')
+    cases = []
+    for seed, first, count in [(1234, 0, 16), (0x100000007, 0, 8), (0, 0, 4),
+                               (0xFFFFFFFFFFFFFFFF, 0xFFFFFFF0, 16),
+                               (1234 ^ (4097 << 20), 1 << 20, 8),
+                               (987654321, 123456789, 8)]:
+        out = subprocess.run([exe, hex(seed), str(first), str(count)], check=True,
+                             capture_output=True, text=True).stdout.split()
+        cases.append({'seed': seed, 'first_counter': first,
+                      'word0': [int(v) for v in out]})
+    with open(os.path.join(HERE, 'philox_kat.json'), 'w') as f:
+        json.dump({'source': 'project_aether/src/custom_kernels/cuda/philox.h compiled with g++',
+                   'cases': cases}, f, indent=1)
+
+
+def replay_fixture(ref):
+    out = {}
+    shapes = [(5000, 10_000), (12_345, 300), (1, 7), (2048, 1), (4096, 16_384)]
+    out['shapes'] = np.array(shapes, np.int64)
+    for i, (n, cells) in enumerate(shapes):
+        rng = np.random.default_rng(n)
+        keys = ((rng.integers(0, cells, n) << ref.SHUFFLE_BITS) |
+                rng.integers(0, 1 << ref.SHUFFLE_BITS, n)).astype(np.int32)
+        values = np.arange(n, dtype=np.int32)
+        sk, sv = ref.onesweep_reference(keys, values, ref.num_passes(cells), rng, tile=256)
+        out[f'keys_{i}'] = keys
+        out[f'sorted_keys_{i}'] = sk
+        out[f'sorted_values_{i}'] = sv
+    status = np.zeros((4, ref.RADIX), np.int64)
+    hist = np.arange(4 * ref.RADIX).reshape(4, ref.RADIX) % 5
+    status[0] = hist[0] | ref.FLAG_INCLUSIVE
+    status[1] = (hist[0] + hist[1]) | ref.FLAG_INCLUSIVE
+    status[2] = hist[2] | ref.FLAG_AGGREGATE
+    out['lookback_status'] = status
+    out['lookback_exclusive'] = ref._lookback(status, 3)
+    cells_list = [1, 2, 7, 128, 300, 10_000, 16_384, 262_144, 2_097_152, 1 << 24]
+    out['num_passes_cells'] = np.array(cells_list, np.int64)
+    out['num_passes'] = np.array([ref.num_passes(c) for c in cells_list], np.int64)
+    np.savez_compressed(os.path.join(HERE, 'replay_cases.npz'), **out)
+
+
+def triton_fixture(ref_root):
+    os.environ['TRITON_INTERPRET'] = '1'
+    import torch
+    import triton
+    from src.custom_kernels.triton import fused_radix_sort as frs
+    from src.custom_kernels.triton import radix_sort_reference as ref
+    cases = {}
+    specs = [
+        ('unit', 3000, ref.CellGrid((0., 0., 0.), (1., 1., 0.64), (25, 25, 16)), 1234),
+        ('offset', 2500, ref.CellGrid((0.1, -0.2, 0.), (1., 1., 0.64), (37, 25, 16)),
+         0x138800007),
+    ]
+    for name, n, grid, seed in specs:
+        gen = torch.Generator().manual_seed(7)
+        pos = [torch.rand(n, generator=gen) * (h - l) * 1.1 + l - 0.05 * (h - l)
+               for l, h in zip(grid.lo, grid.hi)]
+        pos = [p.to(torch.float32) for p in pos]
+        # A few positions exactly on the faces.
+        pos[0][:4] = torch.tensor([grid.lo[0], grid.hi[0], grid.lo[0], grid.hi[0]])
+        x, y, z = pos
+        passes = ref.num_passes(grid.num_cells)
+        keys = torch.empty(n, dtype=torch.int32)
+        values = torch.empty(n, dtype=torch.int32)
+        hist = torch.zeros(ref.MAX_PASSES * ref.RADIX, dtype=torch.int32)
+        tiles = triton.cdiv(n, ref.TILE)
+        inv = [c / (h - l) for l, h, c in zip(grid.lo, grid.hi, grid.cells)]
+        frs._bin_keys_kernel[(tiles,)](
+            x, y, z, keys, values, hist, n, *grid.lo, *inv, *grid.cells, seed,
+            NUM_PASSES=passes, SHUFFLE=ref.SHUFFLE_BITS, PASS_PAD=ref.MAX_PASSES,
+            SUB=ref.SUBTILE, SUBTILES=ref.SUBTILES_PER_TILE, RADIX_C=ref.RADIX,
+            RADIX_BITS_C=ref.RADIX_BITS, num_warps=4)
+        unsorted_keys = keys.clone()
+        keys_alt, values_alt = torch.empty_like(keys), torch.empty_like(values)
+        counts = torch.zeros(grid.num_cells, dtype=torch.int32)
+        status = torch.empty(tiles * ref.RADIX, dtype=torch.int32)
+        counter = torch.empty(1, dtype=torch.int32)
+        for p in range(passes):
+            status.zero_()
+            counter.zero_()
+            frs._onesweep_kernel[(tiles,)](
+                keys, values, keys_alt, values_alt, hist, status, counter, counts, n, p,
+                ref.SHUFFLE_BITS, IS_LAST=p == passes - 1, SUB=ref.SUBTILE,
+                SUBTILES=ref.SUBTILES_PER_TILE, RADIX_C=ref.RADIX,
+                RADIX_BITS_C=ref.RADIX_BITS, FLAG_AGG=ref.FLAG_AGGREGATE,
+                FLAG_INC=ref.FLAG_INCLUSIVE, FLAG_BITS=ref.FLAG_MASK,
+                VALUE_BITS=ref.VALUE_MASK, num_warps=8)
+            keys, keys_alt = keys_alt, keys
+            values, values_alt = values_alt, values
+        start = torch.zeros(grid.num_cells + 1, dtype=torch.int32)
+        start[1:] = torch.cumsum(counts, 0)
+        cases[f'{name}_grid'] = np.array(list(grid.lo) + list(grid.hi) + list(grid.cells),
+                                         np.float64)
+        cases[f'{name}_seed'] = np.array([seed], np.uint64)
+        for k, v in (('x', x), ('y', y), ('z', z), ('unsorted_keys', unsorted_keys),
+                     ('keys', keys), ('index', values), ('counts', counts), ('start', start)):
+            cases[f'{name}_{k}'] = v.numpy()
+    cases['triton_version'] = np.array([triton.__version__])
+    np.savez_compressed(os.path.join(HERE, 'triton_interp.npz'), **cases)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--reference', default='/root/reference/project_aether')
+    ap.add_argument('--triton', action='store_true')
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    from src.custom_kernels.triton import radix_sort_reference as ref
+    philox_fixture()
+    replay_fixture(ref)
+    if args.triton:
+        triton_fixture(args.reference)
+
+
+if __name__ == '__main__':
+    main()
