@@ -1,0 +1,110 @@
+/* C ABI of libaether_sort.so: the DSMC particle sort for NVIDIA B200 (sm_100a).
+ *
+ * Conventions (the ones the reference's native library uses for its ctypes
+ * boundary, project_aether/src/custom_kernels/cuda/dsmc_collide_tma.h:121-129
+ * and dsmc_collide_tma.cu:224-299):
+ *   - every pointer is a raw device pointer owned by the caller; `stream` is a
+ *     cudaStream_t passed as void*; the call only enqueues work on it;
+ *   - the return value is a cudaError_t as int, 0 on success;
+ *     cudaErrorInvalidValue (1) is returned for bad arguments before anything
+ *     is launched;
+ *   - the library allocates nothing: scratch memory is a caller-provided
+ *     workspace whose size comes from AetherSortWorkspaceBytes.
+ *
+ * Keys are UNSIGNED 32-bit: key = (cell << 7) | shuffle, cell id x-fastest
+ * (project_aether/src/custom_kernels/triton/fused_radix_sort.py:93-103).
+ */
+#ifndef AETHER_SORT_H_
+#define AETHER_SORT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Geometry of one sort call.  `inv_d*` = cells / (hi - lo) computed in double
+ * and rounded to float by the host, as the reference's driver does
+ * (fused_radix_sort.py:250).  `nx, ny, nz` is the GLOBAL grid used to compute
+ * (ix, iy, iz); the cell id is linearised over the x-slab
+ * [ix_offset, ix_offset + nx_local): cell = (iz*ny + iy)*nx_local + ix - ix_offset.
+ * A single-GPU sort passes ix_offset = 0, nx_local = nx.  The reference has no
+ * slab form; it is the multi-GPU extension of fused_radix_sort.py:99. */
+typedef struct AetherGrid {
+  float x0, y0, z0;
+  float inv_dx, inv_dy, inv_dz;
+  int32_t nx, ny, nz;
+  int32_t ix_offset, nx_local;
+} AetherGrid;
+
+/* Library / ABI version (bumped when a signature changes). */
+int AetherSortAbiVersion(void);
+
+/* Bytes of workspace needed by the sort entry points for `n` particles and
+ * `num_cells` (slab-local) cells; `with_payload` != 0 when positions and
+ * velocities are to be carried.  Replaces the per-call tensor allocations of
+ * the reference driver (fused_radix_sort.py:245-248,257-263).  Returns 0 if the
+ * arguments are out of range (n < 0, n >= 2^30, key wider than 32 bits). */
+size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload);
+
+/* sort_particles_by_cell (fused_radix_sort.py:221-280): sorted keys,
+ * permutation (original index of every sorted particle), per-cell counts (C)
+ * and exclusive starts (C+1).  Inputs are not modified. */
+int AetherSortParticlesByCell(const float* x, const float* y, const float* z, int64_t n,
+                              const AetherGrid* grid, uint64_t seed, uint32_t* keys_out,
+                              int32_t* index_out, int32_t* cell_counts, int32_t* cell_start,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* The sort plus the payload gather that follows it in the DSMC step
+ * (project_aether/src/physics_engine/dsmc_gpu_pipeline.py:105-109): also
+ * writes positions and velocities in sorted order.  `velocity` and
+ * `velocity_sorted` are (3, padded) row-major with rows vx, vy, vz
+ * (dsmc_gpu_pipeline.py:55,69-71); only columns [0, n) are written.
+ * `path`: 0 = choose, 1 = digit passes + gather, 2 = bucketed path. */
+int AetherSortAndGatherParticles(const float* x, const float* y, const float* z,
+                                 const float* velocity, int64_t padded, int64_t n,
+                                 const AetherGrid* grid, uint64_t seed, uint32_t* keys_out,
+                                 int32_t* index_out, int32_t* cell_counts, int32_t* cell_start,
+                                 float* x_sorted, float* y_sorted, float* z_sorted,
+                                 float* velocity_sorted, int64_t padded_sorted, int path,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* The payload gather alone (dsmc_gpu_pipeline.py:107-109): out[r] = in[index[r]]. */
+int AetherGatherParticles(const int32_t* index, int64_t n, const float* x, const float* y,
+                          const float* z, const float* velocity, int64_t padded,
+                          float* x_sorted, float* y_sorted, float* z_sorted,
+                          float* velocity_sorted, int64_t padded_sorted, void* stream);
+
+/* Key generation alone (the first half of _bin_keys_kernel,
+ * fused_radix_sort.py:87-105): keys[i] for the particles as given. */
+int AetherMakeKeys(const float* x, const float* y, const float* z, int64_t n,
+                   const AetherGrid* grid, uint64_t seed, uint32_t* keys_out, void* stream);
+
+/* Device waits in the digit passes are bounded; a wait that gives up records a
+ * code in the workspace instead of spinning (the reference's look-back spins
+ * without limit, fused_radix_sort.py:160-171).  This call synchronises
+ * `stream`, reads the code back and stores it in *status (0 = clean). */
+int AetherSortReadStatus(const void* workspace, void* stream, int32_t* status);
+
+/* Measurement hooks.  The reference times whole calls with CUDA events around
+ * the Python entry point (project_aether/scripts/phase2_triton_sort_benchmark.py:
+ * 73-84); these give the same kind of event timing per stage of one call.
+ * With stage timing enabled every sort call brackets its stages with events on
+ * the caller's stream.  AetherSortReadStageTimes synchronises on them and
+ * writes the elapsed milliseconds of each stage, averaged over the sort calls
+ * made since timing was enabled (the most recent 32 at most; -1 for a stage
+ * that did not run), into ms_out[0 .. AetherSortStageCount()).
+ * AetherSortKernelLaunches returns how many kernels this library has launched
+ * in this process so far. */
+int AetherSortSetStageTiming(int enabled);
+int AetherSortStageCount(void);
+const char* AetherSortStageName(int stage);
+int AetherSortReadStageTimes(float* ms_out, int capacity);
+uint64_t AetherSortKernelLaunches(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* AETHER_SORT_H_ */

@@ -1,0 +1,200 @@
+// extern "C" entry points of libaether_sort.so (declared in include/aether_sort.h).
+#include "common.cuh"
+
+namespace aether {
+namespace {
+
+int bit_length(int64_t v) {
+  int b = 0;
+  while (v > 0) { ++b; v >>= 1; }
+  return b;
+}
+
+// Bits of (cell << 7 | shuffle); radix_sort_reference.py:62.  The reference
+// stops at 31 bits because its keys are signed; keys here are unsigned, so 32
+// bits are allowed.
+int key_bits_of(int64_t num_cells) {
+  const int cb = bit_length(num_cells - 1);
+  return (cb < 1 ? 1 : cb) + kShuffleBits;
+}
+
+bool grid_ok(const AetherGrid* g) {
+  if (!g) return false;
+  if (g->nx <= 0 || g->ny <= 0 || g->nz <= 0) return false;
+  if (g->nx_local <= 0 || g->ix_offset < 0 || g->ix_offset + g->nx_local > g->nx) return false;
+  const int64_t cells = static_cast<int64_t>(g->nx_local) * g->ny * g->nz;
+  return cells > 0 && key_bits_of(cells) <= 32;
+}
+
+bool count_ok(int64_t n) { return n >= 0 && n < (int64_t{1} << 30); }
+
+int run_sort(SortArgs& a, int path) {
+  if (!count_ok(a.n) || !grid_ok(&a.grid)) return cudaErrorInvalidValue;
+  if (!a.keys_out || !a.index_out || !a.cell_counts || !a.cell_start || !a.workspace)
+    return cudaErrorInvalidValue;
+  if (a.n > 0 && (!a.x || !a.y || !a.z)) return cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(a.workspace) & 255) return cudaErrorInvalidValue;
+  a.num_cells = static_cast<int64_t>(a.grid.nx_local) * a.grid.ny * a.grid.nz;
+  a.key_bits = key_bits_of(a.num_cells);
+  (void)path;
+  stage_reset();
+  return standard_sort(a);
+}
+
+}  // namespace
+}  // namespace aether
+
+namespace aether {
+namespace {
+// Stage timing keeps one event pair per stage for each of the last kTimedCalls
+// sort calls, so that a benchmark can run its timed calls back to back and read
+// the per-stage averages afterwards without a synchronisation in between.
+constexpr int kTimedCalls = 32;
+bool g_timing = false;
+bool g_events_ready = false;
+cudaEvent_t g_begin[kTimedCalls][kNumStages], g_end[kTimedCalls][kNumStages];
+bool g_ran[kTimedCalls][kNumStages];
+int64_t g_call = -1;
+uint64_t g_launches = 0;
+const char* const kStageNames[kNumStages] = {
+    "keygen_upsweep", "digit_pass_0", "digit_pass_1", "digit_pass_2", "digit_pass_3",
+    "cell_tables", "payload_gather", "bucket_count", "bucket_scan", "bucket_scatter",
+    "bucket_finish", "slab_partition", "particle_push"};
+}  // namespace
+
+void stage_reset() {
+  if (!g_timing) return;
+  ++g_call;
+  for (int i = 0; i < kNumStages; ++i) g_ran[g_call % kTimedCalls][i] = false;
+}
+void stage_begin(Stage s, cudaStream_t stream) {
+  if (!g_timing || g_call < 0) return;
+  if (!g_events_ready) {
+    for (int c = 0; c < kTimedCalls; ++c)
+      for (int i = 0; i < kNumStages; ++i) {
+        cudaEventCreate(&g_begin[c][i]);
+        cudaEventCreate(&g_end[c][i]);
+      }
+    g_events_ready = true;
+  }
+  cudaEventRecord(g_begin[g_call % kTimedCalls][s], stream);
+}
+void stage_end(Stage s, cudaStream_t stream) {
+  if (!g_timing || g_call < 0) return;
+  cudaEventRecord(g_end[g_call % kTimedCalls][s], stream);
+  g_ran[g_call % kTimedCalls][s] = true;
+}
+void count_launches(int kernels) { g_launches += kernels; }
+}  // namespace aether
+
+using namespace aether;
+
+extern "C" int AetherSortSetStageTiming(int enabled) {
+  g_timing = enabled != 0;
+  g_call = -1;
+  for (int c = 0; c < kTimedCalls; ++c)
+    for (int i = 0; i < kNumStages; ++i) g_ran[c][i] = false;
+  return 0;
+}
+extern "C" int AetherSortStageCount(void) { return kNumStages; }
+extern "C" const char* AetherSortStageName(int stage) {
+  return stage >= 0 && stage < kNumStages ? kStageNames[stage] : "";
+}
+extern "C" int AetherSortReadStageTimes(float* ms_out, int capacity) {
+  if (!ms_out || capacity < kNumStages) return cudaErrorInvalidValue;
+  for (int i = 0; i < kNumStages; ++i) {
+    ms_out[i] = -1.f;
+    if (!g_events_ready) continue;
+    double sum = 0;
+    int calls = 0;
+    for (int c = 0; c < kTimedCalls; ++c) {
+      if (!g_ran[c][i]) continue;
+      cudaError_t e = cudaEventSynchronize(g_end[c][i]);
+      if (e != cudaSuccess) return e;
+      float ms = 0;
+      e = cudaEventElapsedTime(&ms, g_begin[c][i], g_end[c][i]);
+      if (e != cudaSuccess) return e;
+      sum += ms;
+      ++calls;
+    }
+    if (calls) ms_out[i] = static_cast<float>(sum / calls);
+  }
+  return 0;
+}
+extern "C" uint64_t AetherSortKernelLaunches(void) { return g_launches; }
+
+extern "C" int AetherSortAbiVersion(void) { return 1; }
+
+extern "C" size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload) {
+  if (!count_ok(n) || num_cells <= 0 || key_bits_of(num_cells) > 32) return 0;
+  (void)with_payload;
+  return standard_workspace_bytes(n, num_cells);
+}
+
+extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const float* z,
+                                         int64_t n, const AetherGrid* grid, uint64_t seed,
+                                         uint32_t* keys_out, int32_t* index_out,
+                                         int32_t* cell_counts, int32_t* cell_start,
+                                         void* workspace, size_t workspace_bytes, void* stream) {
+  if (!grid) return cudaErrorInvalidValue;
+  SortArgs a{};
+  a.x = x; a.y = y; a.z = z; a.n = n; a.grid = *grid; a.seed = seed;
+  a.keys_out = keys_out; a.index_out = index_out;
+  a.cell_counts = cell_counts; a.cell_start = cell_start;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_sort(a, 1);
+}
+
+extern "C" int AetherSortAndGatherParticles(
+    const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
+    int64_t n, const AetherGrid* grid, uint64_t seed, uint32_t* keys_out, int32_t* index_out,
+    int32_t* cell_counts, int32_t* cell_start, float* x_sorted, float* y_sorted, float* z_sorted,
+    float* velocity_sorted, int64_t padded_sorted, int path, void* workspace,
+    size_t workspace_bytes, void* stream) {
+  if (!grid || !x_sorted || !y_sorted || !z_sorted) return cudaErrorInvalidValue;
+  if ((velocity == nullptr) != (velocity_sorted == nullptr)) return cudaErrorInvalidValue;
+  if (velocity && (padded < n || padded_sorted < n)) return cudaErrorInvalidValue;
+  if (path < 0 || path > 2) return cudaErrorInvalidValue;
+  SortArgs a{};
+  a.x = x; a.y = y; a.z = z; a.velocity = velocity; a.padded = padded; a.n = n;
+  a.grid = *grid; a.seed = seed;
+  a.keys_out = keys_out; a.index_out = index_out;
+  a.cell_counts = cell_counts; a.cell_start = cell_start;
+  a.xs = x_sorted; a.ys = y_sorted; a.zs = z_sorted; a.vs = velocity_sorted;
+  a.padded_sorted = padded_sorted;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_sort(a, path);
+}
+
+extern "C" int AetherGatherParticles(const int32_t* index, int64_t n, const float* x,
+                                     const float* y, const float* z, const float* velocity,
+                                     int64_t padded, float* x_sorted, float* y_sorted,
+                                     float* z_sorted, float* velocity_sorted,
+                                     int64_t padded_sorted, void* stream) {
+  if (!count_ok(n)) return cudaErrorInvalidValue;
+  if (n > 0 && (!index || !x || !y || !z || !x_sorted || !y_sorted || !z_sorted))
+    return cudaErrorInvalidValue;
+  if ((velocity == nullptr) != (velocity_sorted == nullptr)) return cudaErrorInvalidValue;
+  if (velocity && (padded < n || padded_sorted < n)) return cudaErrorInvalidValue;
+  return launch_gather(index, n, x, y, z, velocity, padded, x_sorted, y_sorted, z_sorted,
+                       velocity_sorted, padded_sorted, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int AetherMakeKeys(const float* x, const float* y, const float* z, int64_t n,
+                              const AetherGrid* grid, uint64_t seed, uint32_t* keys_out,
+                              void* stream) {
+  if (!count_ok(n) || !grid_ok(grid)) return cudaErrorInvalidValue;
+  if (n > 0 && (!x || !y || !z || !keys_out)) return cudaErrorInvalidValue;
+  return launch_make_keys(x, y, z, n, *grid, seed, keys_out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int AetherSortReadStatus(const void* workspace, void* stream, int32_t* status) {
+  if (!workspace || !status) return cudaErrorInvalidValue;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const Header* hdr = static_cast<const Header*>(workspace);
+  cudaError_t e = cudaMemcpyAsync(status, &hdr->error, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return e;
+  return cudaStreamSynchronize(s);
+}

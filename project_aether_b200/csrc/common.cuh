@@ -1,0 +1,152 @@
+// Shared device helpers of the particle sort: key generation (cell id from
+// float32 positions and Philox4x32-10 shuffle bits), small PTX wrappers and the
+// workspace layout.  sm_100a only.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/aether_sort.h"
+
+namespace aether {
+
+constexpr int kShuffleBits = 7;  // radix_sort_reference.py:33
+constexpr int kRadixBits = 8;    // digit width of this implementation
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kMaxPasses = 4;    // 32-bit keys / 8-bit digits
+
+// Status word of the chained scan: flag in bits 30-31, count in bits 0-29.
+// (The reference packs a 2-bit flag over a 29-bit count into a signed word,
+// radix_sort_reference.py:36-40; the unsigned form here leaves 30 value bits.)
+constexpr uint32_t kFlagAggregate = 1u << 30;
+constexpr uint32_t kFlagInclusive = 2u << 30;
+constexpr uint32_t kFlagMask = 3u << 30;
+constexpr uint32_t kValueMask = ~kFlagMask;
+
+// Error codes left in the workspace header by a device wait that gave up.
+constexpr int kErrLookbackTimeout = 1;
+constexpr int kErrBucketOverflow = 2;
+
+// Workspace header (first 1 KiB of the workspace, zeroed by every call).
+struct alignas(16) Header {
+  int32_t error;              // first error code seen, 0 when clean
+  int32_t use_standard;       // bucketed path: 1 when it handed over to the digit passes
+  uint32_t tile_counter[kMaxPasses];  // ticket dispenser of each digit pass
+  uint32_t aux_counter[8];
+  uint32_t max_bucket;        // bucketed path: largest bucket seen
+  uint32_t pad[49];
+  uint32_t digit_hist[kMaxPasses][kRadix];  // global digit histograms (upsweep)
+};
+static_assert(sizeof(Header) % 256 == 0, "header must keep 256-byte alignment");
+
+__host__ __device__ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+// Word 0 of Philox4x32-10 with counter (c0, 0, 0, 0) and key (k0, k1): the
+// value tl.randint(seed, i) gives the reference's key kernel
+// (fused_radix_sort.py:101), restated after the reference's own generator
+// (cuda/philox.h:56-72).  The zero counter words let the first two rounds and
+// the unused outputs of the last round fold away at compile time.
+__device__ __forceinline__ uint32_t philox_word0(uint32_t c0, uint32_t k0, uint32_t k1) {
+  constexpr uint32_t kM0 = 0xD2511F53u, kM1 = 0xCD9E8D57u;
+  constexpr uint32_t kW0 = 0x9E3779B9u, kW1 = 0xBB67AE85u;
+  uint32_t c1 = 0, c2 = 0, c3 = 0;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    if (r > 0) {
+      k0 += kW0;
+      k1 += kW1;
+    }
+    const uint32_t hi0 = __umulhi(kM0, c0), lo0 = kM0 * c0;
+    const uint32_t hi1 = __umulhi(kM1, c2), lo1 = kM1 * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+  }
+  return c0;
+}
+
+// clamp(int32_rz((c - lo) * inv), 0, cells - 1) with separately rounded
+// subtract and multiply (fused_radix_sort.py:93-98).  The intrinsics keep the
+// compiler from contracting the pair into a fused multiply-add.
+__device__ __forceinline__ int axis_index(float c, float lo, float inv, int cells) {
+  const int i = __float2int_rz(__fmul_rn(__fsub_rn(c, lo), inv));
+  return min(max(i, 0), cells - 1);
+}
+
+__device__ __forceinline__ uint32_t cell_of(float x, float y, float z, const AetherGrid& g) {
+  const int ix = axis_index(x, g.x0, g.inv_dx, g.nx);
+  const int iy = axis_index(y, g.y0, g.inv_dy, g.ny);
+  const int iz = axis_index(z, g.z0, g.inv_dz, g.nz);
+  return static_cast<uint32_t>((iz * g.ny + iy) * g.nx_local + (ix - g.ix_offset));
+}
+
+__device__ __forceinline__ uint32_t make_key(uint32_t cell, uint32_t index, uint32_t k0,
+                                             uint32_t k1) {
+  return (cell << kShuffleBits) | (philox_word0(index, k0, k1) >> (32 - kShuffleBits));
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
+__device__ __forceinline__ uint32_t lanemask_lt() {
+  uint32_t m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+// Streaming (read-once / write-once) accesses: keep them from displacing data
+// that is reused out of L2.
+__device__ __forceinline__ float4 ldcs4(const float* p) {
+  return __ldcs(reinterpret_cast<const float4*>(p));
+}
+
+// ---- measurement hooks (api.cu) ----
+enum Stage {
+  kStageKeygen = 0, kStagePass0, kStagePass1, kStagePass2, kStagePass3, kStageCellTables,
+  kStageGather, kStageBucketCount, kStageBucketScan, kStageBucketScatter, kStageBucketFinish,
+  kStageSlabPartition, kStagePush, kNumStages
+};
+void stage_begin(Stage s, cudaStream_t stream);
+void stage_end(Stage s, cudaStream_t stream);
+void stage_reset();
+void count_launches(int kernels);
+
+// ---- host-side launchers of the kernels (one translation unit each) ----
+
+struct SortArgs {
+  const float *x, *y, *z, *velocity;
+  int64_t padded, n;
+  AetherGrid grid;
+  uint64_t seed;
+  uint32_t* keys_out;
+  int32_t* index_out;
+  int32_t *cell_counts, *cell_start;
+  float *xs, *ys, *zs, *vs;
+  int64_t padded_sorted;
+  int64_t num_cells;
+  int key_bits;
+  void* workspace;
+  size_t workspace_bytes;
+  cudaStream_t stream;
+};
+
+size_t standard_workspace_bytes(int64_t n, int64_t num_cells);
+cudaError_t standard_sort(const SortArgs& a);
+cudaError_t launch_make_keys(const float* x, const float* y, const float* z, int64_t n,
+                             const AetherGrid& g, uint64_t seed, uint32_t* keys,
+                             cudaStream_t stream);
+cudaError_t launch_gather(const int32_t* index, int64_t n, const float* x, const float* y,
+                          const float* z, const float* velocity, int64_t padded, float* xs,
+                          float* ys, float* zs, float* vs, int64_t padded_sorted,
+                          cudaStream_t stream);
+cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t num_cells,
+                               int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream);
+
+}  // namespace aether

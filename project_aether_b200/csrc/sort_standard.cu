@@ -1,0 +1,540 @@
+// Digit-pass path of the particle sort:
+//   keygen_upsweep_kernel  cell id + Philox shuffle bits -> keys, and the digit
+//                          histograms of every pass from the same read
+//                          (replaces _bin_keys_kernel, fused_radix_sort.py:63-113)
+//   onesweep_pass_kernel   one stable 8-bit digit pass with a decoupled
+//                          look-back chained scan over per-tile status words
+//                          (replaces _onesweep_kernel, fused_radix_sort.py:116-203)
+//   cell_bounds_kernel / cell_counts_kernel
+//                          cell_start and cell_counts from the sorted keys
+//                          (replaces the last-pass atomics and torch.cumsum,
+//                          fused_radix_sort.py:201-203,277-279)
+//   gather_kernel          sorted SoA payload (dsmc_gpu_pipeline.py:107-109)
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace aether {
+
+namespace {
+
+constexpr int kSmCount = 148;
+
+// ------------------------------------------------------------------------
+// Key generation + upsweep.
+// ------------------------------------------------------------------------
+constexpr int kKeygenThreads = 256;
+constexpr int kKeygenVec = 4;
+constexpr int kKeygenChunk = kKeygenThreads * kKeygenVec;
+
+// Adds one digit to a shared histogram with one atomic per distinct digit of
+// the warp, so that a warp whose keys all share a digit (every particle in one
+// cell) costs one atomic, not 32 serialised ones.
+__device__ __forceinline__ void hist_add(uint32_t* h, uint32_t digit, bool valid) {
+  const uint32_t peers = __match_any_sync(0xffffffffu, valid ? digit : 0xffffffffu);
+  if (valid && (peers & lanemask_lt()) == 0) atomicAdd(&h[digit], __popc(peers));
+}
+
+template <int PASSES, bool VEC>
+__global__ void __launch_bounds__(kKeygenThreads)
+keygen_upsweep_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                      const float* __restrict__ z, int64_t n, AetherGrid g, uint32_t k0,
+                      uint32_t k1, uint32_t* __restrict__ keys, uint32_t* __restrict__ global_hist) {
+  __shared__ uint32_t hist[PASSES][kRadix];
+  for (int i = threadIdx.x; i < PASSES * kRadix; i += kKeygenThreads) (&hist[0][0])[i] = 0;
+  __syncthreads();
+  const int64_t chunks = (n + kKeygenChunk - 1) / kKeygenChunk;
+  for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+    const int64_t i0 = c * kKeygenChunk + threadIdx.x * kKeygenVec;
+    float px[kKeygenVec], py[kKeygenVec], pz[kKeygenVec];
+    uint32_t key[kKeygenVec];
+    if (VEC && i0 + kKeygenVec <= n) {
+      const float4 a = ldcs4(x + i0), b = ldcs4(y + i0), d = ldcs4(z + i0);
+      px[0] = a.x; px[1] = a.y; px[2] = a.z; px[3] = a.w;
+      py[0] = b.x; py[1] = b.y; py[2] = b.z; py[3] = b.w;
+      pz[0] = d.x; pz[1] = d.y; pz[2] = d.z; pz[3] = d.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < kKeygenVec; ++k) {
+        const bool ok = i0 + k < n;
+        px[k] = ok ? x[i0 + k] : 0.f;
+        py[k] = ok ? y[i0 + k] : 0.f;
+        pz[k] = ok ? z[i0 + k] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kKeygenVec; ++k)
+      key[k] = make_key(cell_of(px[k], py[k], pz[k], g), static_cast<uint32_t>(i0 + k), k0, k1);
+    if (VEC && i0 + kKeygenVec <= n) {
+      __stcs(reinterpret_cast<uint4*>(keys + i0), make_uint4(key[0], key[1], key[2], key[3]));
+    } else {
+#pragma unroll
+      for (int k = 0; k < kKeygenVec; ++k)
+        if (i0 + k < n) keys[i0 + k] = key[k];
+    }
+#pragma unroll
+    for (int k = 0; k < kKeygenVec; ++k) {
+      const bool ok = i0 + k < n;
+#pragma unroll
+      for (int p = 0; p < PASSES; ++p)
+        hist_add(hist[p], (key[k] >> (kRadixBits * p)) & (kRadix - 1), ok);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < PASSES * kRadix; i += kKeygenThreads) {
+    const uint32_t v = (&hist[0][0])[i];
+    if (v) atomicAdd(&global_hist[i], v);
+  }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kKeygenThreads)
+make_keys_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                 const float* __restrict__ z, int64_t n, AetherGrid g, uint32_t k0, uint32_t k1,
+                 uint32_t* __restrict__ keys) {
+  const int64_t chunks = (n + kKeygenChunk - 1) / kKeygenChunk;
+  for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+    const int64_t i0 = c * kKeygenChunk + threadIdx.x * kKeygenVec;
+#pragma unroll
+    for (int k = 0; k < kKeygenVec; ++k)
+      if (i0 + k < n)
+        keys[i0 + k] = make_key(cell_of(x[i0 + k], y[i0 + k], z[i0 + k], g),
+                                static_cast<uint32_t>(i0 + k), k0, k1);
+  }
+}
+
+// ------------------------------------------------------------------------
+// One Onesweep digit pass.
+// ------------------------------------------------------------------------
+constexpr int kPassThreads = 384;
+constexpr int kPassItems = 16;
+constexpr int kPassWarps = kPassThreads / 32;
+constexpr int kPassTile = kPassThreads * kPassItems;  // 6144 keys
+constexpr uint32_t kPollLimit = 1u << 22;             // look-back polls before giving up
+
+struct PassSmem {
+  uint32_t keys[kPassTile];
+  uint32_t vals[kPassTile];
+  uint32_t warp_count[kPassWarps][kRadix];
+  uint32_t tile_offset[kRadix];   // exclusive scan of the tile's digit histogram
+  int64_t global_base[kRadix];    // output index of staged slot 0 of each digit
+  uint32_t scan_scratch[8];
+  uint32_t tile_id;
+  uint32_t abort;
+};
+
+// FIRST: the values are the particle indices themselves and are synthesised
+// instead of read (the key kernel does not write an index array).
+template <bool FIRST>
+__global__ void __launch_bounds__(kPassThreads, 2)
+onesweep_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
+                     int shift, const uint32_t* __restrict__ digit_total,
+                     uint32_t* __restrict__ status, uint32_t* __restrict__ tile_counter,
+                     int32_t* __restrict__ error, uint32_t poll_limit) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // Tiles are numbered in the order blocks start, so every tile a block waits
+  // on belongs to a block that is already running.
+  if (tid == 0) {
+    s.tile_id = atomicAdd(tile_counter, 1u);
+    s.abort = 0;
+  }
+#pragma unroll
+  for (int i = lane; i < kRadix; i += 32) s.warp_count[warp][i] = 0;
+  __syncthreads();
+  const uint32_t tile = s.tile_id;
+  const int64_t tile_base = static_cast<int64_t>(tile) * kPassTile;
+  const int valid = static_cast<int>(min(static_cast<long long>(kPassTile), static_cast<long long>(n - tile_base)));
+
+  // Warp-striped load: item k of lane l is element warp*32*ITEMS + k*32 + l,
+  // so (k, lane) order is index order.  Slots past the end get the largest key;
+  // they rank after every real key of the last tile and are never written out.
+  const int warp_first = warp * 32 * kPassItems + lane;
+  uint32_t key[kPassItems], rank[kPassItems];
+#pragma unroll
+  for (int k = 0; k < kPassItems; ++k) {
+    const int e = warp_first + k * 32;
+    key[k] = e < valid ? __ldcs(keys_in + tile_base + e) : 0xffffffffu;
+  }
+
+  // Stable rank inside the warp's segment: lanes with equal digits find each
+  // other with match.any; the lowest of them advances the warp's counter.
+  uint32_t* wc = s.warp_count[warp];
+#pragma unroll
+  for (int k = 0; k < kPassItems; ++k) {
+    const uint32_t d = (key[k] >> shift) & (kRadix - 1);
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    const int leader = __ffs(peers) - 1;
+    uint32_t before = 0;
+    if (lane == leader) {
+      before = wc[d];
+      wc[d] = before + __popc(peers);
+    }
+    __syncwarp();
+    rank[k] = __shfl_sync(0xffffffffu, before, leader) + __popc(peers & lanemask_lt());
+  }
+  __syncthreads();
+
+  // Per digit: turn the warps' counts into exclusive offsets, publish the tile
+  // aggregate, scan the tile histogram, look back.
+  uint32_t tile_count = 0;
+  if (tid < kRadix) {
+#pragma unroll
+    for (int w = 0; w < kPassWarps; ++w) {
+      const uint32_t c = s.warp_count[w][tid];
+      s.warp_count[w][tid] = tile_count;
+      tile_count += c;
+    }
+    st_relaxed(status + static_cast<size_t>(tile) * kRadix + tid,
+               tile_count | (tile == 0 ? kFlagInclusive : kFlagAggregate));
+  }
+  // Exclusive scans over the 256 digits (threads 0..255 = warps 0..7): the
+  // tile's own histogram and the pass's global histogram.
+  uint32_t total = 0, tile_excl = 0, total_excl = 0;
+  if (tid < kRadix) {
+    total = digit_total[tid];
+    uint32_t a = tile_count, b = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t ta = __shfl_up_sync(0xffffffffu, a, o), tb = __shfl_up_sync(0xffffffffu, b, o);
+      if (lane >= o) { a += ta; b += tb; }
+    }
+    if (lane == 31) {
+      s.scan_scratch[warp] = a;
+      s.tile_offset[warp] = b;  // borrowed as scratch until the barrier below
+    }
+    tile_excl = a - tile_count;
+    total_excl = b - total;
+  }
+  __syncthreads();
+  uint32_t tile_carry = 0, total_carry = 0;
+  if (tid < kRadix) {
+    for (int w = 0; w < warp; ++w) {
+      tile_carry += s.scan_scratch[w];
+      total_carry += s.tile_offset[w];
+    }
+  }
+  __syncthreads();
+  if (tid < kRadix) {
+    tile_excl += tile_carry;
+    total_excl += total_carry;
+    s.tile_offset[tid] = tile_excl;
+    // Decoupled look-back over the predecessors' status words of this digit.
+    uint32_t exclusive = 0;
+    bool gave_up = false;
+    for (int64_t pred = static_cast<int64_t>(tile) - 1; pred >= 0; --pred) {
+      const uint32_t* word_ptr = status + static_cast<size_t>(pred) * kRadix + tid;
+      uint32_t word = ld_relaxed(word_ptr);
+      uint32_t polls = 0;
+      while ((word & kFlagMask) == 0) {
+        if (++polls > poll_limit) { gave_up = true; break; }
+        __nanosleep(32);
+        word = ld_relaxed(word_ptr);
+      }
+      if (gave_up) break;
+      exclusive += word & kValueMask;
+      if ((word & kFlagMask) == kFlagInclusive) break;
+    }
+    if (gave_up) {
+      atomicCAS(error, 0, kErrLookbackTimeout);
+      s.abort = 1;
+    }
+    if (tile != 0)
+      st_relaxed(status + static_cast<size_t>(tile) * kRadix + tid,
+                 ((exclusive + tile_count) & kValueMask) | kFlagInclusive);
+    s.global_base[tid] = static_cast<int64_t>(total_excl) + exclusive - tile_excl;
+  }
+  __syncthreads();
+
+  // Stage the tile in digit order in shared memory.
+#pragma unroll
+  for (int k = 0; k < kPassItems; ++k) {
+    const uint32_t d = (key[k] >> shift) & (kRadix - 1);
+    rank[k] += s.tile_offset[d] + s.warp_count[warp][d];
+    s.keys[rank[k]] = key[k];
+  }
+#pragma unroll
+  for (int k = 0; k < kPassItems; ++k) {
+    const int e = warp_first + k * 32;
+    uint32_t v;
+    if (FIRST) v = static_cast<uint32_t>(tile_base + e);
+    else v = e < valid ? __ldcs(vals_in + tile_base + e) : 0u;
+    s.vals[rank[k]] = v;
+  }
+  __syncthreads();
+  if (s.abort) return;
+
+  // Coalesced scatter: consecutive staged slots of one digit go to consecutive
+  // output slots.
+#pragma unroll 4
+  for (int j = tid; j < valid; j += kPassThreads) {
+    const uint32_t kk = s.keys[j];
+    const int64_t dst = s.global_base[(kk >> shift) & (kRadix - 1)] + j;
+    keys_out[dst] = kk;
+    vals_out[dst] = s.vals[j];
+  }
+}
+
+// ------------------------------------------------------------------------
+// cell_start / cell_counts from the sorted keys.
+// ------------------------------------------------------------------------
+constexpr int kBoundsThreads = 256;
+
+// Position i in [0, n] is a boundary when its cell differs from the cell of
+// position i-1 (cell -1 before the first key, cell C after the last).  The
+// boundary thread writes `i` as the start of every cell in (previous, current];
+// long runs of empty cells are filled by the whole warp.
+__global__ void __launch_bounds__(kBoundsThreads)
+cell_bounds_kernel(const uint32_t* __restrict__ keys, int64_t n, int64_t num_cells,
+                   int32_t* __restrict__ cell_start) {
+  const int lane = threadIdx.x & 31;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kBoundsThreads;
+  const int64_t rounds = (n + 1 + stride - 1) / stride;
+  for (int64_t r = 0; r < rounds; ++r) {
+    const int64_t i = r * stride + static_cast<int64_t>(blockIdx.x) * kBoundsThreads + threadIdx.x;
+    int64_t first = 0, last = -1;  // cells [first, last] start at i
+    if (i <= n) {
+      const int64_t cur = i < n ? static_cast<int64_t>(keys[i] >> kShuffleBits) : num_cells;
+      const int64_t prev = i > 0 ? static_cast<int64_t>(keys[i - 1] >> kShuffleBits) : -1;
+      first = prev + 1;
+      last = cur;
+    }
+    const bool is_long = last - first >= 32;
+    if (!is_long)
+      for (int64_t c = first; c <= last; ++c) cell_start[c] = static_cast<int32_t>(i);
+    uint32_t pending = __ballot_sync(0xffffffffu, is_long);
+    while (pending) {
+      const int src = __ffs(pending) - 1;
+      pending &= pending - 1;
+      const int64_t f = __shfl_sync(0xffffffffu, first, src);
+      const int64_t l = __shfl_sync(0xffffffffu, last, src);
+      const int32_t v = static_cast<int32_t>(__shfl_sync(0xffffffffu, i, src));
+      for (int64_t c = f + lane; c <= l; c += 32) cell_start[c] = v;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kBoundsThreads)
+cell_counts_kernel(const int32_t* __restrict__ cell_start, int64_t num_cells,
+                   int32_t* __restrict__ cell_counts) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kBoundsThreads;
+  for (int64_t c = static_cast<int64_t>(blockIdx.x) * kBoundsThreads + threadIdx.x; c < num_cells;
+       c += stride)
+    cell_counts[c] = cell_start[c + 1] - cell_start[c];
+}
+
+// ------------------------------------------------------------------------
+// Payload gather by the final permutation.
+// ------------------------------------------------------------------------
+constexpr int kGatherThreads = 256;
+
+template <bool VEC>
+__global__ void __launch_bounds__(kGatherThreads)
+gather_kernel(const int32_t* __restrict__ index, int64_t n, const float* __restrict__ x,
+              const float* __restrict__ y, const float* __restrict__ z,
+              const float* __restrict__ v, int64_t padded, float* __restrict__ xs,
+              float* __restrict__ ys, float* __restrict__ zs, float* __restrict__ vs,
+              int64_t padded_sorted) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kGatherThreads * 4;
+  for (int64_t i0 = (static_cast<int64_t>(blockIdx.x) * kGatherThreads + threadIdx.x) * 4; i0 < n;
+       i0 += stride) {
+    if (VEC && i0 + 4 <= n) {
+      const int4 p = __ldcs(reinterpret_cast<const int4*>(index + i0));
+      const int q[4] = {p.x, p.y, p.z, p.w};
+      float o[6][4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        o[0][k] = x[q[k]];
+        o[1][k] = y[q[k]];
+        o[2][k] = z[q[k]];
+        if (v) {
+          o[3][k] = v[q[k]];
+          o[4][k] = v[padded + q[k]];
+          o[5][k] = v[2 * padded + q[k]];
+        }
+      }
+      __stcs(reinterpret_cast<float4*>(xs + i0), make_float4(o[0][0], o[0][1], o[0][2], o[0][3]));
+      __stcs(reinterpret_cast<float4*>(ys + i0), make_float4(o[1][0], o[1][1], o[1][2], o[1][3]));
+      __stcs(reinterpret_cast<float4*>(zs + i0), make_float4(o[2][0], o[2][1], o[2][2], o[2][3]));
+      if (v) {
+        __stcs(reinterpret_cast<float4*>(vs + i0),
+               make_float4(o[3][0], o[3][1], o[3][2], o[3][3]));
+        __stcs(reinterpret_cast<float4*>(vs + padded_sorted + i0),
+               make_float4(o[4][0], o[4][1], o[4][2], o[4][3]));
+        __stcs(reinterpret_cast<float4*>(vs + 2 * padded_sorted + i0),
+               make_float4(o[5][0], o[5][1], o[5][2], o[5][3]));
+      }
+    } else {
+      for (int k = 0; k < 4 && i0 + k < n; ++k) {
+        const int q = index[i0 + k];
+        xs[i0 + k] = x[q];
+        ys[i0 + k] = y[q];
+        zs[i0 + k] = z[q];
+        if (v) {
+          vs[i0 + k] = v[q];
+          vs[padded_sorted + i0 + k] = v[padded + q];
+          vs[2 * padded_sorted + i0 + k] = v[2 * padded + q];
+        }
+      }
+    }
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline int grid_for(int64_t work_items, int per_block, int blocks_per_sm) {
+  const int64_t blocks = (work_items + per_block - 1) / per_block;
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks, kSmCount * blocks_per_sm)));
+}
+
+struct StandardLayout {
+  int passes;
+  int64_t tiles;
+  size_t status_off, keys_alt_off, index_alt_off, total;
+};
+
+StandardLayout standard_layout(int64_t n, int key_bits) {
+  StandardLayout l;
+  l.passes = std::max(1, (key_bits + kRadixBits - 1) / kRadixBits);
+  l.tiles = std::max<int64_t>(1, (n + kPassTile - 1) / kPassTile);
+  l.status_off = sizeof(Header);
+  const size_t status_bytes = static_cast<size_t>(l.passes) * l.tiles * kRadix * sizeof(uint32_t);
+  l.keys_alt_off = align_up(l.status_off + status_bytes, 256);
+  l.index_alt_off = align_up(l.keys_alt_off + n * sizeof(uint32_t), 256);
+  l.total = align_up(l.index_alt_off + n * sizeof(uint32_t), 256);
+  return l;
+}
+
+}  // namespace
+
+size_t standard_workspace_bytes(int64_t n, int64_t /*num_cells*/) {
+  return standard_layout(n, 32).total;
+}
+
+cudaError_t launch_make_keys(const float* x, const float* y, const float* z, int64_t n,
+                             const AetherGrid& g, uint64_t seed, uint32_t* keys,
+                             cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  make_keys_kernel<false><<<grid_for(n, kKeygenChunk, 8), kKeygenThreads, 0, stream>>>(
+      x, y, z, n, g, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32), keys);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather(const int32_t* index, int64_t n, const float* x, const float* y,
+                          const float* z, const float* velocity, int64_t padded, float* xs,
+                          float* ys, float* zs, float* vs, int64_t padded_sorted,
+                          cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  bool vec = aligned16(index) && aligned16(xs) && aligned16(ys) && aligned16(zs);
+  if (velocity) vec = vec && aligned16(vs) && padded_sorted % 4 == 0;
+  const int grid = grid_for(n, kGatherThreads * 4, 8);
+  if (vec)
+    gather_kernel<true><<<grid, kGatherThreads, 0, stream>>>(index, n, x, y, z, velocity, padded,
+                                                             xs, ys, zs, vs, padded_sorted);
+  else
+    gather_kernel<false><<<grid, kGatherThreads, 0, stream>>>(index, n, x, y, z, velocity, padded,
+                                                              xs, ys, zs, vs, padded_sorted);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t num_cells,
+                               int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream) {
+  cell_bounds_kernel<<<grid_for(n + 1, kBoundsThreads, 8), kBoundsThreads, 0, stream>>>(
+      sorted_keys, n, num_cells, cell_start);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  cell_counts_kernel<<<grid_for(num_cells, kBoundsThreads, 8), kBoundsThreads, 0, stream>>>(
+      cell_start, num_cells, cell_counts);
+  count_launches(2);
+  return cudaGetLastError();
+}
+
+template <int PASSES>
+static void launch_keygen(const SortArgs& a, bool vec, uint32_t* keys, Header* hdr) {
+  const int grid = grid_for(a.n, kKeygenChunk, 8);
+  const uint32_t k0 = static_cast<uint32_t>(a.seed), k1 = static_cast<uint32_t>(a.seed >> 32);
+  if (vec)
+    keygen_upsweep_kernel<PASSES, true><<<grid, kKeygenThreads, 0, a.stream>>>(
+        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0]);
+  else
+    keygen_upsweep_kernel<PASSES, false><<<grid, kKeygenThreads, 0, a.stream>>>(
+        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0]);
+}
+
+cudaError_t standard_sort(const SortArgs& a) {
+  const StandardLayout l = standard_layout(a.n, a.key_bits);
+  if (a.workspace_bytes < l.total) return cudaErrorInvalidValue;
+  auto* base = static_cast<unsigned char*>(a.workspace);
+  Header* hdr = reinterpret_cast<Header*>(base);
+  uint32_t* status = reinterpret_cast<uint32_t*>(base + l.status_off);
+  uint32_t* keys_alt = reinterpret_cast<uint32_t*>(base + l.keys_alt_off);
+  uint32_t* index_alt = reinterpret_cast<uint32_t*>(base + l.index_alt_off);
+  cudaError_t e = cudaMemsetAsync(base, 0, l.keys_alt_off, a.stream);
+  if (e != cudaSuccess) return e;
+
+  if (a.n > 0) {
+    e = cudaFuncSetAttribute(onesweep_pass_kernel<true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(PassSmem));
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(onesweep_pass_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(PassSmem));
+    if (e != cudaSuccess) return e;
+    // Ping-pong so that the last pass lands in the caller's output arrays.
+    uint32_t* out_k = a.keys_out;
+    uint32_t* out_v = reinterpret_cast<uint32_t*>(a.index_out);
+    uint32_t* cur_k = (l.passes % 2 == 0) ? out_k : keys_alt;
+    uint32_t* cur_v = (l.passes % 2 == 0) ? out_v : index_alt;
+    uint32_t* nxt_k = (l.passes % 2 == 0) ? keys_alt : out_k;
+    uint32_t* nxt_v = (l.passes % 2 == 0) ? index_alt : out_v;
+    const bool vec = aligned16(a.x) && aligned16(a.y) && aligned16(a.z) && aligned16(cur_k);
+    stage_begin(kStageKeygen, a.stream);
+    switch (l.passes) {
+      case 1: launch_keygen<1>(a, vec, cur_k, hdr); break;
+      case 2: launch_keygen<2>(a, vec, cur_k, hdr); break;
+      case 3: launch_keygen<3>(a, vec, cur_k, hdr); break;
+      default: launch_keygen<4>(a, vec, cur_k, hdr); break;
+    }
+    stage_end(kStageKeygen, a.stream);
+    count_launches(1);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    for (int p = 0; p < l.passes; ++p) {
+      uint32_t* st = status + static_cast<size_t>(p) * l.tiles * kRadix;
+      stage_begin(static_cast<Stage>(kStagePass0 + p), a.stream);
+      if (p == 0)
+        onesweep_pass_kernel<true><<<static_cast<int>(l.tiles), kPassThreads, sizeof(PassSmem),
+                                     a.stream>>>(cur_k, nullptr, nxt_k, nxt_v, a.n, 0,
+                                                 hdr->digit_hist[0], st, &hdr->tile_counter[0],
+                                                 &hdr->error, kPollLimit);
+      else
+        onesweep_pass_kernel<false><<<static_cast<int>(l.tiles), kPassThreads, sizeof(PassSmem),
+                                      a.stream>>>(cur_k, cur_v, nxt_k, nxt_v, a.n, kRadixBits * p,
+                                                  hdr->digit_hist[p], st, &hdr->tile_counter[p],
+                                                  &hdr->error, kPollLimit);
+      stage_end(static_cast<Stage>(kStagePass0 + p), a.stream);
+      count_launches(1);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      uint32_t* t = cur_k; cur_k = nxt_k; nxt_k = t;
+      t = cur_v; cur_v = nxt_v; nxt_v = t;
+    }
+  }
+  stage_begin(kStageCellTables, a.stream);
+  e = launch_cell_tables(a.keys_out, a.n, a.num_cells, a.cell_counts, a.cell_start, a.stream);
+  stage_end(kStageCellTables, a.stream);
+  if (e != cudaSuccess) return e;
+  if (a.xs) {
+    stage_begin(kStageGather, a.stream);
+    e = launch_gather(a.index_out, a.n, a.x, a.y, a.z, a.velocity, a.padded, a.xs, a.ys, a.zs,
+                      a.vs, a.padded_sorted, a.stream);
+    stage_end(kStageGather, a.stream);
+  }
+  return e;
+}
+
+}  // namespace aether

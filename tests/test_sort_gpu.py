@@ -1,0 +1,215 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle: bit-exact
+keys, permutation, cell counts, cell starts and sorted payload."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import project_aether_b200 as pa
+from oracle import sort_oracle as so
+from project_aether_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+PATHS = [pa.PATH_DIGIT_PASSES]
+
+
+def _ogrid(grid):
+    return so.Grid(tuple(grid.lo), tuple(grid.hi), tuple(grid.cells))
+
+
+def _check_order(result, want):
+    keys = result.keys.cpu().numpy().view(np.uint32)
+    np.testing.assert_array_equal(keys, want.keys)
+    np.testing.assert_array_equal(result.particle_index.cpu().numpy(), want.particle_index)
+    np.testing.assert_array_equal(result.cell_counts.cpu().numpy(), want.cell_counts)
+    np.testing.assert_array_equal(result.cell_start.cpu().numpy(), want.cell_start)
+
+
+def _check_all(x, y, z, vel, grid, seed, path, big=False, **slab):
+    got = pa.sort_and_gather_particles(x, y, z, vel, grid, seed, path=path, **slab)
+    assert pa.last_sort_status(x.device) == 0
+    xn, yn, zn, vn = (t.cpu().numpy() for t in (x, y, z, vel))
+    if big:
+        want, xs, ys, zs, vs = so.c_sort_particles(xn, yn, zn, vn, _ogrid(grid), seed, **slab)
+    else:
+        want = so.sort_particles(xn, yn, zn, _ogrid(grid), seed, **slab)
+        xs, ys, zs, vs = so.gather_payload(want.particle_index, xn, yn, zn, vn)
+    _check_order(got.order, want)
+    for g, w in zip(got.positions, (xs, ys, zs)):
+        np.testing.assert_array_equal(g.cpu().numpy(), w)
+    n = x.numel()
+    np.testing.assert_array_equal(got.velocity.cpu().numpy()[:, :n], vs[:, :n])
+    assert torch.all(got.velocity[:, n:] == 0)
+    return got
+
+
+def _random_state(n, grid, device, seed=0, spill=0.0):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    pos = []
+    for l, h in zip(grid.lo, grid.hi):
+        u = torch.rand(n, device=device, generator=gen)
+        pos.append(((u * (1 + 2 * spill) - spill) * (h - l) + l).float())
+    padded = -(-n // 4) * 4
+    vel = torch.zeros((3, padded), device=device)
+    vel[:, :n] = torch.randn((3, n), device=device, generator=gen)
+    return pos[0], pos[1], pos[2], vel
+
+
+@pytest.mark.parametrize('path', PATHS)
+@pytest.mark.parametrize('name', ['unit', 'offset'])
+def test_golden_cases_from_the_reference_kernels(cuda, golden_dir, name, path):
+    t = np.load(os.path.join(golden_dir, 'triton_interp.npz'))
+    g = t[name + '_grid']
+    grid = pa.CellGrid(tuple(g[:3]), tuple(g[3:6]), tuple(int(v) for v in g[6:]))
+    seed = int(t[name + '_seed'][0])
+    x, y, z = (torch.from_numpy(t[f'{name}_{c}']).to(cuda) for c in 'xyz')
+    res = pa.sort_particles_by_cell(x, y, z, grid, seed)
+    np.testing.assert_array_equal(res.keys.cpu().numpy(), t[name + '_keys'])
+    np.testing.assert_array_equal(res.particle_index.cpu().numpy(), t[name + '_index'])
+    np.testing.assert_array_equal(res.cell_counts.cpu().numpy(), t[name + '_counts'])
+    np.testing.assert_array_equal(res.cell_start.cpu().numpy(), t[name + '_start'])
+    vel = torch.zeros((3, -(-x.numel() // 4) * 4), device=cuda)
+    got = pa.sort_and_gather_particles(x, y, z, vel, grid, seed, path=path)
+    np.testing.assert_array_equal(got.order.keys.cpu().numpy(), t[name + '_keys'])
+    np.testing.assert_array_equal(got.order.particle_index.cpu().numpy(), t[name + '_index'])
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_reference_gpu_test_invariants_and_bits(cuda, path):
+    """The reference's own GPU test (test_radix_sort.py:60-83), then bit parity."""
+    n = 1_000_003
+    grid = pa.CellGrid(lo=(0.0, 0.0, 0.0), hi=(1.0, 1.0, 1.0), cells=(25, 25, 16))
+    gen = torch.Generator(device='cuda').manual_seed(0)
+    x, y, z = (torch.rand(n, device='cuda', generator=gen) for _ in range(3))
+    out = pa.sort_particles_by_cell(x, y, z, grid, seed=1234)
+    keys = out.keys.cpu().numpy()
+    assert np.all(np.diff(keys) >= 0)
+    cell = keys >> pa.SHUFFLE_BITS
+    index = out.particle_index.cpu().numpy().astype(np.int64)
+    assert np.array_equal(np.sort(index), np.arange(n))
+    expected_cell = (
+        (np.clip((z.cpu().numpy() * 16).astype(int), 0, 15) * 25 +
+         np.clip((y.cpu().numpy() * 25).astype(int), 0, 24)) * 25 +
+        np.clip((x.cpu().numpy() * 25).astype(int), 0, 24))
+    np.testing.assert_array_equal(cell, expected_cell[index])
+    np.testing.assert_array_equal(out.cell_counts.cpu().numpy(),
+                                  np.bincount(cell, minlength=grid.num_cells))
+    vel = torch.zeros((3, n + 1), device=cuda)
+    _check_all(x, y, z, vel, grid, 1234, path)
+
+
+@pytest.mark.parametrize('path', PATHS)
+@pytest.mark.parametrize('n,cells', [(5000, (25, 25, 16)), (12_345, (10, 6, 5)), (1, (7, 1, 1)),
+                                     (2048, (1, 1, 1)), (4096, (32, 32, 16)), (0, (4, 4, 4)),
+                                     (6143, (8, 8, 8)), (6144, (8, 8, 8)), (6145, (8, 8, 8)),
+                                     (3 * 6144 + 17, (64, 64, 64)), (100_000, (512, 256, 256))])
+def test_shapes_of_the_reference_unit_tests_and_tile_edges(cuda, n, cells, path):
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), cells)
+    x, y, z, vel = _random_state(n, grid, cuda, seed=n)
+    _check_all(x, y, z, vel, grid, 1234 ^ (n << 20), path)
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_positions_outside_the_box_nonunit_grid_and_wide_seed(cuda, path):
+    grid = pa.CellGrid((0.1, -0.2, 0.0), (1.0, 1.0, 0.64), (37, 25, 16))
+    x, y, z, vel = _random_state(50_000, grid, cuda, seed=11, spill=0.1)
+    x[:6] = torch.tensor([0.1, 1.0, -5.0, 7.0, float('inf'), float('nan')], device=cuda)
+    y[:3] = torch.tensor([-0.2, 1.0, -1e30], device=cuda)
+    _check_all(x, y, z, vel, grid, 0x138800007, path)
+    _check_all(x, y, z, vel, grid, (1 << 64) - 1, path)
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_every_particle_in_one_cell_and_empty_cells(cuda, path):
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (64, 32, 32))
+    n = 40_000
+    x = torch.full((n,), 0.3, device=cuda)
+    y = torch.full((n,), 0.7, device=cuda)
+    z = torch.full((n,), 0.999, device=cuda)
+    vel = torch.zeros((3, n), device=cuda)
+    vel[:, :] = torch.arange(n, device=cuda).float()
+    got = _check_all(x, y, z, vel, grid, 5, path)
+    assert int(got.order.cell_counts.max()) == n
+    # Two far-apart cells: long runs of empty cells between and after them.
+    x[: n // 2] = 0.01
+    z[: n // 2] = 0.01
+    _check_all(x, y, z, vel, grid, 6, path)
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_unaligned_views_and_wider_velocity_padding(cuda, path):
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (16, 16, 16))
+    n = 10_001
+    x, y, z, vel = _random_state(n + 3, grid, cuda, seed=2)
+    vel = torch.cat([vel, torch.zeros((3, 8), device=cuda)], dim=1)
+    _check_all(x[1:n + 1], y[2:n + 2], z[3:n + 3], vel[:, : n + 5].contiguous(), grid, 77, path)
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_slab_local_cell_ids(cuda, path):
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (32, 16, 8))
+    x, y, z, vel = _random_state(30_000, grid, cuda, seed=4)
+    keep = (x >= 0.25) & (x < 0.5)
+    xs, ys, zs = x[keep], y[keep], z[keep]
+    n = xs.numel()
+    v = torch.zeros((3, -(-n // 4) * 4), device=cuda)
+    v[:, :n] = vel[:, : x.numel()][:, keep]
+    _check_all(xs, ys, zs, v, grid, 31, path, ix_offset=8, nx_local=8)
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_runs_are_deterministic(cuda, path):
+    w = workloads.WORKLOADS['c1_1m_64']
+    x, y, z, vel = workloads.make_particles(w, cuda, seed=0)
+    a = pa.sort_and_gather_particles(x, y, z, vel, w.grid, 1234, path=path)
+    b = pa.sort_and_gather_particles(x, y, z, vel, w.grid, 1234, path=path)
+    assert torch.equal(a.order.particle_index, b.order.particle_index)
+    assert torch.equal(a.order.keys, b.order.keys)
+    assert torch.equal(a.velocity, b.velocity)
+    c = pa.sort_and_gather_particles(x, y, z, vel, w.grid, 1235, path=path)
+    assert not torch.equal(a.order.particle_index, c.order.particle_index)
+    assert torch.equal(a.order.cell_counts, c.order.cell_counts)
+
+
+@pytest.mark.parametrize('path', PATHS)
+@pytest.mark.parametrize('name', ['c1_1m_64', 'c2_16m_128', 'c3_64m_hypersonic'])
+def test_benchmark_configurations_bit_exact(cuda, name, path):
+    w = workloads.WORKLOADS[name]
+    x, y, z, vel = workloads.make_particles(w, cuda, seed=0)
+    _check_all(x, y, z, vel, w.grid, workloads.step_seed(1234, 1), path, big=True)
+
+
+def _properties(got, x, vel, n, cells):
+    keys = got.order.keys.view(torch.uint32) if hasattr(torch, 'uint32') else got.order.keys
+    k64 = got.order.keys.to(torch.int64) & 0xFFFFFFFF
+    assert bool(torch.all(k64[1:] >= k64[:-1]))
+    idx = got.order.particle_index.long()
+    seen = torch.zeros(n, dtype=torch.int32, device=x.device)
+    seen.scatter_add_(0, idx, torch.ones_like(idx, dtype=torch.int32))
+    assert bool(torch.all(seen == 1))
+    assert torch.equal(got.positions[0], x[idx])
+    assert torch.equal(got.velocity[2, :n], vel[2, :n][idx])
+    counts = torch.bincount(k64 >> 7, minlength=cells).int()
+    assert torch.equal(counts, got.order.cell_counts)
+    start = torch.zeros(cells + 1, dtype=torch.int64, device=x.device)
+    start[1:] = torch.cumsum(counts.long(), 0)
+    assert torch.equal(start.int(), got.order.cell_start)
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_largest_single_gpu_configuration_properties(cuda, path):
+    """256M particles, 32-bit keys: sortedness, permutation, gather and table
+    identities (size-independent properties; the oracle is not run at this size)."""
+    w = workloads.WORKLOADS['c4_256m_512']
+    x, y, z, vel = workloads.make_particles(w, cuda, seed=0)
+    got = pa.sort_and_gather_particles(x, y, z, vel, w.grid, 1234, path=path)
+    assert pa.last_sort_status(cuda) == 0
+    _properties(got, x, vel, w.n, w.grid.num_cells)
+    # Ties (same cell and shuffle bits) must keep ascending original index.
+    k64 = got.order.keys.to(torch.int64) & 0xFFFFFFFF
+    same = k64[1:] == k64[:-1]
+    idx = got.order.particle_index
+    assert bool(torch.all(idx[1:][same] > idx[:-1][same]))
