@@ -1,4 +1,6 @@
 // extern "C" entry points of libaether_sort.so (declared in include/aether_sort.h).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace aether {
@@ -36,9 +38,17 @@ int run_sort(SortArgs& a, int path) {
   if (reinterpret_cast<uintptr_t>(a.workspace) & 255) return cudaErrorInvalidValue;
   a.num_cells = static_cast<int64_t>(a.grid.nx_local) * a.grid.ny * a.grid.nz;
   a.key_bits = key_bits_of(a.num_cells);
-  (void)path;
   stage_reset();
-  return standard_sort(a);
+  // The bucketed path carries the payload; without one the digit passes run.
+  const BucketPlan plan = plan_buckets(a.n, a.num_cells);
+  const bool bucketed = a.xs != nullptr && plan.usable && path != 1;
+  if (path == 2 && !bucketed) return cudaErrorInvalidValue;
+  if (!bucketed) return standard_sort(a, nullptr);
+  cudaError_t e = bucketed_sort(a, plan);
+  if (e != cudaSuccess) return e;
+  // Runs only if the device found a bucket the finish kernel cannot hold.
+  const Header* hdr = static_cast<const Header*>(a.workspace);
+  return standard_sort(a, &hdr->use_standard);
 }
 
 }  // namespace
@@ -127,8 +137,9 @@ extern "C" int AetherSortAbiVersion(void) { return 1; }
 
 extern "C" size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload) {
   if (!count_ok(n) || num_cells <= 0 || key_bits_of(num_cells) > 32) return 0;
-  (void)with_payload;
-  return standard_workspace_bytes(n, num_cells);
+  const size_t standard = standard_workspace_bytes(n, num_cells);
+  if (!with_payload) return standard;
+  return std::max(standard, bucketed_workspace_bytes(n, num_cells));
 }
 
 extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const float* z,
@@ -152,7 +163,8 @@ extern "C" int AetherSortAndGatherParticles(
     int32_t* cell_counts, int32_t* cell_start, float* x_sorted, float* y_sorted, float* z_sorted,
     float* velocity_sorted, int64_t padded_sorted, int path, void* workspace,
     size_t workspace_bytes, void* stream) {
-  if (!grid || !x_sorted || !y_sorted || !z_sorted) return cudaErrorInvalidValue;
+  if (!grid) return cudaErrorInvalidValue;
+  if (n > 0 && (!x_sorted || !y_sorted || !z_sorted)) return cudaErrorInvalidValue;
   if ((velocity == nullptr) != (velocity_sorted == nullptr)) return cudaErrorInvalidValue;
   if (velocity && (padded < n || padded_sorted < n)) return cudaErrorInvalidValue;
   if (path < 0 || path > 2) return cudaErrorInvalidValue;

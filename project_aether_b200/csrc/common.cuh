@@ -138,15 +138,28 @@ struct SortArgs {
 };
 
 size_t standard_workspace_bytes(int64_t n, int64_t num_cells);
-cudaError_t standard_sort(const SortArgs& a);
+// `run_if`: device flag; when not null the kernels do nothing unless it is
+// nonzero (the hand-over from the bucketed path), and the first 8 bytes of the
+// workspace header (error code and that flag) are left as they are.
+cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if);
+
+struct BucketPlan {
+  int shift;        // a bucket is 2^shift consecutive cell ids
+  int64_t buckets;
+  bool usable;      // false when even single-cell buckets would be too full on average
+};
+BucketPlan plan_buckets(int64_t n, int64_t num_cells);
+size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells);
+cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p);
 cudaError_t launch_make_keys(const float* x, const float* y, const float* z, int64_t n,
                              const AetherGrid& g, uint64_t seed, uint32_t* keys,
                              cudaStream_t stream);
 cudaError_t launch_gather(const int32_t* index, int64_t n, const float* x, const float* y,
                           const float* z, const float* velocity, int64_t padded, float* xs,
                           float* ys, float* zs, float* vs, int64_t padded_sorted,
-                          cudaStream_t stream);
+                          cudaStream_t stream, const int32_t* run_if = nullptr);
 cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t num_cells,
-                               int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream);
+                               int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream,
+                               const int32_t* run_if = nullptr);
 
 }  // namespace aether

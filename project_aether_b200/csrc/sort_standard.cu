@@ -39,7 +39,9 @@ template <int PASSES, bool VEC>
 __global__ void __launch_bounds__(kKeygenThreads)
 keygen_upsweep_kernel(const float* __restrict__ x, const float* __restrict__ y,
                       const float* __restrict__ z, int64_t n, AetherGrid g, uint32_t k0,
-                      uint32_t k1, uint32_t* __restrict__ keys, uint32_t* __restrict__ global_hist) {
+                      uint32_t k1, uint32_t* __restrict__ keys, uint32_t* __restrict__ global_hist,
+                      const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
   __shared__ uint32_t hist[PASSES][kRadix];
   for (int i = threadIdx.x; i < PASSES * kRadix; i += kKeygenThreads) (&hist[0][0])[i] = 0;
   __syncthreads();
@@ -131,7 +133,9 @@ onesweep_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
                      int shift, const uint32_t* __restrict__ digit_total,
                      uint32_t* __restrict__ status, uint32_t* __restrict__ tile_counter,
-                     int32_t* __restrict__ error, uint32_t poll_limit) {
+                     int32_t* __restrict__ error, uint32_t poll_limit,
+                     const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -289,7 +293,8 @@ constexpr int kBoundsThreads = 256;
 // long runs of empty cells are filled by the whole warp.
 __global__ void __launch_bounds__(kBoundsThreads)
 cell_bounds_kernel(const uint32_t* __restrict__ keys, int64_t n, int64_t num_cells,
-                   int32_t* __restrict__ cell_start) {
+                   int32_t* __restrict__ cell_start, const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
   const int lane = threadIdx.x & 31;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kBoundsThreads;
   const int64_t rounds = (n + 1 + stride - 1) / stride;
@@ -319,7 +324,8 @@ cell_bounds_kernel(const uint32_t* __restrict__ keys, int64_t n, int64_t num_cel
 
 __global__ void __launch_bounds__(kBoundsThreads)
 cell_counts_kernel(const int32_t* __restrict__ cell_start, int64_t num_cells,
-                   int32_t* __restrict__ cell_counts) {
+                   int32_t* __restrict__ cell_counts, const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kBoundsThreads;
   for (int64_t c = static_cast<int64_t>(blockIdx.x) * kBoundsThreads + threadIdx.x; c < num_cells;
        c += stride)
@@ -337,7 +343,8 @@ gather_kernel(const int32_t* __restrict__ index, int64_t n, const float* __restr
               const float* __restrict__ y, const float* __restrict__ z,
               const float* __restrict__ v, int64_t padded, float* __restrict__ xs,
               float* __restrict__ ys, float* __restrict__ zs, float* __restrict__ vs,
-              int64_t padded_sorted) {
+              int64_t padded_sorted, const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kGatherThreads * 4;
   for (int64_t i0 = (static_cast<int64_t>(blockIdx.x) * kGatherThreads + threadIdx.x) * 4; i0 < n;
        i0 += stride) {
@@ -427,46 +434,48 @@ cudaError_t launch_make_keys(const float* x, const float* y, const float* z, int
 cudaError_t launch_gather(const int32_t* index, int64_t n, const float* x, const float* y,
                           const float* z, const float* velocity, int64_t padded, float* xs,
                           float* ys, float* zs, float* vs, int64_t padded_sorted,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const int32_t* run_if) {
   if (n == 0) return cudaSuccess;
   bool vec = aligned16(index) && aligned16(xs) && aligned16(ys) && aligned16(zs);
   if (velocity) vec = vec && aligned16(vs) && padded_sorted % 4 == 0;
   const int grid = grid_for(n, kGatherThreads * 4, 8);
   if (vec)
-    gather_kernel<true><<<grid, kGatherThreads, 0, stream>>>(index, n, x, y, z, velocity, padded,
-                                                             xs, ys, zs, vs, padded_sorted);
+    gather_kernel<true><<<grid, kGatherThreads, 0, stream>>>(
+        index, n, x, y, z, velocity, padded, xs, ys, zs, vs, padded_sorted, run_if);
   else
-    gather_kernel<false><<<grid, kGatherThreads, 0, stream>>>(index, n, x, y, z, velocity, padded,
-                                                              xs, ys, zs, vs, padded_sorted);
+    gather_kernel<false><<<grid, kGatherThreads, 0, stream>>>(
+        index, n, x, y, z, velocity, padded, xs, ys, zs, vs, padded_sorted, run_if);
   count_launches(1);
   return cudaGetLastError();
 }
 
 cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t num_cells,
-                               int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream) {
+                               int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream,
+                               const int32_t* run_if) {
   cell_bounds_kernel<<<grid_for(n + 1, kBoundsThreads, 8), kBoundsThreads, 0, stream>>>(
-      sorted_keys, n, num_cells, cell_start);
+      sorted_keys, n, num_cells, cell_start, run_if);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   cell_counts_kernel<<<grid_for(num_cells, kBoundsThreads, 8), kBoundsThreads, 0, stream>>>(
-      cell_start, num_cells, cell_counts);
+      cell_start, num_cells, cell_counts, run_if);
   count_launches(2);
   return cudaGetLastError();
 }
 
 template <int PASSES>
-static void launch_keygen(const SortArgs& a, bool vec, uint32_t* keys, Header* hdr) {
+static void launch_keygen(const SortArgs& a, bool vec, uint32_t* keys, Header* hdr,
+                          const int32_t* run_if) {
   const int grid = grid_for(a.n, kKeygenChunk, 8);
   const uint32_t k0 = static_cast<uint32_t>(a.seed), k1 = static_cast<uint32_t>(a.seed >> 32);
   if (vec)
     keygen_upsweep_kernel<PASSES, true><<<grid, kKeygenThreads, 0, a.stream>>>(
-        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0]);
+        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
   else
     keygen_upsweep_kernel<PASSES, false><<<grid, kKeygenThreads, 0, a.stream>>>(
-        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0]);
+        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
 }
 
-cudaError_t standard_sort(const SortArgs& a) {
+cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   const StandardLayout l = standard_layout(a.n, a.key_bits);
   if (a.workspace_bytes < l.total) return cudaErrorInvalidValue;
   auto* base = static_cast<unsigned char*>(a.workspace);
@@ -474,7 +483,10 @@ cudaError_t standard_sort(const SortArgs& a) {
   uint32_t* status = reinterpret_cast<uint32_t*>(base + l.status_off);
   uint32_t* keys_alt = reinterpret_cast<uint32_t*>(base + l.keys_alt_off);
   uint32_t* index_alt = reinterpret_cast<uint32_t*>(base + l.index_alt_off);
-  cudaError_t e = cudaMemsetAsync(base, 0, l.keys_alt_off, a.stream);
+  // Zero the header and the status words; a predicated run keeps the error
+  // code and the hand-over flag (the first 8 bytes).
+  const size_t keep = run_if ? 8 : 0;
+  cudaError_t e = cudaMemsetAsync(base + keep, 0, l.keys_alt_off - keep, a.stream);
   if (e != cudaSuccess) return e;
 
   if (a.n > 0) {
@@ -494,10 +506,10 @@ cudaError_t standard_sort(const SortArgs& a) {
     const bool vec = aligned16(a.x) && aligned16(a.y) && aligned16(a.z) && aligned16(cur_k);
     stage_begin(kStageKeygen, a.stream);
     switch (l.passes) {
-      case 1: launch_keygen<1>(a, vec, cur_k, hdr); break;
-      case 2: launch_keygen<2>(a, vec, cur_k, hdr); break;
-      case 3: launch_keygen<3>(a, vec, cur_k, hdr); break;
-      default: launch_keygen<4>(a, vec, cur_k, hdr); break;
+      case 1: launch_keygen<1>(a, vec, cur_k, hdr, run_if); break;
+      case 2: launch_keygen<2>(a, vec, cur_k, hdr, run_if); break;
+      case 3: launch_keygen<3>(a, vec, cur_k, hdr, run_if); break;
+      default: launch_keygen<4>(a, vec, cur_k, hdr, run_if); break;
     }
     stage_end(kStageKeygen, a.stream);
     count_launches(1);
@@ -510,12 +522,12 @@ cudaError_t standard_sort(const SortArgs& a) {
         onesweep_pass_kernel<true><<<static_cast<int>(l.tiles), kPassThreads, sizeof(PassSmem),
                                      a.stream>>>(cur_k, nullptr, nxt_k, nxt_v, a.n, 0,
                                                  hdr->digit_hist[0], st, &hdr->tile_counter[0],
-                                                 &hdr->error, kPollLimit);
+                                                 &hdr->error, kPollLimit, run_if);
       else
         onesweep_pass_kernel<false><<<static_cast<int>(l.tiles), kPassThreads, sizeof(PassSmem),
                                       a.stream>>>(cur_k, cur_v, nxt_k, nxt_v, a.n, kRadixBits * p,
                                                   hdr->digit_hist[p], st, &hdr->tile_counter[p],
-                                                  &hdr->error, kPollLimit);
+                                                  &hdr->error, kPollLimit, run_if);
       stage_end(static_cast<Stage>(kStagePass0 + p), a.stream);
       count_launches(1);
       e = cudaGetLastError();
@@ -525,13 +537,14 @@ cudaError_t standard_sort(const SortArgs& a) {
     }
   }
   stage_begin(kStageCellTables, a.stream);
-  e = launch_cell_tables(a.keys_out, a.n, a.num_cells, a.cell_counts, a.cell_start, a.stream);
+  e = launch_cell_tables(a.keys_out, a.n, a.num_cells, a.cell_counts, a.cell_start, a.stream,
+                         run_if);
   stage_end(kStageCellTables, a.stream);
   if (e != cudaSuccess) return e;
   if (a.xs) {
     stage_begin(kStageGather, a.stream);
     e = launch_gather(a.index_out, a.n, a.x, a.y, a.z, a.velocity, a.padded, a.xs, a.ys, a.zs,
-                      a.vs, a.padded_sorted, a.stream);
+                      a.vs, a.padded_sorted, a.stream, run_if);
     stage_end(kStageGather, a.stream);
   }
   return e;

@@ -13,7 +13,7 @@ from project_aether_b200 import workloads
 
 pytestmark = pytest.mark.gpu
 
-PATHS = [pa.PATH_DIGIT_PASSES]
+PATHS = [pa.PATH_DIGIT_PASSES, pa.PATH_AUTO]
 
 
 def _ogrid(grid):
@@ -137,6 +137,19 @@ def test_every_particle_in_one_cell_and_empty_cells(cuda, path):
     x[: n // 2] = 0.01
     z[: n // 2] = 0.01
     _check_all(x, y, z, vel, grid, 6, path)
+
+
+def test_more_than_255_equal_keys_in_a_bucket(cuda):
+    """The bucketed path counts equal keys of a bucket in byte-wide counters; a
+    bucket that overflows one must hand over to the digit passes, not corrupt."""
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (64, 64, 64))
+    n, seed = 60_000, 4242
+    x, y, z, vel = _random_state(n, grid, cuda, seed=9)
+    same = torch.from_numpy(so.shuffle_bits(n, seed) == 5).to(cuda)
+    assert int(same.sum()) > 300
+    x[same], y[same], z[same] = 0.51, 0.52, 0.53  # one cell, one shuffle value
+    got = _check_all(x, y, z, vel, grid, seed, pa.PATH_AUTO)
+    assert int(got.order.cell_counts.max()) >= int(same.sum())
 
 
 @pytest.mark.parametrize('path', PATHS)
