@@ -32,9 +32,9 @@ bool count_ok(int64_t n) { return n >= 0 && n < (int64_t{1} << 30); }
 
 int run_sort(SortArgs& a, int path) {
   if (!count_ok(a.n) || !grid_ok(&a.grid)) return cudaErrorInvalidValue;
-  if (!a.keys_out || !a.index_out || !a.cell_counts || !a.cell_start || !a.workspace)
+  if (!a.cell_counts || !a.cell_start || !a.workspace) return cudaErrorInvalidValue;
+  if (a.n > 0 && (!a.x || !a.y || !a.z || !a.keys_out || !a.index_out))
     return cudaErrorInvalidValue;
-  if (a.n > 0 && (!a.x || !a.y || !a.z)) return cudaErrorInvalidValue;
   if (reinterpret_cast<uintptr_t>(a.workspace) & 255) return cudaErrorInvalidValue;
   a.num_cells = static_cast<int64_t>(a.grid.nx_local) * a.grid.ny * a.grid.nz;
   a.key_bits = key_bits_of(a.num_cells);

@@ -26,6 +26,7 @@ constexpr uint32_t kValueMask = ~kFlagMask;
 // Error codes left in the workspace header by a device wait that gave up.
 constexpr int kErrLookbackTimeout = 1;
 constexpr int kErrBucketOverflow = 2;
+constexpr int kErrBulkCopyTimeout = 3;
 
 // Workspace header (first 1 KiB of the workspace, zeroed by every call).
 struct alignas(16) Header {

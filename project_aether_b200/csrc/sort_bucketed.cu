@@ -186,35 +186,46 @@ __device__ __forceinline__ uint32_t reserve_slot(uint32_t* cursor, uint32_t b, b
   return slot;
 }
 
-template <bool VEC>
-__global__ void __launch_bounds__(kScatterThreads, 2)
+// ITEMS consecutive particles per thread and round (4: 128-bit loads, 2: 64-bit
+// loads with twice the resident threads to keep more slot reservations in flight).
+template <int ITEMS>
+__device__ __forceinline__ void load_items(const float* p, float* out) {
+  if (ITEMS == 4) {
+    const float4 a = ldcs4(p);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+  } else {
+    const float2 a = __ldcs(reinterpret_cast<const float2*>(p));
+    out[0] = a.x; out[1] = a.y;
+  }
+}
+
+template <bool VEC, int ITEMS>
+__global__ void __launch_bounds__(kScatterThreads, 8 / ITEMS)
 bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                       const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                       int64_t n, AetherGrid g, uint32_t k0, uint32_t k1, int shift,
                       uint32_t* __restrict__ cursor, uint32_t* __restrict__ records,
                       const Header* __restrict__ hdr) {
   if (hdr->use_standard) return;
-  const int64_t groups = (n + 3) / 4;
+  const int64_t groups = (n + ITEMS - 1) / ITEMS;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kScatterThreads;
   const int64_t rounds = (groups + stride - 1) / stride;
   for (int64_t r = 0; r < rounds; ++r) {
     const int64_t i0 = (r * stride + static_cast<int64_t>(blockIdx.x) * kScatterThreads +
-                        threadIdx.x) * 4;
-    float f[6][4];
-    if (VEC && i0 + 4 <= n) {
-      const float4 a = ldcs4(x + i0), b = ldcs4(y + i0), c = ldcs4(z + i0);
-      f[0][0] = a.x; f[0][1] = a.y; f[0][2] = a.z; f[0][3] = a.w;
-      f[1][0] = b.x; f[1][1] = b.y; f[1][2] = b.z; f[1][3] = b.w;
-      f[2][0] = c.x; f[2][1] = c.y; f[2][2] = c.z; f[2][3] = c.w;
+                        threadIdx.x) * ITEMS;
+    float f[6][ITEMS];
+    if (VEC && i0 + ITEMS <= n) {
+      load_items<ITEMS>(x + i0, f[0]);
+      load_items<ITEMS>(y + i0, f[1]);
+      load_items<ITEMS>(z + i0, f[2]);
       if (v) {
-        const float4 d = ldcs4(v + i0), e = ldcs4(v + padded + i0), h = ldcs4(v + 2 * padded + i0);
-        f[3][0] = d.x; f[3][1] = d.y; f[3][2] = d.z; f[3][3] = d.w;
-        f[4][0] = e.x; f[4][1] = e.y; f[4][2] = e.z; f[4][3] = e.w;
-        f[5][0] = h.x; f[5][1] = h.y; f[5][2] = h.z; f[5][3] = h.w;
+        load_items<ITEMS>(v + i0, f[3]);
+        load_items<ITEMS>(v + padded + i0, f[4]);
+        load_items<ITEMS>(v + 2 * padded + i0, f[5]);
       }
     } else {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < ITEMS; ++k) {
         const bool ok = i0 + k < n;
         f[0][k] = ok ? x[i0 + k] : 0.f;
         f[1][k] = ok ? y[i0 + k] : 0.f;
@@ -226,19 +237,21 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     }
     if (!v) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) f[3][k] = f[4][k] = f[5][k] = 0.f;
+      for (int k = 0; k < ITEMS; ++k) f[3][k] = f[4][k] = f[5][k] = 0.f;
+    }
+    uint32_t key[ITEMS], slot[ITEMS];
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t cell = cell_of(f[0][k], f[1][k], f[2][k], g);
+      slot[k] = reserve_slot(cursor, cell >> shift, i0 + k < n);
+      key[k] = make_key(cell, static_cast<uint32_t>(i0 + k), k0, k1);
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const bool ok = i0 + k < n;
-      const uint32_t cell = cell_of(f[0][k], f[1][k], f[2][k], g);
-      const uint32_t index = static_cast<uint32_t>(i0 + k);
-      const uint32_t key = make_key(cell, index, k0, k1);
-      const uint32_t slot = reserve_slot(cursor, cell >> shift, ok);
-      if (ok)
-        store_record(records + static_cast<size_t>(slot) * kRecordWords, key, index, f[0][k],
-                     f[1][k], f[2][k], f[3][k], f[4][k], f[5][k]);
-    }
+    for (int k = 0; k < ITEMS; ++k)
+      if (i0 + k < n)
+        store_record(records + static_cast<size_t>(slot[k]) * kRecordWords, key[k],
+                     static_cast<uint32_t>(i0 + k), f[0][k], f[1][k], f[2][k], f[3][k], f[4][k],
+                     f[5][k]);
   }
 }
 
@@ -246,25 +259,64 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 // Finish: one block sorts one bucket in shared memory and writes the output.
 // ------------------------------------------------------------------------
 constexpr int kFinishThreads = 1024;
-constexpr int kFinishCapacity = 5632;                      // records per bucket
+constexpr int kFinishCapacity = 5376;                      // records per bucket
 constexpr int kFinishItems = (kFinishCapacity + kFinishThreads - 1) / kFinishThreads;  // 6
 constexpr int kMaxLowBits = 15;                            // (cell bits in bucket) + 7
 constexpr int kHistWords = (1 << kMaxLowBits) / 4;         // byte counters, 4 per word
 constexpr int kWordsPerThread = kHistWords / kFinishThreads;  // 8
+constexpr uint32_t kBulkChunkBytes = 32768;                // bytes per bulk copy
+constexpr uint32_t kBulkWaitLimit = 1u << 24;              // polls of the copy barrier
 
-struct FinishSmem {
+struct __align__(128) FinishSmem {
+  uint32_t raw[kFinishCapacity * kRecordWords];  // the bucket's records as they lie in HBM
   uint32_t hist[kHistWords];     // byte counter per low-key value; later: final order (u16)
   uint16_t word_prefix[kHistWords];  // exclusive prefix of each counter word
   uint16_t slot_of[kFinishCapacity];  // record held by each sorted slot (before the tie pass)
-  uint16_t low_key[kFinishCapacity];  // low key bits of each sorted slot
-  uint32_t index[kFinishCapacity];
-  float field[6][kFinishCapacity];
   uint32_t warp_sum[32];
   uint32_t total;
+  uint32_t gave_up;
+  unsigned long long barrier;    // mbarrier of the bulk copy
 };
 static_assert(sizeof(FinishSmem) <= 227 * 1024, "finish kernel shared memory");
 
 __device__ __forceinline__ uint32_t byte_sum(uint32_t w) { return __dp4a(w, 0x01010101u, 0u); }
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// Starts the copy of `bytes` (a multiple of 16, source 16-byte aligned) from
+// global to shared memory with the bulk-copy engine; completion is counted on
+// the mbarrier.  One thread calls this.
+__device__ __forceinline__ void bulk_load_start(void* dst, const void* src, uint32_t bytes,
+                                                unsigned long long* barrier) {
+  const uint32_t bar = smem_addr(barrier);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+  for (uint32_t done = 0; done < bytes; done += kBulkChunkBytes) {
+    const uint32_t part = min(kBulkChunkBytes, bytes - done);
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_addr(static_cast<unsigned char*>(dst) + done)),
+          "l"(static_cast<const unsigned char*>(src) + done), "r"(part), "r"(bar)
+        : "memory");
+  }
+}
+
+// Waits (bounded) for the phase `parity` of the copy barrier; false if it gave up.
+__device__ __forceinline__ bool bulk_load_wait(unsigned long long* barrier, uint32_t parity) {
+  const uint32_t bar = smem_addr(barrier);
+  for (uint32_t polls = 0; polls < kBulkWaitLimit; ++polls) {
+    uint32_t ready;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ready) : "r"(bar), "r"(parity) : "memory");
+    if (ready) return true;
+  }
+  return false;
+}
 
 __global__ void __launch_bounds__(kFinishThreads, 1)
 bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __restrict__ bucket_start,
@@ -274,13 +326,21 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
                      float* __restrict__ xs, float* __restrict__ ys, float* __restrict__ zs,
                      float* __restrict__ vs, int64_t padded_sorted, Header* __restrict__ hdr) {
   if (hdr->use_standard) return;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   FinishSmem& s = *reinterpret_cast<FinishSmem*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int low_bits = shift + kShuffleBits;
   const uint32_t low_mask = (1u << low_bits) - 1;
   const int hist_words = max(1, (1 << low_bits) / 4);
   uint16_t* final_slot = reinterpret_cast<uint16_t*>(s.hist);  // reused after the scan is consumed
+
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s.barrier)) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    s.gave_up = 0;
+  }
+  __syncthreads();
+  uint32_t parity = 0;
 
   for (int b = blockIdx.x; b < buckets; b += gridDim.x) {
     const uint32_t begin = bucket_start[b], end = bucket_start[b + 1];
@@ -289,27 +349,32 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       if (tid == 0) hdr->use_standard = 1;
       continue;
     }
+    // The bucket is one contiguous run of 32-byte records: fetch it with bulk
+    // copies while the counters are cleared.
+    if (tid == 0 && count > 0)
+      bulk_load_start(s.raw, records + static_cast<size_t>(begin) * kRecordWords,
+                      static_cast<uint32_t>(count) * kRecordWords * 4u, &s.barrier);
     for (int i = tid; i < hist_words; i += kFinishThreads) s.hist[i] = 0;
     __syncthreads();
+    if (count > 0) {
+      if (!bulk_load_wait(&s.barrier, parity)) s.gave_up = 1;
+      parity ^= 1;
+    }
+    __syncthreads();
+    if (s.gave_up) {  // the copy never landed: report and stop without touching the output
+      if (tid == 0) atomicCAS(&hdr->error, 0, kErrBulkCopyTimeout);
+      return;
+    }
 
-    // Load the bucket: one 32-byte record per lane and load; keep the payload in
-    // shared memory (SoA) and count the low key bits with byte-wide counters.
+    // Count the low key bits with byte-wide counters; the value an add returns
+    // is the record's rank among equal keys.
     uint32_t packed[kFinishItems];  // low key | rank among equal keys << 16
 #pragma unroll
     for (int k = 0; k < kFinishItems; ++k) {
       const int r = tid + k * kFinishThreads;
       packed[k] = 0;
       if (r < count) {
-        uint32_t w[8];
-        const uint32_t* src = records + (static_cast<size_t>(begin) + r) * kRecordWords;
-        asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]),
-                       "=r"(w[6]), "=r"(w[7])
-                     : "l"(src));
-        s.index[r] = w[1];
-#pragma unroll
-        for (int c = 0; c < 6; ++c) s.field[c][r] = __uint_as_float(w[2 + c]);
-        const uint32_t low = w[0] & low_mask;
+        const uint32_t low = s.raw[r * kRecordWords] & low_mask;
         const int sh = 8 * (low & 3);
         const uint32_t old = atomicAdd(&s.hist[low >> 2], 1u << sh);
         packed[k] = low | (((old >> sh) & 0xffu) << 16);
@@ -384,9 +449,7 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
         const uint32_t low = packed[k] & 0xffffu, rank = packed[k] >> 16;
         const uint32_t word = s.hist[low >> 2];
         const uint32_t below = byte_sum(word & ((1u << (8 * (low & 3))) - 1u));
-        const uint32_t slot = s.word_prefix[low >> 2] + below + rank;
-        s.slot_of[slot] = static_cast<uint16_t>(r);
-        s.low_key[slot] = static_cast<uint16_t>(low);
+        s.slot_of[s.word_prefix[low >> 2] + below + rank] = static_cast<uint16_t>(r);
       }
     }
     __syncthreads();
@@ -394,39 +457,42 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
     // Equal keys must appear in ascending original index: a slot inside a run
     // of equal keys moves to (run start + number of smaller indices in the run).
     for (int d = tid; d < count; d += kFinishThreads) {
-      const uint16_t key = s.low_key[d];
       const uint16_t rec = s.slot_of[d];
+      const uint32_t key = s.raw[rec * kRecordWords];
       int dst = d;
-      const bool tie = (d > 0 && s.low_key[d - 1] == key) || (d + 1 < count && s.low_key[d + 1] == key);
+      const bool tie = (d > 0 && s.raw[s.slot_of[d - 1] * kRecordWords] == key) ||
+                       (d + 1 < count && s.raw[s.slot_of[d + 1] * kRecordWords] == key);
       if (tie) {
-        const uint32_t mine = s.index[rec];
+        const uint32_t mine = s.raw[rec * kRecordWords + 1];
         int lo = d, smaller = 0;
-        while (lo > 0 && s.low_key[lo - 1] == key) {
+        while (lo > 0 && s.raw[s.slot_of[lo - 1] * kRecordWords] == key) {
           --lo;
-          smaller += s.index[s.slot_of[lo]] < mine;
+          smaller += s.raw[s.slot_of[lo] * kRecordWords + 1] < mine;
         }
-        for (int j = d + 1; j < count && s.low_key[j] == key; ++j)
-          smaller += s.index[s.slot_of[j]] < mine;
+        for (int j = d + 1; j < count && s.raw[s.slot_of[j] * kRecordWords] == key; ++j)
+          smaller += s.raw[s.slot_of[j] * kRecordWords + 1] < mine;
         dst = lo + smaller;
       }
       final_slot[dst] = rec;
     }
     __syncthreads();
 
-    // Coalesced output.
-    const uint32_t key_high = static_cast<uint32_t>(b) << low_bits;
+    // Coalesced output: each lane pulls one whole record out of shared memory
+    // and writes its eight words to the eight output arrays.
     for (int d = tid; d < count; d += kFinishThreads) {
       const int rec = final_slot[d];
+      const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords]);
+      const uint4 c = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4]);
       const size_t o = static_cast<size_t>(begin) + d;
-      keys_out[o] = (low_bits < 32 ? key_high : 0u) | s.low_key[d];
-      index_out[o] = static_cast<int32_t>(s.index[rec]);
-      xs[o] = s.field[0][rec];
-      ys[o] = s.field[1][rec];
-      zs[o] = s.field[2][rec];
+      __stcs(keys_out + o, a.x);
+      __stcs(index_out + o, static_cast<int32_t>(a.y));
+      __stcs(xs + o, __uint_as_float(a.z));
+      __stcs(ys + o, __uint_as_float(a.w));
+      __stcs(zs + o, __uint_as_float(c.x));
       if (vs) {
-        vs[o] = s.field[3][rec];
-        vs[padded_sorted + o] = s.field[4][rec];
-        vs[2 * padded_sorted + o] = s.field[5][rec];
+        __stcs(vs + o, __uint_as_float(c.y));
+        __stcs(vs + padded_sorted + o, __uint_as_float(c.z));
+        __stcs(vs + 2 * padded_sorted + o, __uint_as_float(c.w));
       }
     }
     __syncthreads();
@@ -527,10 +593,12 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
 
   stage_begin(kStageBucketScatter, a.stream);
   {
-    const int64_t groups = (a.n + 3) / 4;
+    constexpr int kItems = 2;
+    const int64_t groups = (a.n + kItems - 1) / kItems;
     const int grid = static_cast<int>(std::max<int64_t>(
-        1, std::min<int64_t>((groups + kScatterThreads - 1) / kScatterThreads, kSmCount * 2)));
-    auto kernel = vec ? bucket_scatter_kernel<true> : bucket_scatter_kernel<false>;
+        1, std::min<int64_t>((groups + kScatterThreads - 1) / kScatterThreads,
+                             kSmCount * (8 / kItems))));
+    auto kernel = vec ? bucket_scatter_kernel<true, kItems> : bucket_scatter_kernel<false, kItems>;
     kernel<<<grid, kScatterThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.n,
                                                     a.grid, k0, k1, p.shift, cursor, records, hdr);
   }
