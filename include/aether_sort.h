@@ -87,6 +87,22 @@ int AetherMakeKeys(const float* x, const float* y, const float* z, int64_t n,
  * `stream`, reads the code back and stores it in *status (0 = clean). */
 int AetherSortReadStatus(const void* workspace, void* stream, int32_t* status);
 
+/* Multi-GPU step 1: stable partition of this rank's particles by destination
+ * x-slab.  With `world` ranks (1..8, nx divisible by world) rank r owns global
+ * ix in [r*nx/world, (r+1)*nx/world); ix is computed with the global grid as in
+ * fused_radix_sort.py:93.  Writes six contiguous arrays (x, y, z, vx, vy, vz),
+ * each ordered by destination rank and, inside one destination, in the input
+ * order; counts_out[d] (device, int64) receives the number of particles bound
+ * for rank d.  The reference has no multi-GPU particle path; the ordering rule
+ * matches its all-to-all convention "row s holds what rank s sent"
+ * (project_aether/src/distributed_infra/sccl_synthesizer.py:468-485). */
+size_t AetherSlabPartitionWorkspaceBytes(int64_t n, int world);
+int AetherSlabPartition(const float* x, const float* y, const float* z, const float* velocity,
+                        int64_t padded, int64_t n, const AetherGrid* grid, int world,
+                        float* x_out, float* y_out, float* z_out, float* vx_out, float* vy_out,
+                        float* vz_out, int64_t* counts_out, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
 /* Measurement hooks.  The reference times whole calls with CUDA events around
  * the Python entry point (project_aether/scripts/phase2_triton_sort_benchmark.py:
  * 73-84); these give the same kind of event timing per stage of one call.

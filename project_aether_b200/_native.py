@@ -39,6 +39,10 @@ _SIGNATURES = {
     'AetherMakeKeys': (ctypes.c_int, [_P, _P, _P, _I64, ctypes.POINTER(AetherGrid),
                                       ctypes.c_uint64, _P, _P]),
     'AetherSortReadStatus': (ctypes.c_int, [_P, _P, ctypes.POINTER(ctypes.c_int32)]),
+    'AetherSlabPartitionWorkspaceBytes': (ctypes.c_size_t, [_I64, ctypes.c_int]),
+    'AetherSlabPartition': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.POINTER(AetherGrid),
+                                           ctypes.c_int, _P, _P, _P, _P, _P, _P, _P, _P,
+                                           ctypes.c_size_t, _P]),
     'AetherSortSetStageTiming': (ctypes.c_int, [ctypes.c_int]),
     'AetherSortStageCount': (ctypes.c_int, []),
     'AetherSortStageName': (ctypes.c_char_p, [ctypes.c_int]),

@@ -210,3 +210,24 @@ extern "C" int AetherSortReadStatus(const void* workspace, void* stream, int32_t
   if (e != cudaSuccess) return e;
   return cudaStreamSynchronize(s);
 }
+
+extern "C" size_t AetherSlabPartitionWorkspaceBytes(int64_t n, int world) {
+  if (!count_ok(n) || world < 1 || world > 8) return 0;
+  return slab_partition_workspace_bytes(n, world);
+}
+
+extern "C" int AetherSlabPartition(const float* x, const float* y, const float* z,
+                                   const float* velocity, int64_t padded, int64_t n,
+                                   const AetherGrid* grid, int world, float* x_out, float* y_out,
+                                   float* z_out, float* vx_out, float* vy_out, float* vz_out,
+                                   int64_t* counts_out, void* workspace, size_t workspace_bytes,
+                                   void* stream) {
+  if (!count_ok(n) || !grid_ok(grid) || !counts_out || !workspace) return cudaErrorInvalidValue;
+  if (world < 1 || world > 8 || grid->nx % world != 0) return cudaErrorInvalidValue;
+  if (n > 0 && (!x || !y || !z || !velocity || !x_out || !y_out || !z_out || !vx_out || !vy_out ||
+                !vz_out || padded < n))
+    return cudaErrorInvalidValue;
+  return slab_partition(x, y, z, velocity, padded, n, *grid, world, x_out, y_out, z_out, vx_out,
+                        vy_out, vz_out, counts_out, workspace, workspace_bytes,
+                        static_cast<cudaStream_t>(stream));
+}

@@ -152,6 +152,13 @@ struct BucketPlan {
 BucketPlan plan_buckets(int64_t n, int64_t num_cells);
 size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells);
 cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p);
+
+size_t slab_partition_workspace_bytes(int64_t n, int world);
+cudaError_t slab_partition(const float* x, const float* y, const float* z, const float* v,
+                           int64_t padded, int64_t n, const AetherGrid& g, int world, float* ox,
+                           float* oy, float* oz, float* ovx, float* ovy, float* ovz,
+                           int64_t* totals, void* workspace, size_t workspace_bytes,
+                           cudaStream_t stream);
 cudaError_t launch_make_keys(const float* x, const float* y, const float* z, int64_t n,
                              const AetherGrid& g, uint64_t seed, uint32_t* keys,
                              cudaStream_t stream);

@@ -1,0 +1,134 @@
+"""The N > 1 leg of bench.py: one rank per GPU, x-slab decomposition.
+
+Every rank starts with a random 1/G share of all particles drawn over the whole
+box (generator seed 0 + rank), so (G-1)/G of them must leave in the exchange.
+One step = partition by slab, count exchange, all-to-all, local sort.
+"""
+
+import ctypes
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def run(args, workload: str) -> None:
+    import project_aether_b200 as pa
+    from project_aether_b200 import _native, slab_sort, workloads
+    import bench as bench_mod  # the launcher script (repo root is on sys.path)
+
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', str(args.gpus)))
+    local = int(os.environ.get('LOCAL_RANK', str(rank)))
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    os.environ.setdefault('MASTER_PORT', '29512')
+    device = torch.device('cuda', local)
+    torch.cuda.set_device(device)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+    lib = _native.load_library()
+    w = workloads.WORKLOADS[workload]
+    n_total = w.n
+    n_local = n_total // world
+    x, y, z, v = workloads.make_particles(w, device, seed=rank, n=n_local)
+
+    def step(s):
+        return slab_sort.distributed_sort(x, y, z, v, w.grid, workloads.step_seed(1234, s))
+
+    warmup = max(3, args.warmup)
+    for s in range(warmup):
+        out = step(s)
+    torch.cuda.synchronize()
+    status = torch.tensor([pa.last_sort_status(device)], device=device)
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    assert int(status) == 0
+
+    lib.AetherSortSetStageTiming(1)
+    launches0 = lib.AetherSortKernelLaunches()
+    sampler = bench_mod.ClockSampler(device.index)
+    if rank == 0:
+        sampler.start()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    begin.record()
+    for s in range(args.steps):
+        out = step(100 + s)
+    end.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed = torch.tensor([begin.elapsed_time(end)], device=device)
+    dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms = float(elapsed) / args.steps
+    launches = int(lib.AetherSortKernelLaunches() - launches0)
+    count = lib.AetherSortStageCount()
+    stage_ms = (ctypes.c_float * count)()
+    _native.check(lib.AetherSortReadStageTimes(stage_ms, count), 'AetherSortReadStageTimes')
+    lib.AetherSortSetStageTiming(0)
+    stages = {lib.AetherSortStageName(i).decode(): float(stage_ms[i]) for i in range(count)
+              if stage_ms[i] >= 0}
+    received = torch.tensor([out.order.keys.numel()], device=device, dtype=torch.int64)
+    dist.all_reduce(received)
+    assert int(received) == n_local * world, 'particles were lost in the exchange'
+
+    # End to end: pinned host inputs in, results back to the host, every step.
+    e2e_steps = max(1, min(args.steps, 3))
+    hx, hy, hz, hv = (t.cpu().pin_memory() for t in (x, y, z, v))
+    d2h = [0]
+
+    def e2e_step(s):
+        dx, dy, dz, dv = (t.to(device, non_blocking=True) for t in (hx, hy, hz, hv))
+        r = slab_sort.distributed_sort(dx, dy, dz, dv, w.grid, workloads.step_seed(1234, s))
+        outs = [r.order.keys, r.order.particle_index, r.order.cell_counts, r.order.cell_start,
+                *r.positions, r.velocity]
+        host = [o.to('cpu', non_blocking=False) for o in outs]
+        d2h[0] = sum(h.numel() * h.element_size() for h in host)
+
+    e2e_step(0)
+    dist.barrier()
+    torch.cuda.synchronize()
+    begin.record()
+    for s in range(e2e_steps):
+        e2e_step(200 + s)
+    end.record()
+    torch.cuda.synchronize()
+    e2e_elapsed = torch.tensor([begin.elapsed_time(end)], device=device)
+    dist.all_reduce(e2e_elapsed, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_elapsed) / e2e_steps
+    bytes_io = torch.tensor([sum(t.numel() * t.element_size() for t in (hx, hy, hz, hv)), d2h[0]],
+                            device=device, dtype=torch.int64)
+    dist.all_reduce(bytes_io)
+
+    if rank == 0:
+        peak, peak_kind = bench_mod.measured_peak()
+        n_rank = n_total // world
+        top = max(stages, key=stages.get) if stages else None
+        roofline = None
+        if top:
+            per_particle = bench_mod.STAGE_BYTES_PER_PARTICLE.get(top, 48 if top == 'slab_partition' else 0)
+            nbytes = per_particle * n_rank
+            achieved = nbytes / (stages[top] * 1e-3) / 1e9
+            roofline = {'bound': 'hbm', 'kernel': top, 'achieved': achieved, 'peak': peak,
+                        'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind,
+                        'traffic': None, 'bytes_per_launch': nbytes, 'ms_per_launch': stages[top]}
+        line = {
+            'metric': 'sorted particles/s', 'value': n_total / (ms * 1e-3), 'unit': 'particles/s',
+            'n_gpus': world, 'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms,
+            'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'u32',
+            'data': 'synthetic',
+            'config': {'workload': workload, 'particles': n_total, 'cells': list(w.grid.cells),
+                       'decomposition': f'{world} x-slabs, one all-to-all per payload array',
+                       'initial_share': 'random 1/G of all particles per rank',
+                       'l2': 'inputs larger than L2 (no flush needed)'},
+            'clocks': {'sm_mhz': clocks['sm_mhz'], 'sm_max_mhz': clocks['sm_max_mhz'],
+                       'reasons': clocks['reasons'], 'samples': clocks['samples']},
+            'e2e': {'value': n_total / (e2e_ms * 1e-3), 'unit': 'particles/s',
+                    'h2d_bytes_per_step': int(bytes_io[0]), 'd2h_bytes_per_step': int(bytes_io[1]),
+                    'ms_per_step': e2e_ms, 'steps': e2e_steps},
+            'gpu_launches': launches, 'roofline': roofline, 'stage_ms_rank0': stages,
+            'cpu_baseline': None,
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()

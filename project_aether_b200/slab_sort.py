@@ -1,0 +1,114 @@
+"""Multi-GPU particle sort: x-slab decomposition, one all-to-all, local sort.
+
+The reference's particle path is single-device
+(project_aether/src/physics_engine/dsmc_gpu_pipeline.py:85-113); this module is
+the slab extension the benchmark definition asks for.  With G ranks (one per
+GPU, `torch.distributed`), rank r owns the global columns
+ix in [r*nx/G, (r+1)*nx/G).  One sort is
+
+  1. a stable partition of the rank's particles by destination slab (CUDA,
+     `AetherSlabPartition`);
+  2. an exchange of the GxG counts and one variable-size all-to-all per payload
+     array (NCCL over NVLink);
+  3. the local sort with slab-local cell ids (`ix_offset`, `nx_local`).
+
+Ordering rule, which fixes the Philox counter of every particle and so the
+result: rank d's array after the exchange is the concatenation over source
+ranks s = 0..G-1 of the particles s sent to d, each block in s's original order.
+"""
+
+import ctypes
+from typing import List, NamedTuple, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+from .cell_grid import CellGrid
+from .particle_sort import (PATH_AUTO, SortedParticles, _workspace, native_grid,
+                            sort_and_gather_particles)
+
+
+class SlabParts(NamedTuple):
+    arrays: Tuple[torch.Tensor, ...]  # x, y, z, vx, vy, vz ordered by destination
+    counts: torch.Tensor              # int64 (world,), on the device
+
+
+def slab_range(grid: CellGrid, world: int, rank: int) -> Tuple[int, int]:
+    """(ix_offset, nx_local) of a rank's slab."""
+    nx = grid.cells[0]
+    if world < 1 or nx % world:
+        raise ValueError(f'nx = {nx} is not divisible by {world} ranks')
+    width = nx // world
+    return rank * width, width
+
+
+def partition_by_slab(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
+                      velocity: torch.Tensor, grid: CellGrid, world: int) -> SlabParts:
+    """Stable partition by destination rank on the GPU (no host synchronisation)."""
+    n, device = x.numel(), x.device
+    if not (x.is_cuda and velocity.is_cuda and velocity.dim() == 2 and velocity.shape[0] == 3
+            and velocity.shape[1] >= n and x.dtype == torch.float32):
+        raise ValueError('partition_by_slab needs float32 CUDA positions and a (3, padded) '
+                         'float32 CUDA velocity.')
+    slab_range(grid, world, 0)
+    lib = _native.load_library()
+    g = native_grid(grid)
+    velocity = velocity.contiguous()
+    with torch.cuda.device(device):
+        outs = tuple(torch.empty(n, dtype=torch.float32, device=device) for _ in range(6))
+        counts = torch.zeros(world, dtype=torch.int64, device=device)
+        ws = _workspace(device, lib.AetherSlabPartitionWorkspaceBytes(n, world))
+        stream = torch.cuda.current_stream(device).cuda_stream
+        _native.check(lib.AetherSlabPartition(
+            x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(), velocity.shape[1], n,
+            ctypes.byref(g), world, *(o.data_ptr() for o in outs), counts.data_ptr(),
+            ws.data_ptr(), ws.numel(), ctypes.c_void_p(stream)), 'AetherSlabPartition')
+    return SlabParts(outs, counts)
+
+
+def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    """All ranks' send counts: result[s, d] = particles rank s sends to rank d (on the host)."""
+    world = dist.get_world_size(group)
+    gathered = [torch.empty_like(send_counts) for _ in range(world)]
+    dist.all_gather(gathered, send_counts, group=group)
+    return torch.stack(gathered).cpu()
+
+
+def exchange_particles(arrays: Sequence[torch.Tensor], matrix: torch.Tensor,
+                       group=None) -> List[torch.Tensor]:
+    """One variable-size all-to-all per array.  `arrays` are ordered by destination;
+    `matrix[s, d]` is the host-side count matrix.  Returns the received arrays, each the
+    concatenation of the blocks from source 0..G-1."""
+    rank = dist.get_rank(group)
+    send = [int(c) for c in matrix[rank]]
+    recv = [int(c) for c in matrix[:, rank]]
+    if sum(send) != arrays[0].numel():
+        raise RuntimeError(f'rank {rank}: send counts {sum(send)} do not match the '
+                           f'{arrays[0].numel()} partitioned particles')
+    out = []
+    for a in arrays:
+        r = torch.empty(sum(recv), dtype=a.dtype, device=a.device)
+        dist.all_to_all_single(r, a, output_split_sizes=recv, input_split_sizes=send, group=group)
+        out.append(r)
+    return out
+
+
+def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity: torch.Tensor,
+                     grid: CellGrid, seed: int, group=None, path: int = PATH_AUTO
+                     ) -> SortedParticles:
+    """Sorts the particles of all ranks by cell; every rank ends with its slab's
+    particles, cell-sorted, with slab-local `cell_counts` / `cell_start`."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    ix_offset, nx_local = slab_range(grid, world, rank)
+    if world == 1:
+        return sort_and_gather_particles(x, y, z, velocity, grid, seed, path=path)
+    parts = partition_by_slab(x, y, z, velocity, grid, world)
+    matrix = exchange_counts(parts.counts, group)
+    rx, ry, rz, rvx, rvy, rvz = exchange_particles(parts.arrays, matrix, group)
+    n = rx.numel()
+    padded = -(-n // 4) * 4
+    rv = torch.zeros((3, padded), dtype=torch.float32, device=rx.device)
+    rv[0, :n], rv[1, :n], rv[2, :n] = rvx, rvy, rvz
+    return sort_and_gather_particles(rx, ry, rz, rv, grid, seed, ix_offset=ix_offset,
+                                     nx_local=nx_local, path=path)
