@@ -103,6 +103,33 @@ int AetherSlabPartition(const float* x, const float* y, const float* z, const fl
                         float* vz_out, int64_t* counts_out, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* The same sort for callers that cannot allocate device memory: a plugin that
+ * runs inside a host application which has already handed all of the GPU's
+ * memory to its own pool, or a step of a real-time loop in which cudaMalloc
+ * (which synchronises the whole device) is forbidden.  Such a caller has no
+ * workspace to pass, so this entry point keeps the scratch of the digit-pass
+ * sort in a fixed array inside the library image (9 MiB, reserved on every GPU
+ * that loads the library until the process exits) and allocates nothing: no
+ * cudaMalloc, no cudaFree, no allocating library routine.  It has no
+ * counterpart in the reference, whose driver allocates about ten tensors per
+ * call (fused_radix_sort.py:245-263).
+ *   - Limit: n <= AetherSortStaticMaxParticles() (2^20); larger counts, or a
+ *     grid whose scratch would not fit, return cudaErrorInvalidValue before
+ *     anything is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) with that device current; make that first call
+ *     outside any stream capture.
+ *   - All calls share the one array.  It keeps the previous call's contents; the
+ *     call clears the part that must start at zero itself.  Two calls whose
+ *     work overlaps on the GPU (different streams, no dependency) race on it:
+ *     serialise them.
+ * Inputs, outputs and results are those of AetherSortParticlesByCell. */
+int64_t AetherSortStaticMaxParticles(void);
+int AetherSortParticlesByCellStatic(const float* x, const float* y, const float* z, int64_t n,
+                                    const AetherGrid* grid, uint64_t seed, uint32_t* keys_out,
+                                    int32_t* index_out, int32_t* cell_counts, int32_t* cell_start,
+                                    void* stream);
+
 /* Measurement hooks.  The reference times whole calls with CUDA events around
  * the Python entry point (project_aether/scripts/phase2_triton_sort_benchmark.py:
  * 73-84); these give the same kind of event timing per stage of one call.

@@ -43,6 +43,10 @@ _SIGNATURES = {
     'AetherSlabPartition': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.POINTER(AetherGrid),
                                            ctypes.c_int, _P, _P, _P, _P, _P, _P, _P, _P,
                                            ctypes.c_size_t, _P]),
+    'AetherSortStaticMaxParticles': (ctypes.c_int64, []),
+    'AetherSortParticlesByCellStatic': (ctypes.c_int, [_P, _P, _P, _I64,
+                                                       ctypes.POINTER(AetherGrid),
+                                                       ctypes.c_uint64, _P, _P, _P, _P, _P]),
     'AetherSortSetStageTiming': (ctypes.c_int, [ctypes.c_int]),
     'AetherSortStageCount': (ctypes.c_int, []),
     'AetherSortStageName': (ctypes.c_char_p, [ctypes.c_int]),
