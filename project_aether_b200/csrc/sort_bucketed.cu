@@ -635,14 +635,21 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
     }
     __syncthreads();
 
-    // Exclusive scan of the counters (8 words = 32 counters per thread).
+    // Exclusive scan of the counters (8 words = 32 counters per thread, fetched
+    // as two 128-bit loads so that neighbouring threads do not collide on banks).
     uint32_t local[kWordsPerThread];
     uint32_t sum = 0;
+    {
+      uint32_t w[kWordsPerThread];
+      const uint4 a = *reinterpret_cast<const uint4*>(&s.hist[tid * kWordsPerThread]);
+      const uint4 c = *reinterpret_cast<const uint4*>(&s.hist[tid * kWordsPerThread + 4]);
+      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+      w[4] = c.x; w[5] = c.y; w[6] = c.z; w[7] = c.w;
 #pragma unroll
-    for (int j = 0; j < kWordsPerThread; ++j) {
-      const int w = tid * kWordsPerThread + j;
-      local[j] = sum;
-      sum += w < hist_words ? byte_sum(s.hist[w]) : 0u;
+      for (int j = 0; j < kWordsPerThread; ++j) {
+        local[j] = sum;
+        sum += tid * kWordsPerThread + j < hist_words ? byte_sum(w[j]) : 0u;
+      }
     }
     uint32_t incl = sum;
 #pragma unroll
@@ -665,10 +672,13 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
     }
     __syncthreads();
     const uint32_t thread_base = s.warp_sum[warp] + incl - sum;
-#pragma unroll
-    for (int j = 0; j < kWordsPerThread; ++j) {
-      const int w = tid * kWordsPerThread + j;
-      if (w < hist_words) s.word_prefix[w] = static_cast<uint16_t>(thread_base + local[j]);
+    if (tid * kWordsPerThread < hist_words) {  // hist_words is a multiple of 8
+      uint4 packed_prefix;
+      packed_prefix.x = (thread_base + local[0]) | ((thread_base + local[1]) << 16);
+      packed_prefix.y = (thread_base + local[2]) | ((thread_base + local[3]) << 16);
+      packed_prefix.z = (thread_base + local[4]) | ((thread_base + local[5]) << 16);
+      packed_prefix.w = (thread_base + local[6]) | ((thread_base + local[7]) << 16);
+      *reinterpret_cast<uint4*>(&s.word_prefix[tid * kWordsPerThread]) = packed_prefix;
     }
     // A byte counter that wrapped (more than 255 equal keys) loses 255 from the
     // total: hand the whole call to the digit-pass path.
@@ -891,11 +901,23 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
     stage_begin(kStageBucketCount, a.stream);
     {
       const int64_t groups = (a.n + 3) / 4;
+      const bool shared = table_bytes <= 96 * 1024;
+      const int blocks_per_sm = shared ? (table_bytes <= 48 * 1024 ? 4 : 2) : 4;
       const int grid = static_cast<int>(std::max<int64_t>(
-          1, std::min<int64_t>((groups + kCountThreads - 1) / kCountThreads, kSmCount * 4)));
-      auto kernel = vec ? bucket_count_kernel<false, true> : bucket_count_kernel<false, false>;
-      kernel<<<grid, kCountThreads, 0, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift, buckets,
-                                                    count);
+          1, std::min<int64_t>((groups + kCountThreads - 1) / kCountThreads,
+                               kSmCount * blocks_per_sm)));
+      if (shared) {
+        auto kernel = vec ? bucket_count_kernel<true, true> : bucket_count_kernel<true, false>;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(table_bytes));
+        if (e != cudaSuccess) return e;
+        kernel<<<grid, kCountThreads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.n, a.grid,
+                                                               p.shift, buckets, count);
+      } else {
+        auto kernel = vec ? bucket_count_kernel<false, true> : bucket_count_kernel<false, false>;
+        kernel<<<grid, kCountThreads, 0, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift,
+                                                      buckets, count);
+      }
     }
     stage_end(kStageBucketCount, a.stream);
     stage_begin(kStageBucketScan, a.stream);
