@@ -103,6 +103,14 @@ int AetherSlabPartition(const float* x, const float* y, const float* z, const fl
                         float* vz_out, int64_t* counts_out, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* The move stage that precedes the sort in the DSMC step: x += v*dt, specular
+ * reflection at the six walls, in place (fused_particle_push,
+ * project_aether/src/custom_kernels/triton/fused_particle_push.py:75-92; arithmetic
+ * of its unfused statement reference_push, :95-108).  `lo`, `hi` are host
+ * pointers to three floats each. */
+int AetherParticlePush(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
+                       float dt, const float* lo, const float* hi, void* stream);
+
 /* The same sort for callers that cannot allocate device memory: a plugin that
  * runs inside a host application which has already handed all of the GPU's
  * memory to its own pool, or a step of a real-time loop in which cudaMalloc

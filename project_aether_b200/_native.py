@@ -43,6 +43,9 @@ _SIGNATURES = {
     'AetherSlabPartition': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.POINTER(AetherGrid),
                                            ctypes.c_int, _P, _P, _P, _P, _P, _P, _P, _P,
                                            ctypes.c_size_t, _P]),
+    'AetherParticlePush': (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _I64, ctypes.c_float,
+                                          ctypes.POINTER(ctypes.c_float),
+                                          ctypes.POINTER(ctypes.c_float), _P]),
     'AetherSortStaticMaxParticles': (ctypes.c_int64, []),
     'AetherSortParticlesByCellStatic': (ctypes.c_int, [_P, _P, _P, _I64,
                                                        ctypes.POINTER(AetherGrid),
@@ -65,13 +68,16 @@ def exported_symbols():
 def load_library(path: str | None = None) -> ctypes.CDLL:
     """Loads the CUDA library and declares the C ABI.
 
+    The path is, in this order: the argument, the environment variable
+    AETHER_SORT_LIBRARY, the library built in the package folder.
+
     Raises:
       OSError: if the library is not built or cannot be loaded.
     """
     global _library
     if _library is not None and path is None:
         return _library
-    lib_path = path or LIBRARY_PATH
+    lib_path = path or os.environ.get('AETHER_SORT_LIBRARY') or LIBRARY_PATH
     if not os.path.exists(lib_path):
         raise OSError(f'{lib_path} is not built; run `python -m project_aether_b200.build`')
     library = ctypes.CDLL(lib_path)

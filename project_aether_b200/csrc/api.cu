@@ -231,3 +231,11 @@ extern "C" int AetherSlabPartition(const float* x, const float* y, const float* 
                         vy_out, vz_out, counts_out, workspace, workspace_bytes,
                         static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int AetherParticlePush(float* x, float* y, float* z, float* vx, float* vy, float* vz,
+                                  int64_t n, float dt, const float* lo, const float* hi,
+                                  void* stream) {
+  if (!count_ok(n) || !lo || !hi) return cudaErrorInvalidValue;
+  if (n > 0 && (!x || !y || !z || !vx || !vy || !vz)) return cudaErrorInvalidValue;
+  return particle_push(x, y, z, vx, vy, vz, n, dt, lo, hi, static_cast<cudaStream_t>(stream));
+}

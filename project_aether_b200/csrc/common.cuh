@@ -170,4 +170,7 @@ cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t n
                                int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream,
                                const int32_t* run_if = nullptr);
 
+cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
+                          float dt, const float* lo, const float* hi, cudaStream_t stream);
+
 }  // namespace aether

@@ -65,62 +65,99 @@ slab_count_kernel(const float* __restrict__ x, int64_t n, AetherGrid g, int slab
     tile_count[static_cast<size_t>(threadIdx.x) * gridDim.x + blockIdx.x] = count[threadIdx.x];
 }
 
-// tile_count is [world][tiles]; one block turns it into exclusive offsets in
-// that order and writes the per-destination totals.
-__global__ void __launch_bounds__(1024)
-slab_scan_kernel(uint32_t* __restrict__ tile_count, int64_t entries, int tiles, int world,
-                 int64_t* __restrict__ totals) {
-  __shared__ uint32_t warp_sum[32];
-  __shared__ uint32_t carry;
+// tile_count is [world][tiles].  Its exclusive scan in that order is the output
+// offset of every (destination, tile) run.  Two levels: each block scans 1024
+// entries in place and records its total; one block scans the block totals and
+// writes the per-destination totals.
+constexpr int kScanBlock = 1024;
+
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_sum,
+                                                         uint32_t* total) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) carry = 0;
+  uint32_t incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sum[warp] = incl;
   __syncthreads();
-  for (int64_t base = 0; base < entries; base += 1024) {
-    const int64_t i = base + tid;
-    const uint32_t v = i < entries ? tile_count[i] : 0u;
-    uint32_t incl = v;
+  if (warp == 0) {
+    const uint32_t w = warp_sum[lane];
+    uint32_t wi = w;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
+      const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
     }
-    if (lane == 31) warp_sum[warp] = incl;
+    warp_sum[lane] = wi - w;
+    if (lane == 31) *total = wi;
+  }
+  __syncthreads();
+  return warp_sum[warp] + incl - v;
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+slab_scan_local_kernel(uint32_t* __restrict__ tile_count, int64_t entries,
+                       uint32_t* __restrict__ block_sum) {
+  __shared__ uint32_t warp_sum[32];
+  __shared__ uint32_t total;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kScanBlock + threadIdx.x;
+  const uint32_t v = i < entries ? tile_count[i] : 0u;
+  const uint32_t excl = block_exclusive_scan(v, warp_sum, &total);
+  if (i < entries) tile_count[i] = excl;
+  if (threadIdx.x == 0) block_sum[blockIdx.x] = total;
+}
+
+// One block: exclusive scan of the block totals (any number of them, 1024 at a
+// time with a running carry), then the number of particles per destination.
+__global__ void __launch_bounds__(kScanBlock)
+slab_scan_blocks_kernel(const uint32_t* __restrict__ tile_count, uint32_t* __restrict__ block_sum,
+                        int blocks, int tiles, int world, int64_t n,
+                        int64_t* __restrict__ totals) {
+  __shared__ uint32_t warp_sum[32];
+  __shared__ uint32_t total, carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < blocks; base += kScanBlock) {
+    const int i = base + threadIdx.x;
+    const uint32_t v = i < blocks ? block_sum[i] : 0u;
+    const uint32_t excl = block_exclusive_scan(v, warp_sum, &total);
+    if (i < blocks) block_sum[i] = carry + excl;
     __syncthreads();
-    if (warp == 0) {
-      const uint32_t w = warp_sum[lane];
-      uint32_t wi = w;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-        if (lane >= o) wi += t;
-      }
-      warp_sum[lane] = wi - w;
-    }
-    __syncthreads();
-    const uint32_t excl = carry + warp_sum[warp] + incl - v;
-    if (i < entries) tile_count[i] = excl;
-    __syncthreads();
-    if (tid == 1023) carry = excl + v;
+    if (threadIdx.x == 0) carry += total;
     __syncthreads();
   }
-  // Totals: start of destination d+1 minus start of destination d.
-  if (tid < world) {
-    const uint32_t begin = tile_count[static_cast<size_t>(tid) * tiles];
-    const uint32_t end = tid + 1 < world ? tile_count[static_cast<size_t>(tid + 1) * tiles] : carry;
-    totals[tid] = static_cast<int64_t>(end - begin);
+  if (threadIdx.x < world) {
+    const int64_t first = static_cast<int64_t>(threadIdx.x) * tiles;
+    const int64_t begin = tile_count[first] + block_sum[first / kScanBlock];
+    int64_t end = n;
+    if (threadIdx.x + 1 < world) {
+      const int64_t next = first + tiles;
+      end = tile_count[next] + block_sum[next / kScanBlock];
+    }
+    totals[threadIdx.x] = end - begin;
   }
 }
 
+// Stages the tile in shared memory grouped by destination (stable inside a
+// destination), then writes every destination's run with coalesced stores.
 __global__ void __launch_bounds__(kSlabThreads)
 slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                     int64_t n, AetherGrid g, int slab_width, int world, bool vec,
-                    const uint32_t* __restrict__ tile_offset, float* __restrict__ ox,
+                    const uint32_t* __restrict__ tile_offset,
+                    const uint32_t* __restrict__ block_sum, float* __restrict__ ox,
                     float* __restrict__ oy, float* __restrict__ oz, float* __restrict__ ovx,
                     float* __restrict__ ovy, float* __restrict__ ovz) {
+  extern __shared__ float stage_raw[];  // [6][kSlabTile]
+  float (*stage)[kSlabTile] = reinterpret_cast<float (*)[kSlabTile]>(stage_raw);
   __shared__ unsigned long long warp_lo[8], warp_hi[8];
+  __shared__ uint32_t local_base[kMaxWorld + 1];  // start of each destination's run in the tile
+  __shared__ uint32_t out_base[kMaxWorld];        // start of that run in the output arrays
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * kSlabThreads + tid) * kSlabItems;
+  const int64_t tile_first = static_cast<int64_t>(blockIdx.x) * kSlabTile;
+  const int64_t i0 = tile_first + static_cast<int64_t>(tid) * kSlabItems;
   float f[6][kSlabItems];
   load8(x, i0, n, vec, f[0]);
   load8(y, i0, n, vec, f[1]);
@@ -151,25 +188,48 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   __syncthreads();
   unsigned long long base_lo = ilo - lo, base_hi = ihi - hi;
   for (int w = 0; w < warp; ++w) { base_lo += warp_lo[w]; base_hi += warp_hi[w]; }
+  if (tid == kSlabThreads - 1) {
+    const unsigned long long all_lo = base_lo + lo, all_hi = base_hi + hi;
+    uint32_t run = 0;
+    for (int w = 0; w < kMaxWorld; ++w) {
+      local_base[w] = run;
+      run += static_cast<uint32_t>(((w < 4 ? all_lo : all_hi) >> (16 * (w & 3))) & 0xffffu);
+    }
+    local_base[kMaxWorld] = run;
+  }
+  if (tid < world) {
+    const size_t entry = static_cast<size_t>(tid) * gridDim.x + blockIdx.x;
+    out_base[tid] = tile_offset[entry] + block_sum[entry / kScanBlock];
+  }
+  __syncthreads();
   uint32_t next[kMaxWorld];
 #pragma unroll
-  for (int w = 0; w < kMaxWorld; ++w) {
-    const uint32_t before = static_cast<uint32_t>(((w < 4 ? base_lo : base_hi) >> (16 * (w & 3))) & 0xffffu);
-    next[w] = w < world ? tile_offset[static_cast<size_t>(w) * gridDim.x + blockIdx.x] + before : 0u;
-  }
+  for (int w = 0; w < kMaxWorld; ++w)
+    next[w] = local_base[w] +
+              static_cast<uint32_t>(((w < 4 ? base_lo : base_hi) >> (16 * (w & 3))) & 0xffffu);
 #pragma unroll
   for (int k = 0; k < kSlabItems; ++k) {
     if (dest[k] < 0) continue;
-    uint32_t o = 0;
+    uint32_t p = 0;
 #pragma unroll
     for (int w = 0; w < kMaxWorld; ++w)
-      if (dest[k] == w) o = next[w]++;
-    ox[o] = f[0][k];
-    oy[o] = f[1][k];
-    oz[o] = f[2][k];
-    ovx[o] = f[3][k];
-    ovy[o] = f[4][k];
-    ovz[o] = f[5][k];
+      if (dest[k] == w) p = next[w]++;
+#pragma unroll
+    for (int c = 0; c < 6; ++c) stage[c][p] = f[c][k];
+  }
+  __syncthreads();
+  const int valid = static_cast<int>(local_base[kMaxWorld]);
+  for (int j = tid; j < valid; j += kSlabThreads) {
+    int d = 0;
+#pragma unroll
+    for (int w = 1; w < kMaxWorld; ++w) d += (static_cast<uint32_t>(j) >= local_base[w]);
+    const size_t o = static_cast<size_t>(out_base[d]) + (j - local_base[d]);
+    ox[o] = stage[0][j];
+    oy[o] = stage[1][j];
+    oz[o] = stage[2][j];
+    ovx[o] = stage[3][j];
+    ovy[o] = stage[4][j];
+    ovz[o] = stage[5][j];
   }
 }
 
@@ -179,7 +239,10 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 size_t slab_partition_workspace_bytes(int64_t n, int world) {
   const int64_t tiles = std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile);
-  return static_cast<size_t>(align_up(tiles * world * sizeof(uint32_t), 256));
+  const int64_t entries = tiles * world;
+  const int64_t blocks = (entries + kScanBlock - 1) / kScanBlock;
+  return static_cast<size_t>(align_up(entries * sizeof(uint32_t), 256) +
+                             align_up(blocks * sizeof(uint32_t), 256));
 }
 
 cudaError_t slab_partition(const float* x, const float* y, const float* z, const float* v,
@@ -194,14 +257,23 @@ cudaError_t slab_partition(const float* x, const float* y, const float* z, const
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
   const int slab_width = g.nx / world;
   stage_begin(kStageSlabPartition, stream);
+  const int64_t entries = static_cast<int64_t>(tiles) * world;
+  const int blocks = static_cast<int>((entries + kScanBlock - 1) / kScanBlock);
+  uint32_t* block_sum = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) +
+                                                    align_up(entries * sizeof(uint32_t), 256));
   slab_count_kernel<<<tiles, kSlabThreads, 0, stream>>>(x, n, g, slab_width, world, vec, tile_count);
-  slab_scan_kernel<<<1, 1024, 0, stream>>>(tile_count, static_cast<int64_t>(tiles) * world, tiles,
-                                           world, totals);
-  slab_scatter_kernel<<<tiles, kSlabThreads, 0, stream>>>(x, y, z, v, padded, n, g, slab_width,
-                                                          world, vec, tile_count, ox, oy, oz, ovx,
-                                                          ovy, ovz);
+  slab_scan_local_kernel<<<blocks, kScanBlock, 0, stream>>>(tile_count, entries, block_sum);
+  slab_scan_blocks_kernel<<<1, kScanBlock, 0, stream>>>(tile_count, block_sum, blocks, tiles, world,
+                                                        n, totals);
+  constexpr int kStageBytes = 6 * kSlabTile * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(slab_scatter_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+  if (e != cudaSuccess) return e;
+  slab_scatter_kernel<<<tiles, kSlabThreads, kStageBytes, stream>>>(x, y, z, v, padded, n, g, slab_width,
+                                                          world, vec, tile_count, block_sum, ox, oy,
+                                                          oz, ovx, ovy, ovz);
   stage_end(kStageSlabPartition, stream);
-  count_launches(3);
+  count_launches(4);
   return cudaGetLastError();
 }
 

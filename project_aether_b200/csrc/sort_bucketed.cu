@@ -255,259 +255,6 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   }
 }
 
-// Tile geometry of the staged scatter (chunk_scatter_kernel below).  A block
-// takes a tile of 8192 consecutive particles:
-//   sweep 1  reads x,y,z, counts the tile's particles per bucket in shared
-//            memory (the value each add returns is the particle's rank in its
-//            bucket within the tile);
-//   flush    reserves the tile's slots with one global add per non-empty bucket;
-//            consecutive lanes hit consecutive cursors, so a warp's 32 adds
-//            cost four 32-byte L2 atomic requests instead of 32;
-//   sweep 2  reads x,y,z again (the tile is still in L2) and v, builds keys and
-//            writes the records.
-constexpr int kTileThreads = 512;
-constexpr int kTileRounds = 4;                                  // float4 loads per array
-constexpr int kTileSize = kTileThreads * kTileRounds * 4;       // 8192 particles
-
-// ------------------------------------------------------------------------
-// Staged scatter.  B200 serves scattered 32-byte stores that miss in L2 at a
-// few tens of G requests/s whatever their order in time, but more than four
-// times that rate when they hit a small, resident region.  So the particles are
-// taken in chunks of 2^20: a chunk's records are scattered into a staging buffer
-// of 32 MB that lives in L2 and is reused by every chunk, laid out by bucket,
-// and then each bucket's run of the chunk is copied to its place in the bucket
-// array with full-line loads and stores.
-//   chunk_count_kernel    particles per (chunk, bucket)
-//   chunk_offsets_kernel  per bucket: running sum over the chunks
-//   chunk_scan_kernel     per chunk: exclusive scan over the buckets (staging slots)
-//   chunk_scatter_kernel  chunk -> staging (tiles of 8192, as in the tiled scatter)
-//   chunk_copy_kernel     staging -> bucket array, one warp per bucket
-// ------------------------------------------------------------------------
-constexpr int kChunkLog = 20;
-constexpr int64_t kChunkRecords = int64_t{1} << kChunkLog;
-constexpr int kCountParts = 8;  // count work units per chunk
-
-template <bool VEC>
-__global__ void __launch_bounds__(kCountThreads)
-chunk_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
-                   const float* __restrict__ z, int64_t n, AetherGrid g, int shift, int buckets,
-                   int chunks, uint32_t* __restrict__ chunk_hist) {
-  extern __shared__ uint32_t hist[];
-  const int64_t part_records = kChunkRecords / kCountParts;
-  for (int unit = blockIdx.x; unit < chunks * kCountParts; unit += gridDim.x) {
-    for (int i = threadIdx.x; i < buckets; i += kCountThreads) hist[i] = 0;
-    __syncthreads();
-    const int64_t first = static_cast<int64_t>(unit) * part_records;
-    const int64_t last = min(static_cast<long long>(n), static_cast<long long>(first + part_records));
-    for (int64_t i0 = first + threadIdx.x * 4; i0 < last; i0 += kCountThreads * 4) {
-      float px[4], py[4], pz[4];
-      if (VEC && i0 + 4 <= last) {
-        load_items<4>(x + i0, px);
-        load_items<4>(y + i0, py);
-        load_items<4>(z + i0, pz);
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const bool ok = i0 + k < last;
-          px[k] = ok ? x[i0 + k] : 0.f;
-          py[k] = ok ? y[i0 + k] : 0.f;
-          pz[k] = ok ? z[i0 + k] : 0.f;
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (i0 + k < last) atomicAdd(&hist[cell_of(px[k], py[k], pz[k], g) >> shift], 1u);
-    }
-    __syncthreads();
-    uint32_t* row = chunk_hist + static_cast<size_t>(unit / kCountParts) * buckets;
-    for (int i = threadIdx.x; i < buckets; i += kCountThreads)
-      if (hist[i]) atomicAdd(&row[i], hist[i]);
-    __syncthreads();
-  }
-}
-
-// Per bucket: rel[c][b] = particles of bucket b in chunks before c; total[b].
-__global__ void __launch_bounds__(256)
-chunk_offsets_kernel(const uint32_t* __restrict__ chunk_hist, int buckets, int chunks,
-                     uint32_t* __restrict__ rel, uint32_t* __restrict__ total) {
-  const int b = blockIdx.x * 256 + threadIdx.x;
-  if (b >= buckets) return;
-  uint32_t run = 0;
-  for (int c = 0; c < chunks; ++c) {
-    rel[static_cast<size_t>(c) * buckets + b] = run;
-    run += chunk_hist[static_cast<size_t>(c) * buckets + b];
-  }
-  total[b] = run;
-}
-
-// Per chunk (one block each): staging slot of every bucket's run.
-__global__ void __launch_bounds__(kScanThreads)
-chunk_scan_kernel(const uint32_t* __restrict__ chunk_hist, int buckets,
-                  uint32_t* __restrict__ stage_cursor) {
-  __shared__ uint32_t warp_sum[32];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t* hist = chunk_hist + static_cast<size_t>(blockIdx.x) * buckets;
-  uint32_t* out = stage_cursor + static_cast<size_t>(blockIdx.x) * buckets;
-  const int per = (buckets + kScanThreads - 1) / kScanThreads;
-  const int first = min(buckets, tid * per), last = min(buckets, first + per);
-  uint32_t sum = 0;
-  for (int b = first; b < last; ++b) sum += hist[b];
-  uint32_t incl = sum;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  if (lane == 31) warp_sum[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    const uint32_t w = warp_sum[lane];
-    uint32_t wi = w;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-      if (lane >= o) wi += t;
-    }
-    warp_sum[lane] = wi - w;
-  }
-  __syncthreads();
-  uint32_t run = warp_sum[warp] + incl - sum;
-  for (int b = first; b < last; ++b) {
-    out[b] = run;
-    run += hist[b];
-  }
-}
-
-template <bool VEC>
-__global__ void __launch_bounds__(kTileThreads, 2)
-chunk_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
-                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
-                     int64_t first, int64_t last, AetherGrid g, uint32_t k0, uint32_t k1, int shift,
-                     int buckets, uint32_t* __restrict__ cursor, uint32_t* __restrict__ staging,
-                     const Header* __restrict__ hdr) {
-  if (hdr->use_standard) return;
-  extern __shared__ uint32_t table[];  // per bucket: tile count, then reserved base
-  const int tid = threadIdx.x;
-  for (int b = tid; b < buckets; b += kTileThreads) table[b] = 0;
-  __syncthreads();
-  const int64_t tiles = (last - first + kTileSize - 1) / kTileSize;
-  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    const int64_t tile_base = first + tile * kTileSize;
-    uint32_t rank[kTileRounds][2];  // four 16-bit ranks per round
-#pragma unroll
-    for (int k = 0; k < kTileRounds; ++k) {
-      const int64_t i0 = tile_base + (static_cast<int64_t>(k) * kTileThreads + tid) * 4;
-      float p[3][4];
-      if (VEC && i0 + 4 <= last) {
-        load_items<4>(x + i0, p[0]);
-        load_items<4>(y + i0, p[1]);
-        load_items<4>(z + i0, p[2]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const bool ok = i0 + j < last;
-          p[0][j] = ok ? x[i0 + j] : 0.f;
-          p[1][j] = ok ? y[i0 + j] : 0.f;
-          p[2][j] = ok ? z[i0 + j] : 0.f;
-        }
-      }
-      uint32_t r[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        r[j] = 0;
-        if (i0 + j < last)
-          r[j] = atomicAdd(&table[cell_of(p[0][j], p[1][j], p[2][j], g) >> shift], 1u);
-      }
-      rank[k][0] = r[0] | (r[1] << 16);
-      rank[k][1] = r[2] | (r[3] << 16);
-    }
-    __syncthreads();
-    // One add per non-empty bucket; consecutive lanes hit consecutive cursors.
-#pragma unroll 4
-    for (int b = tid; b < buckets; b += kTileThreads) {
-      const uint32_t c = table[b];
-      if (c) table[b] = atomicAdd(&cursor[b], c);
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < kTileRounds; ++k) {
-      const int64_t i0 = tile_base + (static_cast<int64_t>(k) * kTileThreads + tid) * 4;
-      float f[6][4];
-      if (VEC && i0 + 4 <= last) {
-        load_items<4>(x + i0, f[0]);
-        load_items<4>(y + i0, f[1]);
-        load_items<4>(z + i0, f[2]);
-        if (v) {
-          load_items<4>(v + i0, f[3]);
-          load_items<4>(v + padded + i0, f[4]);
-          load_items<4>(v + 2 * padded + i0, f[5]);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const bool ok = i0 + j < last;
-          f[0][j] = ok ? x[i0 + j] : 0.f;
-          f[1][j] = ok ? y[i0 + j] : 0.f;
-          f[2][j] = ok ? z[i0 + j] : 0.f;
-          f[3][j] = ok && v ? v[i0 + j] : 0.f;
-          f[4][j] = ok && v ? v[padded + i0 + j] : 0.f;
-          f[5][j] = ok && v ? v[2 * padded + i0 + j] : 0.f;
-        }
-      }
-      if (!v) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) f[3][j] = f[4][j] = f[5][j] = 0.f;
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (i0 + j < last) {
-          const uint32_t cell = cell_of(f[0][j], f[1][j], f[2][j], g);
-          const uint32_t index = static_cast<uint32_t>(i0 + j);
-          const uint32_t slot =
-              table[cell >> shift] + ((rank[k][j >> 1] >> (16 * (j & 1))) & 0xffffu);
-          store_record(staging + static_cast<size_t>(slot) * kRecordWords,
-                       make_key(cell, index, k0, k1), index, f[0][j], f[1][j], f[2][j], f[3][j],
-                       f[4][j], f[5][j]);
-        }
-      }
-    }
-    __syncthreads();
-    for (int b = tid; b < buckets; b += kTileThreads) table[b] = 0;
-    __syncthreads();
-  }
-}
-
-constexpr int kCopyThreads = 256;
-
-// One warp per bucket: the chunk's run of the bucket is contiguous in staging
-// (it ends at the advanced cursor) and contiguous in the bucket array.
-__global__ void __launch_bounds__(kCopyThreads)
-chunk_copy_kernel(const uint32_t* __restrict__ staging, const uint32_t* __restrict__ stage_end,
-                  const uint32_t* __restrict__ hist, const uint32_t* __restrict__ rel,
-                  const uint32_t* __restrict__ bucket_start, int buckets,
-                  uint32_t* __restrict__ records, const Header* __restrict__ hdr) {
-  if (hdr->use_standard) return;
-  const int lane = threadIdx.x & 31;
-  const int warps = (gridDim.x * kCopyThreads) >> 5;
-  for (int b = (blockIdx.x * kCopyThreads + threadIdx.x) >> 5; b < buckets; b += warps) {
-    const uint32_t count = hist[b];
-    const uint32_t* src = staging + static_cast<size_t>(stage_end[b] - count) * kRecordWords;
-    uint32_t* dst = records + static_cast<size_t>(bucket_start[b] + rel[b]) * kRecordWords;
-    for (uint32_t r = lane; r < count; r += 32) {
-      uint32_t w[8];
-      asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                   : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]),
-                     "=r"(w[6]), "=r"(w[7])
-                   : "l"(src + static_cast<size_t>(r) * kRecordWords));
-      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(
-                       dst + static_cast<size_t>(r) * kRecordWords),
-                   "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]),
-                   "r"(w[7])
-                   : "memory");
-    }
-  }
-}
-
 // ------------------------------------------------------------------------
 // Finish: one block sorts one bucket in shared memory and writes the output.
 // ------------------------------------------------------------------------
@@ -764,33 +511,16 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-constexpr size_t kTableLimitBytes = 112 * 1024;  // largest per-bucket table kept in shared memory
-// One kernel pair per chunk costs more in launch ramps than the staging saves;
-// the direct scatter stays the default until the staged form runs as one kernel.
-constexpr bool kUseStagedScatter = false;
-
 struct BucketLayout {
-  bool staged;   // chunked scatter through an L2-resident staging buffer
-  int chunks;
-  size_t count_off, start_off, cursor_off, records_off;
-  size_t chunk_hist_off, rel_off, stage_cursor_off, staging_off, total;
+  size_t count_off, start_off, cursor_off, records_off, total;
 };
 
 BucketLayout bucket_layout(int64_t n, int64_t buckets) {
   BucketLayout l;
-  l.staged = kUseStagedScatter && buckets * sizeof(uint32_t) <= kTableLimitBytes;
-  l.chunks = static_cast<int>(std::max<int64_t>(1, (n + kChunkRecords - 1) / kChunkRecords));
   l.count_off = sizeof(Header);
   l.start_off = align_up(l.count_off + buckets * sizeof(uint32_t), 256);
   l.cursor_off = align_up(l.start_off + (buckets + 1) * sizeof(uint32_t), 256);
-  l.chunk_hist_off = align_up(l.cursor_off + buckets * sizeof(uint32_t), 256);
-  const size_t per_chunk = l.staged ? static_cast<size_t>(l.chunks) * buckets * sizeof(uint32_t) : 0;
-  l.rel_off = align_up(l.chunk_hist_off + per_chunk, 256);
-  l.stage_cursor_off = align_up(l.rel_off + per_chunk, 256);
-  l.staging_off = align_up(l.stage_cursor_off + per_chunk, 256);
-  const size_t staging = l.staged ? static_cast<size_t>(std::min<int64_t>(n, kChunkRecords)) *
-                                        kRecordWords * sizeof(uint32_t) : 0;
-  l.records_off = align_up(l.staging_off + staging, 256);
+  l.records_off = align_up(l.cursor_off + buckets * sizeof(uint32_t), 256);
   l.total = align_up(l.records_off + static_cast<size_t>(n) * kRecordWords * sizeof(uint32_t), 256);
   return l;
 }
@@ -832,118 +562,57 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   uint32_t* start = reinterpret_cast<uint32_t*>(base + l.start_off);
   uint32_t* cursor = reinterpret_cast<uint32_t*>(base + l.cursor_off);
   uint32_t* records = reinterpret_cast<uint32_t*>(base + l.records_off);
-  // Zero the header, the bucket counts and (staged form) the per-chunk counts.
-  const size_t zero_to = l.staged ? l.rel_off : l.start_off;
-  cudaError_t e = cudaMemsetAsync(base, 0, l.start_off, a.stream);
+  cudaError_t e = cudaMemsetAsync(base, 0, l.start_off, a.stream);  // header and bucket counts
   if (e != cudaSuccess) return e;
-  if (l.staged) {
-    e = cudaMemsetAsync(base + l.chunk_hist_off, 0, zero_to - l.chunk_hist_off, a.stream);
-    if (e != cudaSuccess) return e;
-  }
   const int buckets = static_cast<int>(p.buckets);
   const uint32_t k0 = static_cast<uint32_t>(a.seed), k1 = static_cast<uint32_t>(a.seed >> 32);
   const bool vec = aligned16(a.x) && aligned16(a.y) && aligned16(a.z) &&
                    (!a.velocity || (aligned16(a.velocity) && a.padded % 4 == 0));
   const size_t table_bytes = static_cast<size_t>(buckets) * sizeof(uint32_t);
-  const int per_sm = table_bytes <= 56 * 1024 ? 2 : 1;
 
-  if (l.staged) {
-    uint32_t* chunk_hist = reinterpret_cast<uint32_t*>(base + l.chunk_hist_off);
-    uint32_t* rel = reinterpret_cast<uint32_t*>(base + l.rel_off);
-    uint32_t* stage_cursor = reinterpret_cast<uint32_t*>(base + l.stage_cursor_off);
-    uint32_t* staging = reinterpret_cast<uint32_t*>(base + l.staging_off);
-    stage_begin(kStageBucketCount, a.stream);
-    {
-      auto kernel = vec ? chunk_count_kernel<true> : chunk_count_kernel<false>;
+  stage_begin(kStageBucketCount, a.stream);
+  {
+    const int64_t groups = (a.n + 3) / 4;
+    const bool shared = table_bytes <= 96 * 1024;
+    const int blocks_per_sm = shared ? (table_bytes <= 48 * 1024 ? 4 : 2) : 4;
+    const int grid = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>((groups + kCountThreads - 1) / kCountThreads,
+                             kSmCount * blocks_per_sm)));
+    if (shared) {
+      auto kernel = vec ? bucket_count_kernel<true, true> : bucket_count_kernel<true, false>;
       e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(table_bytes));
       if (e != cudaSuccess) return e;
-      const int grid = std::min(l.chunks * kCountParts, kSmCount * per_sm * 2);
       kernel<<<grid, kCountThreads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift,
-                                                            buckets, l.chunks, chunk_hist);
+                                                             buckets, count);
+    } else {
+      auto kernel = vec ? bucket_count_kernel<false, true> : bucket_count_kernel<false, false>;
+      kernel<<<grid, kCountThreads, 0, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift, buckets,
+                                                    count);
     }
-    stage_end(kStageBucketCount, a.stream);
-    stage_begin(kStageBucketScan, a.stream);
-    chunk_offsets_kernel<<<(buckets + 255) / 256, 256, 0, a.stream>>>(chunk_hist, buckets, l.chunks,
-                                                                      rel, count);
-    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(count, buckets, a.n, kFinishCapacity,
-                                                         start, cursor, hdr);
-    chunk_scan_kernel<<<l.chunks, kScanThreads, 0, a.stream>>>(chunk_hist, buckets, stage_cursor);
-    stage_end(kStageBucketScan, a.stream);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    count_launches(4);
-
-    stage_begin(kStageBucketScatter, a.stream);
-    auto scatter = vec ? chunk_scatter_kernel<true> : chunk_scatter_kernel<false>;
-    e = cudaFuncSetAttribute(scatter, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(table_bytes));
-    if (e != cudaSuccess) return e;
-    for (int c = 0; c < l.chunks; ++c) {
-      const int64_t first = static_cast<int64_t>(c) * kChunkRecords;
-      const int64_t last = std::min<int64_t>(a.n, first + kChunkRecords);
-      const int64_t tiles = (last - first + kTileSize - 1) / kTileSize;
-      const int grid = static_cast<int>(std::min<int64_t>(tiles, kSmCount * per_sm));
-      const size_t row = static_cast<size_t>(c) * buckets;
-      scatter<<<grid, kTileThreads, table_bytes, a.stream>>>(
-          a.x, a.y, a.z, a.velocity, a.padded, first, last, a.grid, k0, k1, p.shift, buckets,
-          stage_cursor + row, staging, hdr);
-      const int copy_grid = std::min((buckets * 32 + kCopyThreads - 1) / kCopyThreads,
-                                     kSmCount * 8);
-      chunk_copy_kernel<<<copy_grid, kCopyThreads, 0, a.stream>>>(
-          staging, stage_cursor + row, chunk_hist + row, rel + row, start, buckets, records, hdr);
-    }
-    stage_end(kStageBucketScatter, a.stream);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    count_launches(2 * l.chunks);
-  } else {
-    stage_begin(kStageBucketCount, a.stream);
-    {
-      const int64_t groups = (a.n + 3) / 4;
-      const bool shared = table_bytes <= 96 * 1024;
-      const int blocks_per_sm = shared ? (table_bytes <= 48 * 1024 ? 4 : 2) : 4;
-      const int grid = static_cast<int>(std::max<int64_t>(
-          1, std::min<int64_t>((groups + kCountThreads - 1) / kCountThreads,
-                               kSmCount * blocks_per_sm)));
-      if (shared) {
-        auto kernel = vec ? bucket_count_kernel<true, true> : bucket_count_kernel<true, false>;
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(table_bytes));
-        if (e != cudaSuccess) return e;
-        kernel<<<grid, kCountThreads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.n, a.grid,
-                                                               p.shift, buckets, count);
-      } else {
-        auto kernel = vec ? bucket_count_kernel<false, true> : bucket_count_kernel<false, false>;
-        kernel<<<grid, kCountThreads, 0, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift,
-                                                      buckets, count);
-      }
-    }
-    stage_end(kStageBucketCount, a.stream);
-    stage_begin(kStageBucketScan, a.stream);
-    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(count, buckets, a.n, kFinishCapacity,
-                                                         start, cursor, hdr);
-    stage_end(kStageBucketScan, a.stream);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    stage_begin(kStageBucketScatter, a.stream);
-    {
-      constexpr int kItems = 2;
-      const int64_t groups = (a.n + kItems - 1) / kItems;
-      const int grid = static_cast<int>(std::max<int64_t>(
-          1, std::min<int64_t>((groups + kScatterThreads - 1) / kScatterThreads,
-                               kSmCount * (8 / kItems))));
-      auto kernel =
-          vec ? bucket_scatter_kernel<true, kItems> : bucket_scatter_kernel<false, kItems>;
-      kernel<<<grid, kScatterThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.n,
-                                                      a.grid, k0, k1, p.shift, cursor, records,
-                                                      hdr);
-    }
-    stage_end(kStageBucketScatter, a.stream);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    count_launches(3);
   }
+  stage_end(kStageBucketCount, a.stream);
+  stage_begin(kStageBucketScan, a.stream);
+  bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(count, buckets, a.n, kFinishCapacity, start,
+                                                       cursor, hdr);
+  stage_end(kStageBucketScan, a.stream);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  stage_begin(kStageBucketScatter, a.stream);
+  {
+    constexpr int kItems = 2;
+    const int64_t groups = (a.n + kItems - 1) / kItems;
+    const int grid = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>((groups + kScatterThreads - 1) / kScatterThreads,
+                             kSmCount * (8 / kItems) * 4)));
+    auto kernel = vec ? bucket_scatter_kernel<true, kItems> : bucket_scatter_kernel<false, kItems>;
+    kernel<<<grid, kScatterThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.n,
+                                                    a.grid, k0, k1, p.shift, cursor, records, hdr);
+  }
+  stage_end(kStageBucketScatter, a.stream);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  count_launches(3);
 
   stage_begin(kStageBucketFinish, a.stream);
   e = cudaFuncSetAttribute(bucket_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

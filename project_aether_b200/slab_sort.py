@@ -75,23 +75,26 @@ def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
     return torch.stack(gathered).cpu()
 
 
-def exchange_particles(arrays: Sequence[torch.Tensor], matrix: torch.Tensor,
-                       group=None) -> List[torch.Tensor]:
+def exchange_particles(arrays: Sequence[torch.Tensor], matrix: torch.Tensor, group=None,
+                       out: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
     """One variable-size all-to-all per array.  `arrays` are ordered by destination;
     `matrix[s, d]` is the host-side count matrix.  Returns the received arrays, each the
-    concatenation of the blocks from source 0..G-1."""
+    concatenation of the blocks from source 0..G-1.  `out`, if given, are contiguous 1-D
+    tensors of the right length to receive into (e.g. rows of a (3, padded) velocity)."""
     rank = dist.get_rank(group)
     send = [int(c) for c in matrix[rank]]
     recv = [int(c) for c in matrix[:, rank]]
     if sum(send) != arrays[0].numel():
         raise RuntimeError(f'rank {rank}: send counts {sum(send)} do not match the '
                            f'{arrays[0].numel()} partitioned particles')
-    out = []
-    for a in arrays:
-        r = torch.empty(sum(recv), dtype=a.dtype, device=a.device)
+    received = []
+    for k, a in enumerate(arrays):
+        r = out[k] if out is not None else torch.empty(sum(recv), dtype=a.dtype, device=a.device)
+        if r.numel() != sum(recv):
+            raise RuntimeError(f'rank {rank}: receive buffer holds {r.numel()}, needs {sum(recv)}')
         dist.all_to_all_single(r, a, output_split_sizes=recv, input_split_sizes=send, group=group)
-        out.append(r)
-    return out
+        received.append(r)
+    return received
 
 
 def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity: torch.Tensor,
@@ -105,10 +108,14 @@ def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity
         return sort_and_gather_particles(x, y, z, velocity, grid, seed, path=path)
     parts = partition_by_slab(x, y, z, velocity, grid, world)
     matrix = exchange_counts(parts.counts, group)
-    rx, ry, rz, rvx, rvy, rvz = exchange_particles(parts.arrays, matrix, group)
-    n = rx.numel()
+    n = int(matrix[:, rank].sum())
     padded = -(-n // 4) * 4
-    rv = torch.zeros((3, padded), dtype=torch.float32, device=rx.device)
-    rv[0, :n], rv[1, :n], rv[2, :n] = rvx, rvy, rvz
+    device = x.device
+    rx, ry, rz = (torch.empty(n, dtype=torch.float32, device=device) for _ in range(3))
+    rv = torch.empty((3, padded), dtype=torch.float32, device=device)
+    if padded > n:
+        rv[:, n:].zero_()
+    exchange_particles(parts.arrays, matrix, group,
+                       out=(rx, ry, rz, rv[0, :n], rv[1, :n], rv[2, :n]))
     return sort_and_gather_particles(rx, ry, rz, rv, grid, seed, ix_offset=ix_offset,
                                      nx_local=nx_local, path=path)
