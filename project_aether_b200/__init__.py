@@ -2,12 +2,13 @@
 Project AETHER (project_aether/src/custom_kernels/triton/fused_radix_sort.py)."""
 
 from .cell_grid import SHUFFLE_BITS, CellGrid, key_bits, num_passes
+from .particle_push import fused_particle_push
 from .particle_sort import (PATH_AUTO, PATH_BUCKETED, PATH_DIGIT_PASSES, SortedParticles,
                             SortResult, last_sort_status, sort_and_gather_particles,
                             sort_particles_by_cell)
 
 __all__ = [
     'SHUFFLE_BITS', 'CellGrid', 'key_bits', 'num_passes', 'PATH_AUTO', 'PATH_BUCKETED',
-    'PATH_DIGIT_PASSES', 'SortedParticles', 'SortResult', 'last_sort_status',
+    'PATH_DIGIT_PASSES', 'SortedParticles', 'fused_particle_push', 'SortResult', 'last_sort_status',
     'sort_and_gather_particles', 'sort_particles_by_cell',
 ]

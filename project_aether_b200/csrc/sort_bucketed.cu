@@ -40,8 +40,8 @@ constexpr int kRecordWords = 8;  // 32-byte record
 // ------------------------------------------------------------------------
 constexpr int kCountThreads = 512;
 
-// Adds one to a histogram bin per lane; a warp whose lanes all hit the same bin
-// (every particle in one cell) issues a single add.
+// Adds one to a histogram bin per lane.  Lanes hitting the same bin share one add
+// when the whole warp agrees, or (through match.any) when neighbouring lanes do.
 template <bool SHARED>
 __device__ __forceinline__ void bin_add(uint32_t* hist, uint32_t bin, bool valid) {
   const uint32_t active = __ballot_sync(0xffffffffu, valid);
@@ -51,6 +51,13 @@ __device__ __forceinline__ void bin_add(uint32_t* hist, uint32_t bin, bool valid
   const bool uniform = __all_sync(0xffffffffu, !valid || bin == first_bin);
   if (uniform) {
     if (static_cast<int>(lane_id()) == first) atomicAdd(&hist[first_bin], __popc(active));
+    return;
+  }
+  const uint32_t next_bin = __shfl_down_sync(0xffffffffu, bin, 1);
+  const bool clustered = __any_sync(0xffffffffu, valid && lane_id() < 31 && next_bin == bin);
+  if (clustered) {
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? bin : 0xffffffffu) & active;
+    if (valid && (peers & lanemask_lt()) == 0) atomicAdd(&hist[bin], __popc(peers));
   } else if (valid) {
     atomicAdd(&hist[bin], 1u);
   }
@@ -168,8 +175,10 @@ __device__ __forceinline__ void store_record(uint32_t* dst, uint32_t key, uint32
                : "memory");
 }
 
-// Reserves one slot in bucket `b`; a warp whose lanes all target one bucket
-// reserves its slots with a single atomic.
+// Reserves one slot in bucket `b`.  Lanes that target the same bucket share one
+// atomic: always when the whole warp agrees (cell-sorted input), and through
+// match.any when at least two neighbouring lanes agree (nearly sorted input).
+// Random input, where no neighbours agree, goes straight to one atomic per lane.
 __device__ __forceinline__ uint32_t reserve_slot(uint32_t* cursor, uint32_t b, bool valid) {
   const uint32_t active = __ballot_sync(0xffffffffu, valid);
   if (active == 0) return 0;
@@ -179,10 +188,18 @@ __device__ __forceinline__ uint32_t reserve_slot(uint32_t* cursor, uint32_t b, b
   uint32_t slot = 0;
   if (uniform) {
     if (static_cast<int>(lane_id()) == first) slot = atomicAdd(&cursor[first_b], __popc(active));
-    slot = __shfl_sync(0xffffffffu, slot, first) + __popc(active & lanemask_lt());
-  } else if (valid) {
-    slot = atomicAdd(&cursor[b], 1u);
+    return __shfl_sync(0xffffffffu, slot, first) + __popc(active & lanemask_lt());
   }
+  const uint32_t next_b = __shfl_down_sync(0xffffffffu, b, 1);
+  const bool clustered = __any_sync(0xffffffffu, valid && lane_id() < 31 && next_b == b);
+  if (clustered) {
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? b : 0xffffffffu) & active;
+    const int leader = __ffs(peers) - 1;
+    if (valid && static_cast<int>(lane_id()) == leader) slot = atomicAdd(&cursor[b], __popc(peers));
+    slot = __shfl_sync(0xffffffffu, slot, leader < 0 ? 0 : leader) + __popc(peers & lanemask_lt());
+    return slot;
+  }
+  if (valid) slot = atomicAdd(&cursor[b], 1u);
   return slot;
 }
 
@@ -259,7 +276,7 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 // Finish: one block sorts one bucket in shared memory and writes the output.
 // ------------------------------------------------------------------------
 constexpr int kFinishThreads = 1024;
-constexpr int kFinishCapacity = 5056;                      // records per bucket
+constexpr int kFinishCapacity = 5376;                      // records per bucket
 constexpr int kFinishItems = (kFinishCapacity + kFinishThreads - 1) / kFinishThreads;  // 6
 constexpr int kMaxLowBits = 15;                            // (cell bits in bucket) + 7
 constexpr int kHistWords = (1 << kMaxLowBits) / 4;         // byte counters, 4 per word
@@ -269,9 +286,9 @@ constexpr uint32_t kBulkWaitLimit = 1u << 24;              // polls of the copy 
 
 struct __align__(128) FinishSmem {
   uint32_t raw[kFinishCapacity * kRecordWords];  // the bucket's records as they lie in HBM
-  uint32_t hist[kHistWords];     // byte counter per low-key value; later: final order (u16)
+  uint32_t hist[kHistWords];     // byte counter per low-key value
   uint16_t word_prefix[kHistWords];  // exclusive prefix of each counter word
-  uint32_t entry[kFinishCapacity];  // per sorted slot: low key << 16 | record (before the tie pass)
+  uint16_t order[kFinishCapacity];  // record held by each sorted slot
   uint32_t warp_sum[32];
   uint32_t total;
   uint32_t gave_up;
@@ -332,7 +349,6 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
   const int low_bits = shift + kShuffleBits;
   const uint32_t low_mask = (1u << low_bits) - 1;
   const int hist_words = max(1, (1 << low_bits) / 4);
-  uint16_t* final_slot = reinterpret_cast<uint16_t*>(s.hist);  // reused after the scan is consumed
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s.barrier)) : "memory");
@@ -451,46 +467,51 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       if (b == buckets - 1 && tid == 0) cell_start[num_cells] = static_cast<int32_t>(n);
     }
 
-    // Sorted slot of every record.
+    // Sorted slot of every record: start of its key's run + arrival rank.  A
+    // key held by one record only (the usual case) is final at once.
+    uint32_t run[kFinishItems];  // run start | run length << 16, for records that share their key
 #pragma unroll
     for (int k = 0; k < kFinishItems; ++k) {
       const int r = tid + k * kFinishThreads;
+      run[k] = 0;
       if (r < count) {
         const uint32_t low = packed[k] & 0xffffu, rank = packed[k] >> 16;
         const uint32_t word = s.hist[low >> 2];
-        const uint32_t below = byte_sum(word & ((1u << (8 * (low & 3))) - 1u));
-        s.entry[s.word_prefix[low >> 2] + below + rank] = (low << 16) | static_cast<uint32_t>(r);
+        const int sh = 8 * (low & 3);
+        const uint32_t start = s.word_prefix[low >> 2] + byte_sum(word & ((1u << sh) - 1u));
+        const uint32_t length = (word >> sh) & 0xffu;
+        s.order[start + rank] = static_cast<uint16_t>(r);
+        if (length > 1) run[k] = start | (length << 16);
       }
     }
     __syncthreads();
 
-    // Equal keys must appear in ascending original index: a slot inside a run
+    // Equal keys must appear in ascending original index: a record inside a run
     // of equal keys moves to (run start + number of smaller indices in the run).
-    for (int d = tid; d < count; d += kFinishThreads) {
-      const uint32_t e = s.entry[d];
-      const uint32_t key = e >> 16, rec = e & 0xffffu;
-      int dst = d;
-      const bool tie = (d > 0 && (s.entry[d - 1] >> 16) == key) ||
-                       (d + 1 < count && (s.entry[d + 1] >> 16) == key);
-      if (tie) {
-        const uint32_t mine = s.raw[rec * kRecordWords + 1];
-        int lo = d, smaller = 0;
-        while (lo > 0 && (s.entry[lo - 1] >> 16) == key) {
-          --lo;
-          smaller += s.raw[(s.entry[lo] & 0xffffu) * kRecordWords + 1] < mine;
-        }
-        for (int j = d + 1; j < count && (s.entry[j] >> 16) == key; ++j)
-          smaller += s.raw[(s.entry[j] & 0xffffu) * kRecordWords + 1] < mine;
-        dst = lo + smaller;
+    uint32_t moved[kFinishItems];
+#pragma unroll
+    for (int k = 0; k < kFinishItems; ++k) {
+      moved[k] = 0xffffffffu;
+      if (run[k]) {
+        const int r = tid + k * kFinishThreads;
+        const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
+        const uint32_t mine = s.raw[r * kRecordWords + 1];
+        uint32_t smaller = 0;
+        for (uint32_t j = 0; j < length; ++j)
+          smaller += s.raw[s.order[start + j] * kRecordWords + 1] < mine;
+        moved[k] = start + smaller;
       }
-      final_slot[dst] = static_cast<uint16_t>(rec);
     }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kFinishItems; ++k)
+      if (moved[k] != 0xffffffffu) s.order[moved[k]] = static_cast<uint16_t>(tid + k * kFinishThreads);
     __syncthreads();
 
     // Coalesced output: each lane pulls one whole record out of shared memory
     // and writes its eight words to the eight output arrays.
     for (int d = tid; d < count; d += kFinishThreads) {
-      const int rec = final_slot[d];
+      const int rec = s.order[d];
       const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords]);
       const uint4 c = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4]);
       const size_t o = static_cast<size_t>(begin) + d;
