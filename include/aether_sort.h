@@ -103,6 +103,30 @@ int AetherSlabPartition(const float* x, const float* y, const float* z, const fl
                         float* vz_out, int64_t* counts_out, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* Multi-GPU step 1 fused with the exchange: instead of partitioning locally and
+ * handing the arrays to an all-to-all, the scatter writes every particle straight
+ * into the receive buffer of its destination GPU over NVLink (plain peer stores,
+ * coalesced runs).  Two calls, with the ranks' count exchange in between:
+ *   AetherSlabExchangeCount    counts_out[d] (device) = particles bound for rank d;
+ *                              leaves the tile offsets in the workspace;
+ *   AetherSlabExchangeScatter  peer_buffers[d] (host array of device pointers) is
+ *                              rank d's receive buffer of 6 * capacity floats laid
+ *                              out [x | y | z | vx | vy | vz], each `capacity` long
+ *                              (a multiple of 4); recv_base[d] (host) is the number
+ *                              of particles lower ranks send to d.  Same ordering
+ *                              rule as AetherSlabPartition + all-to-all.
+ * The caller must make sure that the peers have finished reading their buffers
+ * before the scatter, and that all ranks' scatters are complete before a buffer
+ * is read (stream-ordered collectives do both).  No counterpart in the reference. */
+int AetherSlabExchangeCount(const float* x, int64_t n, const AetherGrid* grid, int world,
+                            int64_t* counts_out, void* workspace, size_t workspace_bytes,
+                            void* stream);
+int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
+                              const float* velocity, int64_t padded, int64_t n,
+                              const AetherGrid* grid, int world, float* const* peer_buffers,
+                              int64_t capacity, const int64_t* recv_base, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
 /* The move stage that precedes the sort in the DSMC step: x += v*dt, specular
  * reflection at the six walls, in place (fused_particle_push,
  * project_aether/src/custom_kernels/triton/fused_particle_push.py:75-92; arithmetic

@@ -69,7 +69,7 @@ uint64_t g_launches = 0;
 const char* const kStageNames[kNumStages] = {
     "keygen_upsweep", "digit_pass_0", "digit_pass_1", "digit_pass_2", "digit_pass_3",
     "cell_tables", "payload_gather", "bucket_count", "bucket_scan", "bucket_scatter",
-    "bucket_finish", "slab_partition", "particle_push"};
+    "bucket_finish", "slab_partition", "particle_push", "slab_exchange"};
 }  // namespace
 
 void stage_reset() {
@@ -238,4 +238,28 @@ extern "C" int AetherParticlePush(float* x, float* y, float* z, float* vx, float
   if (!count_ok(n) || !lo || !hi) return cudaErrorInvalidValue;
   if (n > 0 && (!x || !y || !z || !vx || !vy || !vz)) return cudaErrorInvalidValue;
   return particle_push(x, y, z, vx, vy, vz, n, dt, lo, hi, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int AetherSlabExchangeCount(const float* x, int64_t n, const AetherGrid* grid, int world,
+                                       int64_t* counts_out, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  if (!count_ok(n) || !grid_ok(grid) || !counts_out || !workspace) return cudaErrorInvalidValue;
+  if (n > 0 && !x) return cudaErrorInvalidValue;
+  return slab_exchange_count(x, n, *grid, world, counts_out, workspace, workspace_bytes,
+                             static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
+                                         const float* velocity, int64_t padded, int64_t n,
+                                         const AetherGrid* grid, int world,
+                                         float* const* peer_buffers, int64_t capacity,
+                                         const int64_t* recv_base, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  if (!count_ok(n) || !grid_ok(grid) || !peer_buffers || !recv_base || !workspace)
+    return cudaErrorInvalidValue;
+  if (capacity <= 0 || capacity % 4 != 0 || world < 1 || world > 8) return cudaErrorInvalidValue;
+  if (n > 0 && (!x || !y || !z || !velocity || padded < n)) return cudaErrorInvalidValue;
+  return slab_exchange_scatter(x, y, z, velocity, padded, n, *grid, world, peer_buffers, capacity,
+                               recv_base, workspace, workspace_bytes,
+                               static_cast<cudaStream_t>(stream));
 }

@@ -112,7 +112,7 @@ __device__ __forceinline__ float4 ldcs4(const float* p) {
 enum Stage {
   kStageKeygen = 0, kStagePass0, kStagePass1, kStagePass2, kStagePass3, kStageCellTables,
   kStageGather, kStageBucketCount, kStageBucketScan, kStageBucketScatter, kStageBucketFinish,
-  kStageSlabPartition, kStagePush, kNumStages
+  kStageSlabPartition, kStagePush, kStageSlabExchange, kNumStages
 };
 void stage_begin(Stage s, cudaStream_t stream);
 void stage_end(Stage s, cudaStream_t stream);
@@ -170,6 +170,14 @@ cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t n
                                int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream,
                                const int32_t* run_if = nullptr);
 
+cudaError_t slab_exchange_count(const float* x, int64_t n, const AetherGrid& g, int world,
+                                int64_t* totals, void* workspace, size_t workspace_bytes,
+                                cudaStream_t stream);
+cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
+                                  int64_t padded, int64_t n, const AetherGrid& g, int world,
+                                  float* const* peer_buffers, int64_t capacity,
+                                  const int64_t* recv_base, void* workspace,
+                                  size_t workspace_bytes, cudaStream_t stream);
 cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
                           float dt, const float* lo, const float* hi, cudaStream_t stream);
 

@@ -140,16 +140,27 @@ slab_scan_blocks_kernel(const uint32_t* __restrict__ tile_count, uint32_t* __res
   }
 }
 
+// Where each destination's particles go: six arrays per destination.  In the
+// local form every destination shares the same six arrays and the position is
+// the rank-wide prefix (destination-major).  In the exchange form the arrays are
+// the receive buffers of the destination GPUs, written over NVLink, and the
+// position is recv_base[d] (what lower ranks send to d) plus the offset inside
+// this rank's block for d.
+struct SlabTargets {
+  float* array[kMaxWorld][6];
+  uint32_t recv_base[kMaxWorld];
+  int exchange;
+};
+
 // Stages the tile in shared memory grouped by destination (stable inside a
-// destination), then writes every destination's run with coalesced stores.
+// destination), then writes every destination's run with coalesced stores:
+// plain stores, to local memory or straight into a peer GPU's memory.
 __global__ void __launch_bounds__(kSlabThreads)
 slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                     int64_t n, AetherGrid g, int slab_width, int world, bool vec,
                     const uint32_t* __restrict__ tile_offset,
-                    const uint32_t* __restrict__ block_sum, float* __restrict__ ox,
-                    float* __restrict__ oy, float* __restrict__ oz, float* __restrict__ ovx,
-                    float* __restrict__ ovy, float* __restrict__ ovz) {
+                    const uint32_t* __restrict__ block_sum, SlabTargets tg) {
   extern __shared__ float stage_raw[];  // [6][kSlabTile]
   float (*stage)[kSlabTile] = reinterpret_cast<float (*)[kSlabTile]>(stage_raw);
   __shared__ unsigned long long warp_lo[8], warp_hi[8];
@@ -199,7 +210,12 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   }
   if (tid < world) {
     const size_t entry = static_cast<size_t>(tid) * gridDim.x + blockIdx.x;
-    out_base[tid] = tile_offset[entry] + block_sum[entry / kScanBlock];
+    uint32_t base = tile_offset[entry] + block_sum[entry / kScanBlock];
+    if (tg.exchange) {
+      const size_t first = static_cast<size_t>(tid) * gridDim.x;  // this rank's first tile for tid
+      base = base - (tile_offset[first] + block_sum[first / kScanBlock]) + tg.recv_base[tid];
+    }
+    out_base[tid] = base;
   }
   __syncthreads();
   uint32_t next[kMaxWorld];
@@ -224,12 +240,8 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 #pragma unroll
     for (int w = 1; w < kMaxWorld; ++w) d += (static_cast<uint32_t>(j) >= local_base[w]);
     const size_t o = static_cast<size_t>(out_base[d]) + (j - local_base[d]);
-    ox[o] = stage[0][j];
-    oy[o] = stage[1][j];
-    oz[o] = stage[2][j];
-    ovx[o] = stage[3][j];
-    ovy[o] = stage[4][j];
-    ovz[o] = stage[5][j];
+#pragma unroll
+    for (int c = 0; c < 6; ++c) tg.array[d][c][o] = stage[c][j];
   }
 }
 
@@ -245,6 +257,47 @@ size_t slab_partition_workspace_bytes(int64_t n, int world) {
                              align_up(blocks * sizeof(uint32_t), 256));
 }
 
+namespace {
+
+// Counts and scans: leaves the (destination, tile) offsets in the workspace and
+// the per-destination totals in `totals`.
+cudaError_t slab_count(const float* x, int64_t n, const AetherGrid& g, int world, bool vec,
+                       int64_t* totals, void* workspace, cudaStream_t stream) {
+  const int tiles = static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
+  uint32_t* tile_count = static_cast<uint32_t*>(workspace);
+  const int64_t entries = static_cast<int64_t>(tiles) * world;
+  const int blocks = static_cast<int>((entries + kScanBlock - 1) / kScanBlock);
+  uint32_t* block_sum = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) +
+                                                    align_up(entries * sizeof(uint32_t), 256));
+  slab_count_kernel<<<tiles, kSlabThreads, 0, stream>>>(x, n, g, g.nx / world, world, vec,
+                                                        tile_count);
+  slab_scan_local_kernel<<<blocks, kScanBlock, 0, stream>>>(tile_count, entries, block_sum);
+  slab_scan_blocks_kernel<<<1, kScanBlock, 0, stream>>>(tile_count, block_sum, blocks, tiles, world,
+                                                        n, totals);
+  count_launches(3);
+  return cudaGetLastError();
+}
+
+cudaError_t slab_scatter(const float* x, const float* y, const float* z, const float* v,
+                         int64_t padded, int64_t n, const AetherGrid& g, int world, bool vec,
+                         const SlabTargets& tg, void* workspace, cudaStream_t stream) {
+  const int tiles = static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
+  uint32_t* tile_count = static_cast<uint32_t*>(workspace);
+  const int64_t entries = static_cast<int64_t>(tiles) * world;
+  uint32_t* block_sum = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) +
+                                                    align_up(entries * sizeof(uint32_t), 256));
+  constexpr int kStageBytes = 6 * kSlabTile * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(slab_scatter_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+  if (e != cudaSuccess) return e;
+  slab_scatter_kernel<<<tiles, kSlabThreads, kStageBytes, stream>>>(
+      x, y, z, v, padded, n, g, g.nx / world, world, vec, tile_count, block_sum, tg);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
 cudaError_t slab_partition(const float* x, const float* y, const float* z, const float* v,
                            int64_t padded, int64_t n, const AetherGrid& g, int world, float* ox,
                            float* oy, float* oz, float* ovx, float* ovy, float* ovz,
@@ -252,29 +305,52 @@ cudaError_t slab_partition(const float* x, const float* y, const float* z, const
                            cudaStream_t stream) {
   if (world < 1 || world > kMaxWorld || g.nx % world != 0) return cudaErrorInvalidValue;
   if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
-  const int tiles = static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
-  uint32_t* tile_count = static_cast<uint32_t*>(workspace);
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
-  const int slab_width = g.nx / world;
   stage_begin(kStageSlabPartition, stream);
-  const int64_t entries = static_cast<int64_t>(tiles) * world;
-  const int blocks = static_cast<int>((entries + kScanBlock - 1) / kScanBlock);
-  uint32_t* block_sum = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) +
-                                                    align_up(entries * sizeof(uint32_t), 256));
-  slab_count_kernel<<<tiles, kSlabThreads, 0, stream>>>(x, n, g, slab_width, world, vec, tile_count);
-  slab_scan_local_kernel<<<blocks, kScanBlock, 0, stream>>>(tile_count, entries, block_sum);
-  slab_scan_blocks_kernel<<<1, kScanBlock, 0, stream>>>(tile_count, block_sum, blocks, tiles, world,
-                                                        n, totals);
-  constexpr int kStageBytes = 6 * kSlabTile * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(slab_scatter_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+  cudaError_t e = slab_count(x, n, g, world, vec, totals, workspace, stream);
   if (e != cudaSuccess) return e;
-  slab_scatter_kernel<<<tiles, kSlabThreads, kStageBytes, stream>>>(x, y, z, v, padded, n, g, slab_width,
-                                                          world, vec, tile_count, block_sum, ox, oy,
-                                                          oz, ovx, ovy, ovz);
+  SlabTargets tg{};
+  for (int d = 0; d < world; ++d) {
+    float* arrays[6] = {ox, oy, oz, ovx, ovy, ovz};
+    for (int c = 0; c < 6; ++c) tg.array[d][c] = arrays[c];
+  }
+  e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, workspace, stream);
   stage_end(kStageSlabPartition, stream);
-  count_launches(4);
-  return cudaGetLastError();
+  return e;
+}
+
+// The two halves of the fused partition + exchange: count, then (after the
+// ranks have exchanged their counts) scatter straight into the peers' buffers.
+cudaError_t slab_exchange_count(const float* x, int64_t n, const AetherGrid& g, int world,
+                                int64_t* totals, void* workspace, size_t workspace_bytes,
+                                cudaStream_t stream) {
+  if (world < 1 || world > kMaxWorld || g.nx % world != 0) return cudaErrorInvalidValue;
+  if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
+  stage_begin(kStageSlabPartition, stream);
+  cudaError_t e = slab_count(x, n, g, world, aligned16(x), totals, workspace, stream);
+  stage_end(kStageSlabPartition, stream);
+  return e;
+}
+
+cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
+                                  int64_t padded, int64_t n, const AetherGrid& g, int world,
+                                  float* const* peer_buffers, int64_t capacity,
+                                  const int64_t* recv_base, void* workspace,
+                                  size_t workspace_bytes, cudaStream_t stream) {
+  if (world < 1 || world > kMaxWorld || g.nx % world != 0) return cudaErrorInvalidValue;
+  if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
+  SlabTargets tg{};
+  tg.exchange = 1;
+  for (int d = 0; d < world; ++d) {
+    if (!peer_buffers[d] || recv_base[d] < 0 || recv_base[d] > capacity) return cudaErrorInvalidValue;
+    for (int c = 0; c < 6; ++c) tg.array[d][c] = peer_buffers[d] + static_cast<size_t>(c) * capacity;
+    tg.recv_base[d] = static_cast<uint32_t>(recv_base[d]);
+  }
+  const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
+  stage_begin(kStageSlabExchange, stream);
+  cudaError_t e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, workspace, stream);
+  stage_end(kStageSlabExchange, stream);
+  return e;
 }
 
 }  // namespace aether

@@ -32,8 +32,11 @@ def run(args, workload: str) -> None:
     n_local = n_total // world
     x, y, z, v = workloads.make_particles(w, device, seed=rank, n=n_local)
 
+    exchange = os.environ.get('AETHER_EXCHANGE', 'peer')  # 'peer' (NVLink stores) or 'nccl'
+
     def step(s):
-        return slab_sort.distributed_sort(x, y, z, v, w.grid, workloads.step_seed(1234, s))
+        return slab_sort.distributed_sort(x, y, z, v, w.grid, workloads.step_seed(1234, s),
+                                          exchange=exchange)
 
     warmup = max(3, args.warmup)
     for s in range(warmup):
@@ -68,6 +71,12 @@ def run(args, workload: str) -> None:
     lib.AetherSortSetStageTiming(0)
     stages = {lib.AetherSortStageName(i).decode(): float(stage_ms[i]) for i in range(count)
               if stage_ms[i] >= 0}
+    # Phase times of one more step (events on the stream; the count exchange includes a host wait).
+    marks = []
+    slab_sort.distributed_sort(x, y, z, v, w.grid, workloads.step_seed(1234, 999), marks=marks,
+                               exchange=exchange)
+    torch.cuda.synchronize()
+    phases = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) for i in range(1, len(marks))}
     received = torch.tensor([out.order.keys.numel()], device=device, dtype=torch.int64)
     dist.all_reduce(received)
     assert int(received) == n_local * world, 'particles were lost in the exchange'
@@ -79,7 +88,8 @@ def run(args, workload: str) -> None:
 
     def e2e_step(s):
         dx, dy, dz, dv = (t.to(device, non_blocking=True) for t in (hx, hy, hz, hv))
-        r = slab_sort.distributed_sort(dx, dy, dz, dv, w.grid, workloads.step_seed(1234, s))
+        r = slab_sort.distributed_sort(dx, dy, dz, dv, w.grid, workloads.step_seed(1234, s),
+                                       exchange=exchange)
         outs = [r.order.keys, r.order.particle_index, r.order.cell_counts, r.order.cell_start,
                 *r.positions, r.velocity]
         host = [o.to('cpu', non_blocking=False) for o in outs]
@@ -118,7 +128,10 @@ def run(args, workload: str) -> None:
             'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'u32',
             'data': 'synthetic',
             'config': {'workload': workload, 'particles': n_total, 'cells': list(w.grid.cells),
-                       'decomposition': f'{world} x-slabs, one all-to-all per payload array',
+                       'decomposition': f'{world} x-slabs',
+                       'exchange': ('partition kernel stores into the peers\' receive buffers '
+                                    'over NVLink' if exchange == 'peer'
+                                    else 'one NCCL all-to-all per payload array'),
                        'initial_share': 'random 1/G of all particles per rank',
                        'l2': 'inputs larger than L2 (no flush needed)'},
             'clocks': {'sm_mhz': clocks['sm_mhz'], 'sm_max_mhz': clocks['sm_max_mhz'],
@@ -127,6 +140,7 @@ def run(args, workload: str) -> None:
                     'h2d_bytes_per_step': int(bytes_io[0]), 'd2h_bytes_per_step': int(bytes_io[1]),
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': launches, 'roofline': roofline, 'stage_ms_rank0': stages,
+            'phase_ms_rank0': phases,
             'cpu_baseline': None,
         }
         print(json.dumps(line))

@@ -142,7 +142,8 @@ def sort_particles_by_cell(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
 def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
                               velocity: torch.Tensor, grid: CellGrid, seed: int, *,
                               ix_offset: int = 0, nx_local: Optional[int] = None,
-                              path: int = PATH_AUTO) -> SortedParticles:
+                              path: int = PATH_AUTO,
+                              padded_out: Optional[int] = None) -> SortedParticles:
     """Sorts by cell and returns the particle payload in sorted order.
 
     One call for lines 105-109 of the reference's DSMC step
@@ -155,6 +156,7 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
         (the reference keeps padded = ceil(N / 4) * 4, dsmc_gpu_pipeline.py:69-71).
       grid, seed, ix_offset, nx_local: as in `sort_particles_by_cell`.
       path: PATH_AUTO, PATH_DIGIT_PASSES or PATH_BUCKETED (same results).
+      padded_out: row stride of the sorted velocity (default: that of the input).
 
     Returns:
       SortedParticles(order, (x, y, z) sorted, velocity sorted (3, padded) with
@@ -167,8 +169,9 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
             or velocity.shape[0] != 3 or velocity.shape[1] < n):
         raise ValueError('Velocity must be a float32 CUDA tensor of shape (3, padded) '
                          'with padded >= N.')
-    velocity = velocity.contiguous()
-    padded = velocity.shape[1]
+    if velocity.stride(1) != 1:
+        velocity = velocity.contiguous()
+    padded = velocity.stride(0) if velocity.shape[1] > 0 else velocity.shape[1]
     lib = _native.load_library()
     g = native_grid(grid, ix_offset, nx_local)
     cells = g.nx_local * g.ny * g.nz
@@ -179,8 +182,11 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
         counts = torch.empty(cells, dtype=torch.int32, device=device)
         start = torch.empty(cells + 1, dtype=torch.int32, device=device)
         xs, ys, zs = (torch.empty(n, dtype=torch.float32, device=device) for _ in range(3))
-        vs = torch.empty((3, padded), dtype=torch.float32, device=device)
-        if padded > n:
+        padded_sorted = padded if padded_out is None else int(padded_out)
+        if padded_sorted < n:
+            raise ValueError('padded_out must be at least the number of particles.')
+        vs = torch.empty((3, padded_sorted), dtype=torch.float32, device=device)
+        if padded_sorted > n:
             vs[:, n:].zero_()
         nbytes = lib.AetherSortWorkspaceBytes(n, cells, 1)
         ws = _workspace(device, nbytes)
@@ -188,7 +194,7 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
         _native.check(lib.AetherSortAndGatherParticles(
             _ptr(x), _ptr(y), _ptr(z), _ptr(velocity), padded, n, ctypes.byref(g),
             int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(keys), _ptr(index), _ptr(counts), _ptr(start),
-            _ptr(xs), _ptr(ys), _ptr(zs), _ptr(vs), padded, int(path), _ptr(ws), ws.numel(),
+            _ptr(xs), _ptr(ys), _ptr(zs), _ptr(vs), padded_sorted, int(path), _ptr(ws), ws.numel(),
             ctypes.c_void_p(stream)), 'AetherSortAndGatherParticles')
     return SortedParticles(SortResult(keys, index, counts, start), (xs, ys, zs), vs)
 

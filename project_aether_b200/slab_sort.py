@@ -97,17 +97,119 @@ def exchange_particles(arrays: Sequence[torch.Tensor], matrix: torch.Tensor, gro
     return received
 
 
+class PeerBuffers:
+    """Receive buffers of all ranks, mapped into every rank's address space
+    (`torch.distributed._symmetric_memory`): 6 arrays of `capacity` floats per rank,
+    [x | y | z | vx | vy | vz].  The fused partition + exchange kernel stores into
+    them over NVLink."""
+
+    def __init__(self, capacity: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.capacity = -(-int(capacity) // 4) * 4
+        self.buffer = symm_mem.empty(6 * self.capacity, dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, group if group is not None
+                                          else dist.group.WORLD)
+        self.pointers = [int(p) for p in self.handle.buffer_ptrs]
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def views(self, n: int):
+        """(x, y, z, velocity(3, capacity)) of the first n received particles."""
+        c = self.capacity
+        b = self.buffer
+        return b[0:n], b[c:c + n], b[2 * c:2 * c + n], b[3 * c:6 * c].view(3, c)
+
+
+_peer_buffers = {}
+
+
+def _buffers_for(capacity: int, device: torch.device, group) -> PeerBuffers:
+    key = (device.index, id(group))
+    have = _peer_buffers.get(key)
+    if have is None or have.capacity < capacity:
+        # Collective: every rank takes this branch together, because the capacity asked for
+        # is computed from the count matrix that all ranks hold.
+        have = PeerBuffers(int(capacity * 1.25) + 1024, device, group)
+        _peer_buffers[key] = have
+    return have
+
+
+def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
+                       path: int = PATH_AUTO, mark=lambda name: None) -> SortedParticles:
+    """distributed_sort with the partition and the exchange fused: one kernel reads the
+    rank's particles once and stores each into its destination GPU's receive buffer over
+    NVLink; the count all-gather before it and a one-word all-reduce after it are the only
+    collectives."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    ix_offset, nx_local = slab_range(grid, world, rank)
+    n, device = x.numel(), x.device
+    lib = _native.load_library()
+    g = native_grid(grid)
+    if velocity.stride(1) != 1:
+        velocity = velocity.contiguous()
+    with torch.cuda.device(device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        counts = torch.zeros(world, dtype=torch.int64, device=device)
+        ws = _workspace(device, lib.AetherSlabPartitionWorkspaceBytes(n, world))
+        # The scatter below needs the offsets this call leaves in the workspace, and the sort
+        # that follows reuses the cached workspace: give the partition its own slice.
+        part_ws = torch.empty(lib.AetherSlabPartitionWorkspaceBytes(n, world), dtype=torch.uint8,
+                              device=device)
+        del ws
+        _native.check(lib.AetherSlabExchangeCount(
+            x.data_ptr(), n, ctypes.byref(g), world, counts.data_ptr(), part_ws.data_ptr(),
+            part_ws.numel(), stream), 'AetherSlabExchangeCount')
+        mark('partition')
+        matrix = exchange_counts(counts, group)  # also orders this step after the peers' last sort
+        mark('counts')
+        received = matrix.sum(dim=0)
+        buffers = _buffers_for(int(received.max()), device, group)
+        pointers = (ctypes.c_void_p * world)(*buffers.pointers)
+        recv_base = (ctypes.c_int64 * world)(*[int(matrix[:rank, d].sum()) for d in range(world)])
+        _native.check(lib.AetherSlabExchangeScatter(
+            x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(), velocity.stride(0), n,
+            ctypes.byref(g), world, pointers, buffers.capacity, recv_base, part_ws.data_ptr(),
+            part_ws.numel(), stream), 'AetherSlabExchangeScatter')
+        # Every rank's stores must have landed before anyone reads its buffer.
+        dist.all_reduce(buffers.flag, group=group)
+        mark('exchange')
+        m = int(received[rank])
+        rx, ry, rz, rv = buffers.views(m)
+        out = sort_and_gather_particles(rx, ry, rz, rv, grid, seed, ix_offset=ix_offset,
+                                        nx_local=nx_local, path=path,
+                                        padded_out=-(-m // 4) * 4)
+        mark('sort')
+    return out
+
+
 def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity: torch.Tensor,
-                     grid: CellGrid, seed: int, group=None, path: int = PATH_AUTO
-                     ) -> SortedParticles:
+                     grid: CellGrid, seed: int, group=None, path: int = PATH_AUTO,
+                     marks: Optional[list] = None, exchange: str = 'peer') -> SortedParticles:
     """Sorts the particles of all ranks by cell; every rank ends with its slab's
-    particles, cell-sorted, with slab-local `cell_counts` / `cell_start`."""
+    particles, cell-sorted, with slab-local `cell_counts` / `cell_start`.
+
+    `exchange`: 'peer' fuses the partition with the exchange (stores into the peers'
+    receive buffers over NVLink); 'nccl' partitions locally and calls one NCCL all-to-all per
+    payload array.  Same result either way.
+    `marks`, if given, receives (name, cuda event) pairs recorded on the current stream
+    after each phase (partition, counts, exchange, sort), for phase timing."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     ix_offset, nx_local = slab_range(grid, world, rank)
     if world == 1:
         return sort_and_gather_particles(x, y, z, velocity, grid, seed, path=path)
+
+    def mark(name):
+        if marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append((name, ev))
+
+    mark('begin')
+    if exchange == 'peer':
+        return peer_exchange_sort(x, y, z, velocity, grid, seed, group, path, mark)
     parts = partition_by_slab(x, y, z, velocity, grid, world)
+    mark('partition')
     matrix = exchange_counts(parts.counts, group)
+    mark('counts')
     n = int(matrix[:, rank].sum())
     padded = -(-n // 4) * 4
     device = x.device
@@ -117,5 +219,8 @@ def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity
         rv[:, n:].zero_()
     exchange_particles(parts.arrays, matrix, group,
                        out=(rx, ry, rz, rv[0, :n], rv[1, :n], rv[2, :n]))
-    return sort_and_gather_particles(rx, ry, rz, rv, grid, seed, ix_offset=ix_offset,
-                                     nx_local=nx_local, path=path)
+    mark('exchange')
+    out = sort_and_gather_particles(rx, ry, rz, rv, grid, seed, ix_offset=ix_offset,
+                                    nx_local=nx_local, path=path)
+    mark('sort')
+    return out

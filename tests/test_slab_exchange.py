@@ -147,19 +147,25 @@ def _nccl_worker(rank, world, port, result_dir):
         ogrid = so.Grid(grid.lo, grid.hi, grid.cells)
         shares = [_device_share(grid, 50_000 + 3 * r, 100 + r, device) for r in range(world)]
         x, y, z, v = shares[rank]
-        got = slab_sort.distributed_sort(x, y, z, v, grid, 91)
         host = [tuple(a.cpu().numpy() for a in (sh[0], sh[1], sh[2], sh[3][0, :sh[0].numel()],
                                                 sh[3][1, :sh[0].numel()], sh[3][2, :sh[0].numel()]))
                 for sh in shares]
         mine = so.exchange_replay(host, ogrid, world)[rank]
         off, width = slab_sort.slab_range(grid, world, rank)
         want = so.sort_particles(*mine[:3], ogrid, 91, ix_offset=off, nx_local=width)
-        np.testing.assert_array_equal(got.order.keys.cpu().numpy().view(np.uint32), want.keys)
-        np.testing.assert_array_equal(got.order.particle_index.cpu().numpy(), want.particle_index)
-        np.testing.assert_array_equal(got.order.cell_counts.cpu().numpy(), want.cell_counts)
-        np.testing.assert_array_equal(got.positions[0].cpu().numpy(), mine[0][want.particle_index])
-        np.testing.assert_array_equal(got.velocity.cpu().numpy()[2, :want.keys.size],
-                                      mine[5][want.particle_index])
+        # Both exchanges (NCCL all-to-all; stores into the peers' buffers), twice each: the
+        # second round reuses the peer buffers of the first.
+        for exchange in ('nccl', 'peer', 'peer', 'nccl'):
+            got = slab_sort.distributed_sort(x, y, z, v, grid, 91, exchange=exchange)
+            np.testing.assert_array_equal(got.order.keys.cpu().numpy().view(np.uint32), want.keys)
+            np.testing.assert_array_equal(got.order.particle_index.cpu().numpy(),
+                                          want.particle_index)
+            np.testing.assert_array_equal(got.order.cell_counts.cpu().numpy(), want.cell_counts)
+            np.testing.assert_array_equal(got.positions[0].cpu().numpy(),
+                                          mine[0][want.particle_index])
+            np.testing.assert_array_equal(got.velocity.cpu().numpy()[2, :want.keys.size],
+                                          mine[5][want.particle_index])
+            assert got.velocity.shape[1] == -(-want.keys.size // 4) * 4
         open(os.path.join(result_dir, f'ok{rank}'), 'w').close()
     finally:
         dist.destroy_process_group()
