@@ -112,8 +112,12 @@ int AetherSlabPartition(const float* x, const float* y, const float* z, const fl
  *   AetherSlabExchangeScatter  peer_buffers[d] (host array of device pointers) is
  *                              rank d's receive buffer of 6 * capacity floats laid
  *                              out [x | y | z | vx | vy | vz], each `capacity` long
- *                              (a multiple of 4); recv_base[d] (host) is the number
- *                              of particles lower ranks send to d.  Same ordering
+ *                              (a multiple of 4); count_matrix (device, int64
+ *                              [world][world], [s][d] = particles s sends to d) is
+ *                              the all-gathered counts, read on the device so that
+ *                              the host need not wait for it; if some rank would
+ *                              receive more than `capacity`, nothing is stored for
+ *                              it and *error_out (device) is set.  Same ordering
  *                              rule as AetherSlabPartition + all-to-all.
  * The caller must make sure that the peers have finished reading their buffers
  * before the scatter, and that all ranks' scatters are complete before a buffer
@@ -123,8 +127,9 @@ int AetherSlabExchangeCount(const float* x, int64_t n, const AetherGrid* grid, i
                             void* stream);
 int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
                               const float* velocity, int64_t padded, int64_t n,
-                              const AetherGrid* grid, int world, float* const* peer_buffers,
-                              int64_t capacity, const int64_t* recv_base, void* workspace,
+                              const AetherGrid* grid, int world, int rank,
+                              float* const* peer_buffers, int64_t capacity,
+                              const int64_t* count_matrix, int32_t* error_out, void* workspace,
                               size_t workspace_bytes, void* stream);
 
 /* The move stage that precedes the sort in the DSMC step: x += v*dt, specular

@@ -47,9 +47,8 @@ _SIGNATURES = {
                                                _P, _P, ctypes.c_size_t, _P]),
     'AetherSlabExchangeScatter': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64,
                                                  ctypes.POINTER(AetherGrid), ctypes.c_int,
-                                                 ctypes.POINTER(ctypes.c_void_p), _I64,
-                                                 ctypes.POINTER(ctypes.c_int64), _P,
-                                                 ctypes.c_size_t, _P]),
+                                                 ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                                 _I64, _P, _P, _P, ctypes.c_size_t, _P]),
     'AetherParticlePush': (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _I64, ctypes.c_float,
                                           ctypes.POINTER(ctypes.c_float),
                                           ctypes.POINTER(ctypes.c_float), _P]),

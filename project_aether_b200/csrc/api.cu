@@ -251,15 +251,15 @@ extern "C" int AetherSlabExchangeCount(const float* x, int64_t n, const AetherGr
 
 extern "C" int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
                                          const float* velocity, int64_t padded, int64_t n,
-                                         const AetherGrid* grid, int world,
+                                         const AetherGrid* grid, int world, int rank,
                                          float* const* peer_buffers, int64_t capacity,
-                                         const int64_t* recv_base, void* workspace,
-                                         size_t workspace_bytes, void* stream) {
-  if (!count_ok(n) || !grid_ok(grid) || !peer_buffers || !recv_base || !workspace)
+                                         const int64_t* count_matrix, int32_t* error_out,
+                                         void* workspace, size_t workspace_bytes, void* stream) {
+  if (!count_ok(n) || !grid_ok(grid) || !peer_buffers || !count_matrix || !error_out || !workspace)
     return cudaErrorInvalidValue;
   if (capacity <= 0 || capacity % 4 != 0 || world < 1 || world > 8) return cudaErrorInvalidValue;
   if (n > 0 && (!x || !y || !z || !velocity || padded < n)) return cudaErrorInvalidValue;
-  return slab_exchange_scatter(x, y, z, velocity, padded, n, *grid, world, peer_buffers, capacity,
-                               recv_base, workspace, workspace_bytes,
+  return slab_exchange_scatter(x, y, z, velocity, padded, n, *grid, world, rank, peer_buffers,
+                               capacity, count_matrix, error_out, workspace, workspace_bytes,
                                static_cast<cudaStream_t>(stream));
 }

@@ -27,6 +27,7 @@ constexpr uint32_t kValueMask = ~kFlagMask;
 constexpr int kErrLookbackTimeout = 1;
 constexpr int kErrBucketOverflow = 2;
 constexpr int kErrBulkCopyTimeout = 3;
+constexpr int kErrReceiveOverflow = 5;
 
 // Workspace header (first 1 KiB of the workspace, zeroed by every call).
 struct alignas(16) Header {
@@ -175,8 +176,8 @@ cudaError_t slab_exchange_count(const float* x, int64_t n, const AetherGrid& g, 
                                 cudaStream_t stream);
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
                                   int64_t padded, int64_t n, const AetherGrid& g, int world,
-                                  float* const* peer_buffers, int64_t capacity,
-                                  const int64_t* recv_base, void* workspace,
+                                  int rank, float* const* peer_buffers, int64_t capacity,
+                                  const int64_t* count_matrix, int32_t* error, void* workspace,
                                   size_t workspace_bytes, cudaStream_t stream);
 cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
                           float dt, const float* lo, const float* hi, cudaStream_t stream);

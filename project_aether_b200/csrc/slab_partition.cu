@@ -148,8 +148,11 @@ slab_scan_blocks_kernel(const uint32_t* __restrict__ tile_count, uint32_t* __res
 // this rank's block for d.
 struct SlabTargets {
   float* array[kMaxWorld][6];
-  uint32_t recv_base[kMaxWorld];
+  const int64_t* count_matrix;  // exchange form: [world][world] on the device, [s][d] = s sends d
+  int64_t capacity;             // exchange form: particles a receive buffer holds
+  int rank;
   int exchange;
+  int32_t* error;               // exchange form: set to kErrReceiveOverflow if a buffer is too small
 };
 
 // Stages the tile in shared memory grouped by destination (stable inside a
@@ -212,8 +215,20 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     const size_t entry = static_cast<size_t>(tid) * gridDim.x + blockIdx.x;
     uint32_t base = tile_offset[entry] + block_sum[entry / kScanBlock];
     if (tg.exchange) {
+      // Receive position: what lower ranks send to destination tid, then this rank's block.
+      int64_t lower = 0, all = 0;
+      for (int s = 0; s < world; ++s) {
+        const int64_t c = tg.count_matrix[s * world + tid];
+        if (s < tg.rank) lower += c;
+        all += c;
+      }
       const size_t first = static_cast<size_t>(tid) * gridDim.x;  // this rank's first tile for tid
-      base = base - (tile_offset[first] + block_sum[first / kScanBlock]) + tg.recv_base[tid];
+      base = base - (tile_offset[first] + block_sum[first / kScanBlock]) +
+             static_cast<uint32_t>(lower);
+      if (all > tg.capacity) {  // never store past a peer's buffer
+        base = 0xffffffffu;
+        if (blockIdx.x == 0) atomicCAS(tg.error, 0, kErrReceiveOverflow);
+      }
     }
     out_base[tid] = base;
   }
@@ -239,6 +254,7 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     int d = 0;
 #pragma unroll
     for (int w = 1; w < kMaxWorld; ++w) d += (static_cast<uint32_t>(j) >= local_base[w]);
+    if (out_base[d] == 0xffffffffu) continue;
     const size_t o = static_cast<size_t>(out_base[d]) + (j - local_base[d]);
 #pragma unroll
     for (int c = 0; c < 6; ++c) tg.array[d][c][o] = stage[c][j];
@@ -334,17 +350,21 @@ cudaError_t slab_exchange_count(const float* x, int64_t n, const AetherGrid& g, 
 
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
                                   int64_t padded, int64_t n, const AetherGrid& g, int world,
-                                  float* const* peer_buffers, int64_t capacity,
-                                  const int64_t* recv_base, void* workspace,
+                                  int rank, float* const* peer_buffers, int64_t capacity,
+                                  const int64_t* count_matrix, int32_t* error, void* workspace,
                                   size_t workspace_bytes, cudaStream_t stream) {
   if (world < 1 || world > kMaxWorld || g.nx % world != 0) return cudaErrorInvalidValue;
+  if (rank < 0 || rank >= world || !count_matrix || !error) return cudaErrorInvalidValue;
   if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
   SlabTargets tg{};
   tg.exchange = 1;
+  tg.count_matrix = count_matrix;
+  tg.capacity = capacity;
+  tg.rank = rank;
+  tg.error = error;
   for (int d = 0; d < world; ++d) {
-    if (!peer_buffers[d] || recv_base[d] < 0 || recv_base[d] > capacity) return cudaErrorInvalidValue;
+    if (!peer_buffers[d]) return cudaErrorInvalidValue;
     for (int c = 0; c < 6; ++c) tg.array[d][c] = peer_buffers[d] + static_cast<size_t>(c) * capacity;
-    tg.recv_base[d] = static_cast<uint32_t>(recv_base[d]);
   }
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
   stage_begin(kStageSlabExchange, stream);

@@ -137,8 +137,9 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
                        path: int = PATH_AUTO, mark=lambda name: None) -> SortedParticles:
     """distributed_sort with the partition and the exchange fused: one kernel reads the
     rank's particles once and stores each into its destination GPU's receive buffer over
-    NVLink; the count all-gather before it and a one-word all-reduce after it are the only
-    collectives."""
+    NVLink.  The count all-gather before it and a one-word all-reduce after it are the only
+    collectives.  The kernel reads the gathered counts on the device, so the host waits for
+    them (it needs its own receive count to launch the local sort) while the exchange runs."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     ix_offset, nx_local = slab_range(grid, world, rank)
     n, device = x.numel(), x.device
@@ -146,31 +147,51 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
     g = native_grid(grid)
     if velocity.stride(1) != 1:
         velocity = velocity.contiguous()
+    key = (device.index, id(group))
     with torch.cuda.device(device):
-        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        current = torch.cuda.current_stream(device)
+        stream = ctypes.c_void_p(current.cuda_stream)
         counts = torch.zeros(world, dtype=torch.int64, device=device)
-        ws = _workspace(device, lib.AetherSlabPartitionWorkspaceBytes(n, world))
-        # The scatter below needs the offsets this call leaves in the workspace, and the sort
-        # that follows reuses the cached workspace: give the partition its own slice.
         part_ws = torch.empty(lib.AetherSlabPartitionWorkspaceBytes(n, world), dtype=torch.uint8,
                               device=device)
-        del ws
         _native.check(lib.AetherSlabExchangeCount(
             x.data_ptr(), n, ctypes.byref(g), world, counts.data_ptr(), part_ws.data_ptr(),
             part_ws.numel(), stream), 'AetherSlabExchangeCount')
         mark('partition')
-        matrix = exchange_counts(counts, group)  # also orders this step after the peers' last sort
+        # The all-gather also orders this step after the peers' previous sort.
+        matrix_dev = torch.empty((world, world), dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(matrix_dev, counts, group=group)
+        gathered = torch.cuda.Event()
+        gathered.record(current)
         mark('counts')
-        received = matrix.sum(dim=0)
-        buffers = _buffers_for(int(received.max()), device, group)
-        pointers = (ctypes.c_void_p * world)(*buffers.pointers)
-        recv_base = (ctypes.c_int64 * world)(*[int(matrix[:rank, d].sum()) for d in range(world)])
-        _native.check(lib.AetherSlabExchangeScatter(
-            x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(), velocity.stride(0), n,
-            ctypes.byref(g), world, pointers, buffers.capacity, recv_base, part_ws.data_ptr(),
-            part_ws.numel(), stream), 'AetherSlabExchangeScatter')
-        # Every rank's stores must have landed before anyone reads its buffer.
-        dist.all_reduce(buffers.flag, group=group)
+        buffers = _peer_buffers.get(key)
+        while True:
+            if buffers is not None:
+                pointers = (ctypes.c_void_p * world)(*buffers.pointers)
+                error = torch.zeros(1, dtype=torch.int32, device=device)
+                _native.check(lib.AetherSlabExchangeScatter(
+                    x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
+                    velocity.stride(0), n, ctypes.byref(g), world, rank, pointers,
+                    buffers.capacity, matrix_dev.data_ptr(), error.data_ptr(), part_ws.data_ptr(),
+                    part_ws.numel(), stream), 'AetherSlabExchangeScatter')
+                # Every rank's stores must have landed before anyone reads its buffer.
+                dist.all_reduce(buffers.flag, group=group)
+            # Fetch the counts on a side stream so that the copy does not queue behind the
+            # exchange kernel.
+            side = _side_stream(device)
+            side.wait_event(gathered)
+            with torch.cuda.stream(side):
+                matrix = matrix_dev.to('cpu', non_blocking=True)
+            side.synchronize()
+            received = matrix.sum(dim=0)
+            if buffers is not None and int(received.max()) <= buffers.capacity:
+                break
+            # First call, or a rank would receive more than the buffers hold: (re)allocate,
+            # collectively, and run the exchange again.  Nobody may still be storing into
+            # the buffers that are about to be dropped.
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)
+            buffers = _buffers_for(int(received.max()), device, group)
         mark('exchange')
         m = int(received[rank])
         rx, ry, rz, rv = buffers.views(m)
@@ -179,6 +200,17 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
                                         padded_out=-(-m // 4) * 4)
         mark('sort')
     return out
+
+
+_side_streams = {}
+
+
+def _side_stream(device: torch.device) -> torch.cuda.Stream:
+    s = _side_streams.get(device.index)
+    if s is None:
+        s = torch.cuda.Stream(device=device)
+        _side_streams[device.index] = s
+    return s
 
 
 def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity: torch.Tensor,
