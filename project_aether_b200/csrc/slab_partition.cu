@@ -152,6 +152,7 @@ struct SlabTargets {
   int64_t capacity;             // exchange form: particles a receive buffer holds
   int rank;
   int exchange;
+  int aligned;                  // every output array starts on a 16-byte boundary
   int32_t* error;               // exchange form: set to kErrReceiveOverflow if a buffer is too small
 };
 
@@ -249,15 +250,33 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     for (int c = 0; c < 6; ++c) stage[c][p] = f[c][k];
   }
   __syncthreads();
-  const int valid = static_cast<int>(local_base[kMaxWorld]);
-  for (int j = tid; j < valid; j += kSlabThreads) {
-    int d = 0;
-#pragma unroll
-    for (int w = 1; w < kMaxWorld; ++w) d += (static_cast<uint32_t>(j) >= local_base[w]);
+  // Write every destination's run: 16-byte stores over the part of the run whose
+  // destination is 16-byte aligned (longer NVLink and HBM bursts), scalar stores for
+  // the up to three elements before and after it.
+  for (int d = 0; d < world; ++d) {
     if (out_base[d] == 0xffffffffu) continue;
-    const size_t o = static_cast<size_t>(out_base[d]) + (j - local_base[d]);
+    const int lb = static_cast<int>(local_base[d]), le = static_cast<int>(local_base[d + 1]);
+    if (le <= lb) continue;
+    const size_t g0 = out_base[d];
+    const int head = tg.aligned ? min(le - lb, static_cast<int>((4 - (g0 & 3)) & 3)) : le - lb;
+    const int quads = (le - lb - head) / 4;
+    const int tail_first = lb + head + 4 * quads;
+    for (int q = tid; q < quads; q += kSlabThreads) {
+      const int j = lb + head + 4 * q;
+      const size_t o = g0 + (j - lb);
 #pragma unroll
-    for (int c = 0; c < 6; ++c) tg.array[d][c][o] = stage[c][j];
+      for (int c = 0; c < 6; ++c)
+        *reinterpret_cast<float4*>(tg.array[d][c] + o) =
+            make_float4(stage[c][j], stage[c][j + 1], stage[c][j + 2], stage[c][j + 3]);
+    }
+    for (int i = tid; i < head; i += kSlabThreads) {
+#pragma unroll
+      for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + i] = stage[c][lb + i];
+    }
+    for (int j = tail_first + tid; j < le; j += kSlabThreads) {
+#pragma unroll
+      for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + (j - lb)] = stage[c][j];
+    }
   }
 }
 
@@ -330,6 +349,8 @@ cudaError_t slab_partition(const float* x, const float* y, const float* z, const
     float* arrays[6] = {ox, oy, oz, ovx, ovy, ovz};
     for (int c = 0; c < 6; ++c) tg.array[d][c] = arrays[c];
   }
+  tg.aligned = aligned16(ox) && aligned16(oy) && aligned16(oz) && aligned16(ovx) &&
+               aligned16(ovy) && aligned16(ovz);
   e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, workspace, stream);
   stage_end(kStageSlabPartition, stream);
   return e;
@@ -365,6 +386,7 @@ cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z
   for (int d = 0; d < world; ++d) {
     if (!peer_buffers[d]) return cudaErrorInvalidValue;
     for (int c = 0; c < 6; ++c) tg.array[d][c] = peer_buffers[d] + static_cast<size_t>(c) * capacity;
+    tg.aligned = (d == 0 ? 1 : tg.aligned) && aligned16(peer_buffers[d]);
   }
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
   stage_begin(kStageSlabExchange, stream);
