@@ -110,6 +110,25 @@ def run(args, workload: str) -> None:
                             device=device, dtype=torch.int64)
     dist.all_reduce(bytes_io)
 
+    # Strong-scaling denominator: the same workload, whole, on one GPU (rank 0 alone).
+    single = None
+    del hx, hy, hz, hv
+    if rank == 0:
+        ax, ay, az, av = workloads.make_particles(w, device, seed=0)
+        for s in range(2):
+            pa.sort_and_gather_particles(ax, ay, az, av, w.grid, workloads.step_seed(1234, s))
+        torch.cuda.synchronize()
+        begin.record()
+        for s in range(3):
+            pa.sort_and_gather_particles(ax, ay, az, av, w.grid, workloads.step_seed(1234, 50 + s))
+        end.record()
+        torch.cuda.synchronize()
+        one_ms = begin.elapsed_time(end) / 3
+        single = {'value': n_total / (one_ms * 1e-3), 'unit': 'particles/s', 'ms_per_step': one_ms,
+                  'steps': 3}
+        del ax, ay, az, av
+    dist.barrier()
+
     if rank == 0:
         peak, peak_kind = bench_mod.measured_peak()
         n_rank = n_total // world
@@ -141,6 +160,7 @@ def run(args, workload: str) -> None:
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': launches, 'roofline': roofline, 'stage_ms_rank0': stages,
             'phase_ms_rank0': phases,
+            'single_gpu_same_workload': single,
             'cpu_baseline': None,
         }
         print(json.dumps(line))
