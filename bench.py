@@ -44,6 +44,14 @@ STAGE_BYTES_PER_PARTICLE = {
 }
 
 
+# DRAM bytes per particle (dram__bytes_read.sum + dram__bytes_write.sum) of each bucketed-path
+# kernel, from one ncu capture at 2^24 particles of the same density
+# (profiles/bucketed_kernels_c3_hypersonic_16m.md); traffic grows in proportion to the
+# particle count, so a launch's traffic is this figure times its particles.
+NCU_DRAM_BYTES_PER_PARTICLE = {'bucket_count': 12.2, 'bucket_scatter': 52.9,
+                               'bucket_finish': 61.5}
+
+
 def measured_peak():
     path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(path):
@@ -238,7 +246,10 @@ def run_single(args, workload):
         achieved = bytes_per_launch / (stages[top] * 1e-3) / 1e9
         roofline = {'bound': 'hbm', 'kernel': top, 'achieved': achieved, 'peak': peak,
                     'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind,
-                    'traffic': None, 'bytes_per_launch': bytes_per_launch,
+                    'traffic': (NCU_DRAM_BYTES_PER_PARTICLE[top] * n
+                                if top in NCU_DRAM_BYTES_PER_PARTICLE else None),
+                    'traffic_source': 'ncu capture at 2^24 particles scaled by particle count',
+                    'bytes_per_launch': bytes_per_launch,
                     'ms_per_launch': stages[top]}
     b_alg = algorithmic_bytes(n, cells)
     path_gbs = b_alg / (ms * 1e-3) / 1e9

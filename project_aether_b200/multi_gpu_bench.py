@@ -140,7 +140,9 @@ def run(args, workload: str) -> None:
             achieved = nbytes / (stages[top] * 1e-3) / 1e9
             roofline = {'bound': 'hbm', 'kernel': top, 'achieved': achieved, 'peak': peak,
                         'unit': 'GB/s', 'frac': achieved / peak, 'peak_kind': peak_kind,
-                        'traffic': None, 'bytes_per_launch': nbytes, 'ms_per_launch': stages[top]}
+                        'traffic': (bench_mod.NCU_DRAM_BYTES_PER_PARTICLE[top] * n_rank
+                                    if top in bench_mod.NCU_DRAM_BYTES_PER_PARTICLE else None),
+                        'bytes_per_launch': nbytes, 'ms_per_launch': stages[top]}
         line = {
             'metric': 'sorted particles/s', 'value': n_total / (ms * 1e-3), 'unit': 'particles/s',
             'n_gpus': world, 'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms,
