@@ -103,6 +103,34 @@ __device__ __forceinline__ uint32_t lanemask_lt() {
   return m;
 }
 
+// Exclusive scan of one value per thread over a block of up to 1024 threads;
+// `warp_sum` is 32 words of shared memory, *total receives the block's sum.
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_sum,
+                                                         uint32_t* total) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sum[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t w = warp_sum[lane];
+    uint32_t wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    warp_sum[lane] = wi - w;
+    if (lane == 31) *total = wi;
+  }
+  __syncthreads();
+  return warp_sum[warp] + incl - v;
+}
+
 // Streaming (read-once / write-once) accesses: keep them from displacing data
 // that is reused out of L2.
 __device__ __forceinline__ float4 ldcs4(const float* p) {

@@ -71,32 +71,6 @@ slab_count_kernel(const float* __restrict__ x, int64_t n, AetherGrid g, int slab
 // writes the per-destination totals.
 constexpr int kScanBlock = 1024;
 
-__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_sum,
-                                                         uint32_t* total) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  uint32_t incl = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  if (lane == 31) warp_sum[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    const uint32_t w = warp_sum[lane];
-    uint32_t wi = w;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-      if (lane >= o) wi += t;
-    }
-    warp_sum[lane] = wi - w;
-    if (lane == 31) *total = wi;
-  }
-  __syncthreads();
-  return warp_sum[warp] + incl - v;
-}
-
 __global__ void __launch_bounds__(kScanBlock)
 slab_scan_local_kernel(uint32_t* __restrict__ tile_count, int64_t entries,
                        uint32_t* __restrict__ block_sum) {
