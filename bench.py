@@ -78,7 +78,12 @@ class ClockSampler:
             self.file = tempfile.NamedTemporaryFile('w+', suffix='.csv', delete=False)
             self.proc = subprocess.Popen(
                 ['nvidia-smi', f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
-                 '-i', str(self.gpu), '-lms', '100'], stdout=self.file, stderr=subprocess.DEVNULL)
+                 '-i', str(self.gpu), '-lms', '50'], stdout=self.file, stderr=subprocess.DEVNULL)
+            # nvidia-smi takes a moment to start: wait for its first line so that the samples
+            # that follow fall inside the measured regions.
+            deadline = time.time() + 2.0
+            while time.time() < deadline and os.path.getsize(self.file.name) == 0:
+                time.sleep(0.01)
         except Exception:
             self.proc = None
 
@@ -226,7 +231,6 @@ def run_single(args, workload):
         out = step(100 + s)
     end.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
     launches = int(lib.AetherSortKernelLaunches() - launches0)
     ms = begin.elapsed_time(end) / args.steps
     stage_count = lib.AetherSortStageCount()
@@ -270,32 +274,49 @@ def run_single(args, workload):
         crossing = float(((lib_keys >> 7) != before).float().mean())
         del before, lib_keys
     hx, hy, hz, hv = (t.cpu().pin_memory() for t in (x, y, z, v))
-    res_host = None
+    # Two streams: `up` carries a step's host->device copies and its sort, `down` its
+    # device->host copies, so that one step's results travel back while the next step's
+    # inputs travel in (PCIe is full duplex).  Every step still copies all its inputs in and
+    # all its results out inside the timed region; result buffers on the host alternate.
+    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    res_sets = [None, None]
     torch.cuda.synchronize()
 
-    def e2e_step(s):
-        nonlocal res_host
-        dx, dy, dz, dv = (t.to(device, non_blocking=True) for t in (hx, hy, hz, hv))
-        r = pa.sort_and_gather_particles(dx, dy, dz, dv, w.grid, workloads.step_seed(1234, s),
-                                         path=path)
-        outs = [r.order.keys, r.order.particle_index, r.order.cell_counts, r.order.cell_start,
-                *r.positions, r.velocity]
-        if res_host is None:
-            res_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-        for h, o in zip(res_host, outs):
-            h.copy_(o, non_blocking=True)
-        return outs
+    def e2e_step(s, slot):
+        with torch.cuda.stream(up):
+            dx, dy, dz, dv = (t.to(device, non_blocking=True) for t in (hx, hy, hz, hv))
+            r = pa.sort_and_gather_particles(dx, dy, dz, dv, w.grid, workloads.step_seed(1234, s),
+                                             path=path)
+            outs = [r.order.keys, r.order.particle_index, r.order.cell_counts,
+                    r.order.cell_start, *r.positions, r.velocity]
+            sorted_done = torch.cuda.Event()
+            sorted_done.record(up)
+        if res_sets[slot] is None:
+            res_sets[slot] = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        down.wait_event(sorted_done)
+        with torch.cuda.stream(down):
+            for h, o in zip(res_sets[slot], outs):
+                h.copy_(o, non_blocking=True)
+                o.record_stream(down)
 
-    e2e_step(0)
+    e2e_step(0, 0)
+    e2e_step(1, 1)
     torch.cuda.synchronize()
-    begin.record()
+    with torch.cuda.stream(up):
+        begin.record(up)
     for s in range(e2e_steps):
-        outs = e2e_step(200 + s)
-    end.record()
+        e2e_step(200 + s, s % 2)
+    up.wait_stream(down)
+    with torch.cuda.stream(up):
+        end.record(up)
     torch.cuda.synchronize()
     e2e_ms = begin.elapsed_time(end) / e2e_steps
+    clocks = sampler.stop()  # samples span the device-resident and the end-to-end regions
+    res_host = res_sets[(e2e_steps - 1) % 2]
     h2d = sum(t.numel() * t.element_size() for t in (hx, hy, hz, hv))
     d2h = sum(t.numel() * t.element_size() for t in res_host)
+    with torch.cuda.stream(up):
+        assert pa.last_sort_status(device) == 0
 
     # ---- CPU baseline on this box's host cores (rank 0, N = 1 only) + parity ----
     cores = os.cpu_count() or 1
@@ -323,7 +344,8 @@ def run_single(args, workload):
         'clocks': {'sm_mhz': clocks['sm_mhz'], 'sm_max_mhz': clocks['sm_max_mhz'],
                    'reasons': clocks['reasons'], 'samples': clocks['samples']},
         'e2e': {'value': n / (e2e_ms * 1e-3), 'unit': 'particles/s', 'h2d_bytes_per_step': h2d,
-                'd2h_bytes_per_step': d2h, 'ms_per_step': e2e_ms, 'steps': e2e_steps},
+                'd2h_bytes_per_step': d2h, 'ms_per_step': e2e_ms, 'steps': e2e_steps,
+                'overlap': 'results of step k copied out while inputs of step k+1 are copied in'},
         'gpu_launches': launches,
         'roofline': roofline,
         'path_roofline': {'algorithmic_bytes': b_alg, 'achieved_gbs': path_gbs,
