@@ -133,23 +133,24 @@ onesweep_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
                      int shift, const uint32_t* __restrict__ digit_total,
                      uint32_t* __restrict__ status, uint32_t* __restrict__ tile_counter,
-                     int32_t* __restrict__ error, uint32_t poll_limit,
+                     uint32_t tiles, int32_t* __restrict__ error, uint32_t poll_limit,
                      const int32_t* __restrict__ run_if) {
   if (run_if && *run_if == 0) return;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  // Tiles are numbered in the order blocks start, so every tile a block waits
-  // on belongs to a block that is already running.
-  if (tid == 0) {
-    s.tile_id = atomicAdd(tile_counter, 1u);
-    s.abort = 0;
-  }
+  // A block works through tiles until none is left.  Tiles are handed out in
+  // ticket order and a block holds one tile at a time, so every tile a block
+  // waits on belongs to a block that is already running.
+  if (tid == 0) s.abort = 0;
+  for (;;) {
+  if (tid == 0) s.tile_id = atomicAdd(tile_counter, 1u);
 #pragma unroll
   for (int i = lane; i < kRadix; i += 32) s.warp_count[warp][i] = 0;
   __syncthreads();
   const uint32_t tile = s.tile_id;
+  if (tile >= tiles) break;
   const int64_t tile_base = static_cast<int64_t>(tile) * kPassTile;
   const int valid = static_cast<int>(min(static_cast<long long>(kPassTile), static_cast<long long>(n - tile_base)));
 
@@ -279,6 +280,8 @@ onesweep_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     const int64_t dst = s.global_base[(kk >> shift) & (kRadix - 1)] + j;
     keys_out[dst] = kk;
     vals_out[dst] = s.vals[j];
+  }
+  __syncthreads();  // the staged tile and the ticket slot are reused by the next tile
   }
 }
 
@@ -515,19 +518,19 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
     count_launches(1);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
+    const int pass_grid = static_cast<int>(std::min<int64_t>(l.tiles, kSmCount * 2));
     for (int p = 0; p < l.passes; ++p) {
       uint32_t* st = status + static_cast<size_t>(p) * l.tiles * kRadix;
       stage_begin(static_cast<Stage>(kStagePass0 + p), a.stream);
       if (p == 0)
-        onesweep_pass_kernel<true><<<static_cast<int>(l.tiles), kPassThreads, sizeof(PassSmem),
-                                     a.stream>>>(cur_k, nullptr, nxt_k, nxt_v, a.n, 0,
-                                                 hdr->digit_hist[0], st, &hdr->tile_counter[0],
-                                                 &hdr->error, kPollLimit, run_if);
+        onesweep_pass_kernel<true><<<pass_grid, kPassThreads, sizeof(PassSmem), a.stream>>>(
+            cur_k, nullptr, nxt_k, nxt_v, a.n, 0, hdr->digit_hist[0], st, &hdr->tile_counter[0],
+            static_cast<uint32_t>(l.tiles), &hdr->error, kPollLimit, run_if);
       else
-        onesweep_pass_kernel<false><<<static_cast<int>(l.tiles), kPassThreads, sizeof(PassSmem),
-                                      a.stream>>>(cur_k, cur_v, nxt_k, nxt_v, a.n, kRadixBits * p,
-                                                  hdr->digit_hist[p], st, &hdr->tile_counter[p],
-                                                  &hdr->error, kPollLimit, run_if);
+        onesweep_pass_kernel<false><<<pass_grid, kPassThreads, sizeof(PassSmem), a.stream>>>(
+            cur_k, cur_v, nxt_k, nxt_v, a.n, kRadixBits * p, hdr->digit_hist[p], st,
+            &hdr->tile_counter[p], static_cast<uint32_t>(l.tiles), &hdr->error, kPollLimit,
+            run_if);
       stage_end(static_cast<Stage>(kStagePass0 + p), a.stream);
       count_launches(1);
       e = cudaGetLastError();
