@@ -39,9 +39,12 @@ int run_sort(SortArgs& a, int path) {
   a.num_cells = static_cast<int64_t>(a.grid.nx_local) * a.grid.ny * a.grid.nz;
   a.key_bits = key_bits_of(a.num_cells);
   stage_reset();
-  // The bucketed path carries the payload; without one the digit passes run.
+  // path 1 asks for the digit passes; otherwise the bucketed path runs whenever its plan fits
+  // (with or without payload outputs) and the workspace is large enough for its records.  A
+  // keys-only caller with a small workspace (the static-scratch entry point) gets the digit passes.
   const BucketPlan plan = plan_buckets(a.n, a.num_cells);
-  const bool bucketed = a.xs != nullptr && plan.usable && path != 1;
+  const bool roomy = a.workspace_bytes >= bucketed_workspace_bytes(a.n, a.num_cells);
+  const bool bucketed = plan.usable && path != 1 && (roomy || a.xs != nullptr || path == 2);
   if (path == 2 && !bucketed) return cudaErrorInvalidValue;
   if (!bucketed) return standard_sort(a, nullptr);
   cudaError_t e = bucketed_sort(a, plan);
@@ -137,9 +140,8 @@ extern "C" int AetherSortAbiVersion(void) { return 1; }
 
 extern "C" size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload) {
   if (!count_ok(n) || num_cells <= 0 || key_bits_of(num_cells) > 32) return 0;
-  const size_t standard = standard_workspace_bytes(n, num_cells);
-  if (!with_payload) return standard;
-  return std::max(standard, bucketed_workspace_bytes(n, num_cells));
+  (void)with_payload;  // both forms use the same workspace
+  return std::max(standard_workspace_bytes(n, num_cells), bucketed_workspace_bytes(n, num_cells));
 }
 
 extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const float* z,
@@ -154,7 +156,7 @@ extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const f
   a.cell_counts = cell_counts; a.cell_start = cell_start;
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
-  return run_sort(a, 1);
+  return run_sort(a, 0);
 }
 
 extern "C" int AetherSortAndGatherParticles(

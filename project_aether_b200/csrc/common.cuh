@@ -103,6 +103,28 @@ __device__ __forceinline__ uint32_t lanemask_lt() {
   return m;
 }
 
+// Adds one to a histogram bin per lane.  Lanes hitting the same bin share one add
+// when the whole warp agrees, or (through match.any) when neighbouring lanes do.
+__device__ __forceinline__ void bin_add(uint32_t* hist, uint32_t bin, bool valid) {
+  const uint32_t active = __ballot_sync(0xffffffffu, valid);
+  if (active == 0) return;
+  const int first = __ffs(active) - 1;
+  const uint32_t first_bin = __shfl_sync(0xffffffffu, bin, first);
+  const bool uniform = __all_sync(0xffffffffu, !valid || bin == first_bin);
+  if (uniform) {
+    if (static_cast<int>(lane_id()) == first) atomicAdd(&hist[first_bin], __popc(active));
+    return;
+  }
+  const uint32_t next_bin = __shfl_down_sync(0xffffffffu, bin, 1);
+  const bool clustered = __any_sync(0xffffffffu, valid && lane_id() < 31 && next_bin == bin);
+  if (clustered) {
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? bin : 0xffffffffu) & active;
+    if (valid && (peers & lanemask_lt()) == 0) atomicAdd(&hist[bin], __popc(peers));
+  } else if (valid) {
+    atomicAdd(&hist[bin], 1u);
+  }
+}
+
 // Exclusive scan of one value per thread over a block of up to 1024 threads;
 // `warp_sum` is 32 words of shared memory, *total receives the block's sum.
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_sum,

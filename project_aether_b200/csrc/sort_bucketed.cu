@@ -47,29 +47,6 @@ constexpr int kRecordWords = 8;  // 32-byte record
 // ------------------------------------------------------------------------
 constexpr int kCountThreads = 512;
 
-// Adds one to a histogram bin per lane.  Lanes hitting the same bin share one add
-// when the whole warp agrees, or (through match.any) when neighbouring lanes do.
-template <bool SHARED>
-__device__ __forceinline__ void bin_add(uint32_t* hist, uint32_t bin, bool valid) {
-  const uint32_t active = __ballot_sync(0xffffffffu, valid);
-  if (active == 0) return;
-  const int first = __ffs(active) - 1;
-  const uint32_t first_bin = __shfl_sync(0xffffffffu, bin, first);
-  const bool uniform = __all_sync(0xffffffffu, !valid || bin == first_bin);
-  if (uniform) {
-    if (static_cast<int>(lane_id()) == first) atomicAdd(&hist[first_bin], __popc(active));
-    return;
-  }
-  const uint32_t next_bin = __shfl_down_sync(0xffffffffu, bin, 1);
-  const bool clustered = __any_sync(0xffffffffu, valid && lane_id() < 31 && next_bin == bin);
-  if (clustered) {
-    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? bin : 0xffffffffu) & active;
-    if (valid && (peers & lanemask_lt()) == 0) atomicAdd(&hist[bin], __popc(peers));
-  } else if (valid) {
-    atomicAdd(&hist[bin], 1u);
-  }
-}
-
 constexpr int kChunkLog = 22;      // particles per chunk of the record layout (2^22; 2^21, 2^23
                                    // and 2^24 measured slower end to end) ...
 constexpr int kNoChunkLog = 31;    // ... or one chunk for everything
@@ -117,7 +94,7 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        bin_add<SHARED>(target, cell_of(px[k], py[k], pz[k], g) >> shift, i0 + k < last);
+        bin_add(target, cell_of(px[k], py[k], pz[k], g) >> shift, i0 + k < last);
     }
     if (SHARED) {
       __syncthreads();
@@ -661,9 +638,11 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       const size_t o = static_cast<size_t>(begin) + d;
       __stcs(keys_out + o, a.x);
       __stcs(index_out + o, static_cast<int32_t>(a.y));
-      __stcs(xs + o, __uint_as_float(a.z));
-      __stcs(ys + o, __uint_as_float(a.w));
-      __stcs(zs + o, __uint_as_float(c.x));
+      if (xs) {  // keys-only calls leave the payload out
+        __stcs(xs + o, __uint_as_float(a.z));
+        __stcs(ys + o, __uint_as_float(a.w));
+        __stcs(zs + o, __uint_as_float(c.x));
+      }
       if (vs) {
         __stcs(vs + o, __uint_as_float(c.y));
         __stcs(vs + padded_sorted + o, __uint_as_float(c.z));

@@ -27,14 +27,6 @@ constexpr int kKeygenThreads = 256;
 constexpr int kKeygenVec = 4;
 constexpr int kKeygenChunk = kKeygenThreads * kKeygenVec;
 
-// Adds one digit to a shared histogram with one atomic per distinct digit of
-// the warp, so that a warp whose keys all share a digit (every particle in one
-// cell) costs one atomic, not 32 serialised ones.
-__device__ __forceinline__ void hist_add(uint32_t* h, uint32_t digit, bool valid) {
-  const uint32_t peers = __match_any_sync(0xffffffffu, valid ? digit : 0xffffffffu);
-  if (valid && (peers & lanemask_lt()) == 0) atomicAdd(&h[digit], __popc(peers));
-}
-
 template <int PASSES, bool VEC>
 __global__ void __launch_bounds__(kKeygenThreads)
 keygen_upsweep_kernel(const float* __restrict__ x, const float* __restrict__ y,
@@ -79,7 +71,7 @@ keygen_upsweep_kernel(const float* __restrict__ x, const float* __restrict__ y,
       const bool ok = i0 + k < n;
 #pragma unroll
       for (int p = 0; p < PASSES; ++p)
-        hist_add(hist[p], (key[k] >> (kRadixBits * p)) & (kRadix - 1), ok);
+        bin_add(hist[p], (key[k] >> (kRadixBits * p)) & (kRadix - 1), ok);
     }
   }
   __syncthreads();
