@@ -144,6 +144,7 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   __shared__ unsigned long long warp_lo[8], warp_hi[8];
   __shared__ uint32_t local_base[kMaxWorld + 1];  // start of each destination's run in the tile
   __shared__ uint32_t out_base[kMaxWorld];        // start of that run in the output arrays
+  __shared__ int run_head[kMaxWorld], run_quads[kMaxWorld];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t tile_first = static_cast<int64_t>(blockIdx.x) * kSlabTile;
   const int64_t i0 = tile_first + static_cast<int64_t>(tid) * kSlabItems;
@@ -226,23 +227,46 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   __syncthreads();
   // Write every destination's run: 16-byte stores over the part of the run whose
   // destination is 16-byte aligned (longer NVLink and HBM bursts), scalar stores for
-  // the up to three elements before and after it.
-  for (int d = 0; d < world; ++d) {
-    if (out_base[d] == 0xffffffffu) continue;
-    const int lb = static_cast<int>(local_base[d]), le = static_cast<int>(local_base[d + 1]);
-    if (le <= lb) continue;
-    const size_t g0 = out_base[d];
-    const int head = tg.aligned ? min(le - lb, static_cast<int>((4 - (g0 & 3)) & 3)) : le - lb;
-    const int quads = (le - lb - head) / 4;
-    const int tail_first = lb + head + 4 * quads;
-    for (int q = tid; q < quads; q += kSlabThreads) {
-      const int j = lb + head + 4 * q;
-      const size_t o = g0 + (j - lb);
-#pragma unroll
-      for (int c = 0; c < 6; ++c)
-        *reinterpret_cast<float4*>(tg.array[d][c] + o) =
-            make_float4(stage[c][j], stage[c][j + 1], stage[c][j + 2], stage[c][j + 3]);
+  // the up to three elements before and after it.  The quads of all destinations
+  // form one list that the block's threads share, so that short runs (eight
+  // destinations) keep every thread storing.
+  if (tid < world) {
+    const int lb = static_cast<int>(local_base[tid]), le = static_cast<int>(local_base[tid + 1]);
+    int head = 0, quads = 0;
+    if (out_base[tid] != 0xffffffffu && le > lb) {
+      head = tg.aligned ? min(le - lb, static_cast<int>((4 - (out_base[tid] & 3)) & 3)) : le - lb;
+      quads = (le - lb - head) / 4;
+    } else if (out_base[tid] == 0xffffffffu) {
+      head = -1;  // nothing of this run is written
     }
+    run_head[tid] = head;
+    run_quads[tid] = quads;
+  }
+  __syncthreads();
+  int quad_first[kMaxWorld + 1];
+  quad_first[0] = 0;
+#pragma unroll
+  for (int d = 0; d < kMaxWorld; ++d) quad_first[d + 1] = quad_first[d] + (d < world ? run_quads[d] : 0);
+  for (int q = tid; q < quad_first[kMaxWorld]; q += kSlabThreads) {
+    int d = 0;
+#pragma unroll
+    for (int w = 1; w < kMaxWorld; ++w) d += q >= quad_first[w];
+    const int lb = static_cast<int>(local_base[d]);
+    const int j = lb + run_head[d] + 4 * (q - quad_first[d]);
+    const size_t o = static_cast<size_t>(out_base[d]) + (j - lb);
+#pragma unroll
+    for (int c = 0; c < 6; ++c)
+      *reinterpret_cast<float4*>(tg.array[d][c] + o) =
+          make_float4(stage[c][j], stage[c][j + 1], stage[c][j + 2], stage[c][j + 3]);
+  }
+  // Heads and tails: at most three elements each per destination when aligned;
+  // the whole run when the buffers are not 16-byte aligned.
+  for (int d = 0; d < world; ++d) {
+    const int head = run_head[d];
+    if (head < 0) continue;
+    const int lb = static_cast<int>(local_base[d]), le = static_cast<int>(local_base[d + 1]);
+    const size_t g0 = out_base[d];
+    const int tail_first = lb + head + 4 * run_quads[d];
     for (int i = tid; i < head; i += kSlabThreads) {
 #pragma unroll
       for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + i] = stage[c][lb + i];

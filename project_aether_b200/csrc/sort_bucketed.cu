@@ -45,7 +45,8 @@ constexpr int kRecordWords = 8;  // 32-byte record
 // ------------------------------------------------------------------------
 // Upsweep: particles per bucket.
 // ------------------------------------------------------------------------
-constexpr int kCountThreads = 512;
+constexpr int kCountThreads = 512;       // blocks that share an SM (table up to 96 KB)
+constexpr int kCountThreadsWide = 1024;  // one block per SM (table up to 200 KB)
 
 constexpr int kChunkLog = 22;      // particles per chunk of the record layout (2^22; 2^21, 2^23
                                    // and 2^24 measured slower end to end) ...
@@ -54,8 +55,8 @@ constexpr int kNoChunkLog = 31;    // ... or one chunk for everything
 // Work unit = one slice of one chunk; a block counts the slice into a table
 // (shared memory, or the global counts directly when the table does not fit)
 // and adds the table to the chunk's row of counts, count[chunk * buckets + b].
-template <bool SHARED, bool VEC>
-__global__ void __launch_bounds__(kCountThreads)
+template <bool SHARED, bool VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, int64_t n, AetherGrid g, int shift,
                     int buckets, int chunks, int chunk_log, int parts, int64_t slice,
@@ -65,7 +66,7 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
     const int chunk = unit / parts, part = unit % parts;
     uint32_t* row = bucket_count + static_cast<size_t>(chunk) * buckets;
     if (SHARED) {
-      for (int i = threadIdx.x; i < buckets; i += kCountThreads) hist[i] = 0;
+      for (int i = threadIdx.x; i < buckets; i += THREADS) hist[i] = 0;
       __syncthreads();
     }
     uint32_t* target = SHARED ? hist : row;
@@ -74,9 +75,9 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
                                    static_cast<long long>(chunk_first + (int64_t{1} << chunk_log)));
     const int64_t first = chunk_first + part * slice;
     const int64_t last = min(static_cast<long long>(chunk_last), static_cast<long long>(first + slice));
-    const int64_t rounds = first < last ? (last - first + kCountThreads * 4 - 1) / (kCountThreads * 4) : 0;
+    const int64_t rounds = first < last ? (last - first + THREADS * 4 - 1) / (THREADS * 4) : 0;
     for (int64_t r = 0; r < rounds; ++r) {
-      const int64_t i0 = first + (r * kCountThreads + threadIdx.x) * 4;
+      const int64_t i0 = first + (r * THREADS + threadIdx.x) * 4;
       float px[4], py[4], pz[4];
       if (VEC && i0 + 4 <= last) {
         const float4 a = ldcs4(x + i0), b = ldcs4(y + i0), c = ldcs4(z + i0);
@@ -98,7 +99,7 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
     }
     if (SHARED) {
       __syncthreads();
-      for (int i = threadIdx.x; i < buckets; i += kCountThreads)
+      for (int i = threadIdx.x; i < buckets; i += THREADS)
         if (hist[i]) atomicAdd(&row[i], hist[i]);
       __syncthreads();
     }
@@ -339,7 +340,8 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 constexpr int kFinishThreads = 1024;
 constexpr int kFinishCapacity = 5376;                      // records per bucket
 constexpr int kFinishItems = (kFinishCapacity + kFinishThreads - 1) / kFinishThreads;  // 6
-constexpr int kMaxLowBits = 15;                            // (cell bits in bucket) + 7
+constexpr int kMaxLowBits = 15;                            // bits the counters resolve
+constexpr int kMaxShift = 10;                              // bucket = up to 1024 cells
 constexpr int kHistWords = (1 << kMaxLowBits) / 4;         // byte counters, 4 per word
 constexpr int kWordsPerThread = kHistWords / kFinishThreads;  // 8
 constexpr uint32_t kBulkChunkBytes = 32768;                // bytes per bulk copy
@@ -405,9 +407,15 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FinishSmem& s = *reinterpret_cast<FinishSmem*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // The key bits below the bucket id: shift cell bits and the 7 shuffle bits.  The
+  // counters resolve the upper 15 of them; up to two lowest bits (buckets of 512 or
+  // 1024 cells) are left to the tie step, which orders by (those bits, index).
   const int low_bits = shift + kShuffleBits;
   const uint32_t low_mask = (1u << low_bits) - 1;
-  const int hist_words = max(1, (1 << low_bits) / 4);
+  const int drop = max(0, low_bits - kMaxLowBits);
+  const uint32_t drop_mask = (1u << drop) - 1;
+  const int hist_words = max(1, (1 << (low_bits - drop)) / 4);
+  const int cell_words = 32 >> drop;  // counter words per cell
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s.barrier)) : "memory");
@@ -509,7 +517,7 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       const int r = tid + k * kFinishThreads;
       packed[k] = 0;
       if (r < count) {
-        const uint32_t low = s.raw[r * kRecordWords] & low_mask;
+        const uint32_t low = (s.raw[r * kRecordWords] & low_mask) >> drop;
         const int sh = 8 * (low & 3);
         const uint32_t old = atomicAdd(&s.hist[low >> 2], 1u << sh);
         packed[k] = low | (((old >> sh) & 0xffu) << 16);
@@ -571,15 +579,15 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       continue;
     }
 
-    // Cell tables of this bucket: every cell is 128 consecutive counters.
+    // Cell tables of this bucket: every cell is 128 >> drop consecutive counters.
     {
       const int64_t first_cell = static_cast<int64_t>(b) << shift;
       const int cells_here = static_cast<int>(
           min(static_cast<long long>(1) << shift, static_cast<long long>(num_cells - first_cell)));
       for (int c = tid; c < cells_here; c += kFinishThreads) {
-        const uint32_t lo = s.word_prefix[c * 32];
-        const uint32_t hi = (c + 1) * 32 < hist_words ? s.word_prefix[(c + 1) * 32]
-                                                       : static_cast<uint32_t>(count);
+        const uint32_t lo = s.word_prefix[c * cell_words];
+        const uint32_t hi = (c + 1) * cell_words < hist_words ? s.word_prefix[(c + 1) * cell_words]
+                                                               : static_cast<uint32_t>(count);
         cell_start[first_cell + c] = static_cast<int32_t>(begin + lo);
         cell_counts[first_cell + c] = static_cast<int32_t>(hi - lo);
       }
@@ -605,8 +613,10 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
     }
     __syncthreads();
 
-    // Equal keys must appear in ascending original index: a record inside a run
-    // of equal keys moves to (run start + number of smaller indices in the run).
+    // Records that share a counter must appear in ascending (dropped key bits,
+    // original index): a record inside such a run moves to (run start + number of
+    // smaller records in the run).  Indices stay below 2^30, so the dropped bits
+    // ride above them in one word.
     uint32_t moved[kFinishItems];
 #pragma unroll
     for (int k = 0; k < kFinishItems; ++k) {
@@ -614,10 +624,12 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       if (run[k]) {
         const int r = tid + k * kFinishThreads;
         const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
-        const uint32_t mine = s.raw[r * kRecordWords + 1];
+        const uint32_t mine = ((s.raw[r * kRecordWords] & drop_mask) << 30) | s.raw[r * kRecordWords + 1];
         uint32_t smaller = 0;
-        for (uint32_t j = 0; j < length; ++j)
-          smaller += s.raw[s.order[start + j] * kRecordWords + 1] < mine;
+        for (uint32_t j = 0; j < length; ++j) {
+          const uint32_t* other = &s.raw[s.order[start + j] * kRecordWords];
+          smaller += (((other[0] & drop_mask) << 30) | other[1]) < mine;
+        }
         moved[k] = start + smaller;
       }
     }
@@ -694,14 +706,16 @@ BucketLayout bucket_layout(int64_t n, int64_t buckets) {
 }  // namespace
 
 BucketPlan plan_buckets(int64_t n, int64_t num_cells) {
-  // Largest bucket width 2^s (s <= 8 so the low key fits 15 bits) whose average
-  // load stays at or below the target.
+  // Largest bucket width 2^s (s <= 10: the counters of the finish kernel resolve 15
+  // low key bits and its tie step two more) whose average load stays at or below the
+  // target.
   BucketPlan p;
   p.shift = 0;
   const int64_t target = 4224;
-  for (int s = 8; s >= 0; --s) {
+  for (int s = kMaxShift; s >= 0; --s) {
     const int64_t buckets = (num_cells + (int64_t{1} << s) - 1) >> s;
-    if (n <= target * buckets || s == 0) {
+    // Fewer than 1024 buckets make the slot counters of the scatter contend.
+    if ((n <= target * buckets && buckets >= 1024) || s == 0) {
       p.shift = s;
       break;
     }
@@ -741,29 +755,35 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
 
   stage_begin(kStageBucketCount, a.stream);
   {
-    const bool shared = table_bytes <= 96 * 1024;
-    const int blocks_per_sm = shared ? (table_bytes <= 48 * 1024 ? 4 : 2) : 4;
+    const bool shared = table_bytes <= 200 * 1024;
+    const bool wide = table_bytes > 96 * 1024;  // one 1024-thread block per SM holds the table
+    const int threads = shared && wide ? kCountThreadsWide : kCountThreads;
+    const int blocks_per_sm = shared ? (wide ? 1 : table_bytes <= 48 * 1024 ? 4 : 2) : 4;
     const int64_t chunk_size = int64_t{1} << l.chunk_log;
     const int64_t covered = std::min<int64_t>(a.n, chunk_size);
     // Slices of a chunk: enough units to fill the GPU twice over, each a multiple of one
-    // block round (2048 particles) so that the 16-byte loads stay aligned.
+    // block round (4 particles per thread) so that the 16-byte loads stay aligned.
     const int want = std::max(1, kSmCount * blocks_per_sm * 2 / l.chunks);
-    const int64_t round = kCountThreads * 4;
+    const int64_t round = threads * 4;
     const int64_t slice = std::max<int64_t>(round, ((covered + want - 1) / want + round - 1) / round * round);
     const int parts = static_cast<int>((covered + slice - 1) / slice);
     const int grid = std::max(1, std::min(l.chunks * parts, kSmCount * blocks_per_sm));
     if (shared) {
-      auto kernel = vec ? bucket_count_kernel<true, true> : bucket_count_kernel<true, false>;
+      auto kernel = wide ? (vec ? bucket_count_kernel<true, true, kCountThreadsWide>
+                                : bucket_count_kernel<true, false, kCountThreadsWide>)
+                         : (vec ? bucket_count_kernel<true, true, kCountThreads>
+                                : bucket_count_kernel<true, false, kCountThreads>);
       e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(table_bytes));
       if (e != cudaSuccess) return e;
-      kernel<<<grid, kCountThreads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift,
-                                                             buckets, l.chunks, l.chunk_log, parts,
-                                                             slice, count);
+      kernel<<<grid, threads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift,
+                                                       buckets, l.chunks, l.chunk_log, parts,
+                                                       slice, count);
     } else {
-      auto kernel = vec ? bucket_count_kernel<false, true> : bucket_count_kernel<false, false>;
-      kernel<<<grid, kCountThreads, 0, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift, buckets,
-                                                    l.chunks, l.chunk_log, parts, slice, count);
+      auto kernel = vec ? bucket_count_kernel<false, true, kCountThreads>
+                        : bucket_count_kernel<false, false, kCountThreads>;
+      kernel<<<grid, threads, 0, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift, buckets,
+                                             l.chunks, l.chunk_log, parts, slice, count);
     }
   }
   stage_end(kStageBucketCount, a.stream);
