@@ -85,6 +85,7 @@ def run(args, workload: str) -> None:
     e2e_steps = max(1, min(args.steps, 3))
     hx, hy, hz, hv = (t.cpu().pin_memory() for t in (x, y, z, v))
     d2h = [0]
+    pinned = {}
 
     def e2e_step(s):
         dx, dy, dz, dv = (t.to(device, non_blocking=True) for t in (hx, hy, hz, hv))
@@ -92,8 +93,12 @@ def run(args, workload: str) -> None:
                                        exchange=exchange)
         outs = [r.order.keys, r.order.particle_index, r.order.cell_counts, r.order.cell_start,
                 *r.positions, r.velocity]
-        host = [o.to('cpu', non_blocking=False) for o in outs]
-        d2h[0] = sum(h.numel() * h.element_size() for h in host)
+        for i, o in enumerate(outs):  # pinned result buffers, kept across steps
+            if i not in pinned or pinned[i].shape != o.shape:
+                pinned[i] = torch.empty(o.shape, dtype=o.dtype, pin_memory=True)
+            pinned[i].copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        d2h[0] = sum(o.numel() * o.element_size() for o in outs)
 
     e2e_step(0)
     dist.barrier()
@@ -135,7 +140,11 @@ def run(args, workload: str) -> None:
         top = max(stages, key=stages.get) if stages else None
         roofline = None
         if top:
-            per_particle = bench_mod.STAGE_BYTES_PER_PARTICLE.get(top, 48 if top == 'slab_partition' else 0)
+            # The exchange kernel reads 24 B per particle and stores 24 B, (G-1)/G of them into
+            # the peers' memory: NVLink bounds it, so its line also carries the crossing bytes
+            # against the peer-copy bandwidth measured on this pool (770 GB/s per direction).
+            per_particle = bench_mod.STAGE_BYTES_PER_PARTICLE.get(
+                top, 48 if top in ('slab_partition', 'slab_exchange') else 0)
             nbytes = per_particle * n_rank
             achieved = nbytes / (stages[top] * 1e-3) / 1e9
             roofline = {'bound': 'hbm', 'kernel': top, 'achieved': achieved, 'peak': peak,
@@ -143,6 +152,12 @@ def run(args, workload: str) -> None:
                         'traffic': (bench_mod.NCU_DRAM_BYTES_PER_PARTICLE[top] * n_rank
                                     if top in bench_mod.NCU_DRAM_BYTES_PER_PARTICLE else None),
                         'bytes_per_launch': nbytes, 'ms_per_launch': stages[top]}
+            if top == 'slab_exchange' and exchange == 'peer':
+                crossing = 24 * n_rank * (world - 1) / world
+                link = crossing / (stages[top] * 1e-3) / 1e9
+                roofline['nvlink'] = {'bytes_out_per_gpu': crossing, 'achieved': link,
+                                      'peak': 770.0, 'unit': 'GB/s', 'frac': link / 770.0,
+                                      'peak_kind': 'peer copy measured on this pool'}
         line = {
             'metric': 'sorted particles/s', 'value': n_total / (ms * 1e-3), 'unit': 'particles/s',
             'n_gpus': world, 'steps': args.steps, 'warmup': warmup, 'ms_per_step': ms,
