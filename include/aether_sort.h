@@ -140,6 +140,25 @@ int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
 int AetherParticlePush(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
                        float dt, const float* lo, const float* hi, void* stream);
 
+/* The stage that follows the sort in the DSMC step: No-Time-Counter collisions
+ * on the cell-sorted velocities, in place.  Name, arguments and return value are
+ * those of the reference's entry point, so its ctypes binding loads this library
+ * unchanged (project_aether/src/custom_kernels/cuda/dsmc_collide_tma.h:121-129,
+ * bound in project_aether/src/custom_kernels/cuda/tma_collide.py:67-78); the
+ * kernel behind it is written for sm_100a and uses no tensor map.
+ *   velocity     (3, padded_particles) floats, rows vx, vy, vz, cell-sorted, updated in place;
+ *                padded_particles is a multiple of 4
+ *   cell_start   (num_cells + 1) exclusive prefix of the cell counts
+ *   sigma_g_max  (num_cells) majorant of sigma_T * g per cell, raised to the largest value seen
+ *   collisions   (num_cells) receives the accepted pairs of every cell
+ * The candidate pairs of a cell are (start + 2j, start + 1 + 2j): the sort's shuffle
+ * bits have already randomised the order inside a cell.  Pair arithmetic follows
+ * dsmc_collide_tma.h:59-113. */
+int AetherDsmcCollideTma(float* velocity, const int* cell_start, float* sigma_g_max,
+                         int* collisions, int num_particles, int padded_particles, int num_cells,
+                         float selection_factor, float vhs_coefficient, float vhs_speed_exponent,
+                         uint64_t seed, uint64_t step, void* stream);
+
 /* The same sort for callers that cannot allocate device memory: a plugin that
  * runs inside a host application which has already handed all of the GPU's
  * memory to its own pool, or a step of a real-time loop in which cudaMalloc

@@ -52,6 +52,8 @@ _SIGNATURES = {
     'AetherParticlePush': (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _I64, ctypes.c_float,
                                           ctypes.POINTER(ctypes.c_float),
                                           ctypes.POINTER(ctypes.c_float), _P]),
+    'AetherDsmcCollideTma': (ctypes.c_int, [_P] * 4 + [ctypes.c_int] * 3 + [ctypes.c_float] * 3 +
+                             [ctypes.c_uint64] * 2 + [_P]),
     'AetherSortStaticMaxParticles': (ctypes.c_int64, []),
     'AetherSortParticlesByCellStatic': (ctypes.c_int, [_P, _P, _P, _I64,
                                                        ctypes.POINTER(AetherGrid),

@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, 'csrc')
 LIB = os.path.join(PKG, 'libaether_sort.so')
 SOURCES = ['api.cu', 'sort_standard.cu', 'sort_bucketed.cu', 'slab_partition.cu', 'particle_push.cu',
-           'static_scratch.cu']
+           'static_scratch.cu', 'collide.cu']
 NVCC_FLAGS = [
     '-O3', '-std=c++17', '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo',
     '-Xcompiler', '-fPIC', '-shared', '--use_fast_math=false',

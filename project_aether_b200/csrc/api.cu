@@ -72,7 +72,7 @@ uint64_t g_launches = 0;
 const char* const kStageNames[kNumStages] = {
     "keygen_upsweep", "digit_pass_0", "digit_pass_1", "digit_pass_2", "digit_pass_3",
     "cell_tables", "payload_gather", "bucket_count", "bucket_scan", "bucket_scatter",
-    "bucket_finish", "slab_partition", "particle_push", "slab_exchange"};
+    "bucket_finish", "slab_partition", "particle_push", "slab_exchange", "collide"};
 }  // namespace
 
 void stage_reset() {
@@ -240,6 +240,16 @@ extern "C" int AetherParticlePush(float* x, float* y, float* z, float* vx, float
   if (!count_ok(n) || !lo || !hi) return cudaErrorInvalidValue;
   if (n > 0 && (!x || !y || !z || !vx || !vy || !vz)) return cudaErrorInvalidValue;
   return particle_push(x, y, z, vx, vy, vz, n, dt, lo, hi, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int AetherDsmcCollideTma(float* velocity, const int* cell_start, float* sigma_g_max,
+                                    int* collisions, int num_particles, int padded_particles,
+                                    int num_cells, float selection_factor, float vhs_coefficient,
+                                    float vhs_speed_exponent, uint64_t seed, uint64_t step,
+                                    void* stream) {
+  return collide_cells(velocity, cell_start, sigma_g_max, collisions, num_particles,
+                       padded_particles, num_cells, selection_factor, vhs_coefficient,
+                       vhs_speed_exponent, seed, step, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int AetherSlabExchangeCount(const float* x, int64_t n, const AetherGrid* grid, int world,

@@ -139,7 +139,7 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* w
   if (lane == 31) warp_sum[warp] = incl;
   __syncthreads();
   if (warp == 0) {
-    const uint32_t w = warp_sum[lane];
+    const uint32_t w = lane < static_cast<int>((blockDim.x + 31) >> 5) ? warp_sum[lane] : 0u;
     uint32_t wi = w;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -163,7 +163,7 @@ __device__ __forceinline__ float4 ldcs4(const float* p) {
 enum Stage {
   kStageKeygen = 0, kStagePass0, kStagePass1, kStagePass2, kStagePass3, kStageCellTables,
   kStageGather, kStageBucketCount, kStageBucketScan, kStageBucketScatter, kStageBucketFinish,
-  kStageSlabPartition, kStagePush, kStageSlabExchange, kNumStages
+  kStageSlabPartition, kStagePush, kStageSlabExchange, kStageCollide, kNumStages
 };
 void stage_begin(Stage s, cudaStream_t stream);
 void stage_end(Stage s, cudaStream_t stream);
@@ -231,5 +231,9 @@ cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z
                                   size_t workspace_bytes, cudaStream_t stream);
 cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
                           float dt, const float* lo, const float* hi, cudaStream_t stream);
+cudaError_t collide_cells(float* velocity, const int* cell_start, float* sigma_g_max,
+                          int* collisions, int num_particles, int padded, int num_cells,
+                          float selection_factor, float coefficient, float exponent,
+                          uint64_t seed, uint64_t step, cudaStream_t stream);
 
 }  // namespace aether

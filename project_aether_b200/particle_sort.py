@@ -143,7 +143,8 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
                               velocity: torch.Tensor, grid: CellGrid, seed: int, *,
                               ix_offset: int = 0, nx_local: Optional[int] = None,
                               path: int = PATH_AUTO,
-                              padded_out: Optional[int] = None) -> SortedParticles:
+                              padded_out: Optional[int] = None,
+                              out: Optional[SortedParticles] = None) -> SortedParticles:
     """Sorts by cell and returns the particle payload in sorted order.
 
     One call for lines 105-109 of the reference's DSMC step
@@ -157,6 +158,8 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
       grid, seed, ix_offset, nx_local: as in `sort_particles_by_cell`.
       path: PATH_AUTO, PATH_DIGIT_PASSES or PATH_BUCKETED (same results).
       padded_out: row stride of the sorted velocity (default: that of the input).
+      out: result tensors of an earlier call with the same sizes to write into
+        instead of allocating (a stepping loop alternates between two sets).
 
     Returns:
       SortedParticles(order, (x, y, z) sorted, velocity sorted (3, padded) with
@@ -177,15 +180,22 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
     cells = g.nx_local * g.ny * g.nz
     num_passes(cells)
     with torch.cuda.device(device):
-        keys = torch.empty(n, dtype=torch.int32, device=device)
-        index = torch.empty(n, dtype=torch.int32, device=device)
-        counts = torch.empty(cells, dtype=torch.int32, device=device)
-        start = torch.empty(cells + 1, dtype=torch.int32, device=device)
-        xs, ys, zs = (torch.empty(n, dtype=torch.float32, device=device) for _ in range(3))
         padded_sorted = padded if padded_out is None else int(padded_out)
         if padded_sorted < n:
             raise ValueError('padded_out must be at least the number of particles.')
-        vs = torch.empty((3, padded_sorted), dtype=torch.float32, device=device)
+        if out is not None:
+            (keys, index, counts, start), (xs, ys, zs), vs = out
+            if (keys.numel() != n or index.numel() != n or counts.numel() != cells
+                    or start.numel() != cells + 1 or any(t.numel() != n for t in (xs, ys, zs))
+                    or tuple(vs.shape) != (3, padded_sorted) or vs.device != device):
+                raise ValueError('`out` does not match the sizes of this call.')
+        else:
+            keys = torch.empty(n, dtype=torch.int32, device=device)
+            index = torch.empty(n, dtype=torch.int32, device=device)
+            counts = torch.empty(cells, dtype=torch.int32, device=device)
+            start = torch.empty(cells + 1, dtype=torch.int32, device=device)
+            xs, ys, zs = (torch.empty(n, dtype=torch.float32, device=device) for _ in range(3))
+            vs = torch.empty((3, padded_sorted), dtype=torch.float32, device=device)
         if padded_sorted > n:
             vs[:, n:].zero_()
         nbytes = lib.AetherSortWorkspaceBytes(n, cells, 1)

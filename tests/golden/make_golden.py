@@ -133,6 +133,56 @@ def triton_fixture(ref_root):
     np.savez_compressed(os.path.join(HERE, 'triton_interp.npz'), **cases)
 
 
+def collide_fixture():
+    """Runs the reference's own inline collision functions (harness oracle/_ref/collide_ref,
+    built from dsmc_collide_tma.h) on small seeded cases and stores inputs and outputs."""
+    import tempfile
+    sys.path.insert(0, ROOT)
+    from oracle import collide_oracle
+    exe = os.path.join(ROOT, 'oracle', '_ref', 'collide_ref')
+    rng = np.random.default_rng(7)
+    specs = {
+        # Poisson occupancy with an oversized cell, as dsmc_collide_tma_test.cu:86-96 (smaller).
+        # The selection factor of that test (2e-17) selects no pair at all with its majorant
+        # (expected pairs per cell 2.7e-28); these cases use factors that select some.
+        'poisson_300': dict(counts=np.r_[rng.poisson(300.0, 20), 3000], rng_seed=1,
+                            selection_factor=2.0e12),
+        # DSMC-like small cells, empty cells, single particles, odd counts; a 64-bit step and seed.
+        'small_cells': dict(counts=np.r_[rng.poisson(12.0, 300), 0, 0, 1, 2, 3, 0, 5],
+                            rng_seed=2, selection_factor=1.0e14, seed=0x1234567890abcdef,
+                            step=(1 << 32) + 5),
+        # High majorant use: most candidates are accepted; a raised majorant appears.
+        'dense_accept': dict(counts=rng.poisson(40.0, 100), rng_seed=3, selection_factor=2.0e15,
+                             majorant=2.0e-17),
+    }
+    out = {}
+    for name, kw in specs.items():
+        case = collide_oracle.make_case(**kw)
+        with tempfile.TemporaryDirectory() as tmp:
+            fin, fout = os.path.join(tmp, 'in.bin'), os.path.join(tmp, 'out.bin')
+            with open(fin, 'wb') as f:
+                f.write(np.array([case.sigma_g_max.size, case.velocity.shape[1]], np.int32).tobytes())
+                f.write(np.array([case.selection_factor, case.coefficient, case.exponent],
+                                 np.float32).tobytes())
+                f.write(np.array([case.seed, case.step], np.uint64).tobytes())
+                f.write(case.cell_start.tobytes())
+                f.write(case.sigma_g_max.tobytes())
+                f.write(case.velocity.tobytes())
+            subprocess.run([exe, fin, fout], check=True)
+            raw = open(fout, 'rb').read()
+        nv, c = case.velocity.size, case.sigma_g_max.size
+        out[name + '/velocity_in'] = case.velocity
+        out[name + '/cell_start'] = case.cell_start
+        out[name + '/sigma_in'] = case.sigma_g_max
+        out[name + '/scalars'] = np.array([case.selection_factor, case.coefficient, case.exponent],
+                                          np.float32)
+        out[name + '/seed_step'] = np.array([case.seed, case.step], np.uint64)
+        out[name + '/velocity_out'] = np.frombuffer(raw, np.float32, nv).reshape(3, -1)
+        out[name + '/sigma_out'] = np.frombuffer(raw, np.float32, c, offset=4 * nv)
+        out[name + '/collisions'] = np.frombuffer(raw, np.int32, c, offset=4 * (nv + c))
+    np.savez_compressed(os.path.join(HERE, 'collide_cases.npz'), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--reference', default='/root/reference/project_aether')
@@ -142,6 +192,7 @@ def main():
     from src.custom_kernels.triton import radix_sort_reference as ref
     philox_fixture()
     replay_fixture(ref)
+    collide_fixture()
     if args.triton:
         triton_fixture(args.reference)
 
