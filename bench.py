@@ -41,6 +41,7 @@ STAGE_BYTES_PER_PARTICLE = {
     'keygen_upsweep': 12 + 4, 'digit_pass_0': 4 + 8, 'digit_pass_1': 16, 'digit_pass_2': 16,
     'digit_pass_3': 16, 'cell_tables': 4, 'payload_gather': 4 + 24 + 24,
     'bucket_count': 12, 'bucket_scan': 0, 'bucket_scatter': 24 + 32, 'bucket_finish': 32 + 32,
+    'particle_push': 24 + 24, 'collide': 12 + 12,
 }
 
 
@@ -204,6 +205,14 @@ def run_single(args, workload):
             fused_particle_push([st['x'], st['y'], st['z']], [st['v'][k, :n] for k in range(3)],
                                 steady_dt, w.grid.lo, w.grid.hi)
 
+    if steady and args.collide:
+        # Unit thermal speed: sigma*g = g^0.46 stays below the majorant 3; the selection factor
+        # gives about one candidate pair per two cells of 8 particles.
+        from project_aether_b200 import ntc_collide
+        gas = (0.006, 1.0, 0.46)
+        sigma_g_max = torch.full((cells,), 3.0, dtype=torch.float32, device=device)
+        collisions = torch.zeros(cells, dtype=torch.int32, device=device)
+
     def step(s):
         if steady:
             move(state)
@@ -211,6 +220,9 @@ def run_single(args, workload):
                                          workloads.step_seed(1234, s), path=path)
         if steady:
             state.update(x=r.positions[0], y=r.positions[1], z=r.positions[2], v=r.velocity)
+            if args.collide:  # the stage after the sort, on the sorted velocities in place
+                ntc_collide.collide(lib, r.velocity, r.order.cell_start, sigma_g_max, collisions,
+                                    n, ntc_collide.CollisionParams(*gas, 1234, s))
         return r
 
     warmup = max(3, args.warmup)
@@ -338,7 +350,8 @@ def run_single(args, workload):
         'config': {'workload': workload, 'particles': n, 'cells': list(w.grid.cells),
                    'path': args.path, 'l2': 'inputs larger than L2 (no flush needed)',
                    'steady_state': ({'dt': steady_dt, 'cell_crossing_fraction': crossing,
-                                     'step': 'push + re-sort of the previous sorted state'}
+                                     'step': ('push + re-sort of the previous sorted state' +
+                                              (' + collisions' if args.collide else ''))}
                                     if steady else None),
                    'seed_per_step': 'run_seed ^ (step << 20)'},
         'clocks': {'sm_mhz': clocks['sm_mhz'], 'sm_max_mhz': clocks['sm_max_mhz'],
@@ -370,6 +383,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default=None)
+    ap.add_argument('--collide', action='store_true',
+                    help='steady-state workload only: run the collision stage after every sort')
     ap.add_argument('--path', default='auto', choices=['auto', 'digits', 'bucketed'])
     args = ap.parse_args()
     workload = args.workload or ('c3_64m_hypersonic' if args.gpus == 1 else 'c4_256m_512')

@@ -140,8 +140,10 @@ extern "C" int AetherSortAbiVersion(void) { return 1; }
 
 extern "C" size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload) {
   if (!count_ok(n) || num_cells <= 0 || key_bits_of(num_cells) > 32) return 0;
-  (void)with_payload;  // both forms use the same workspace
-  return std::max(standard_workspace_bytes(n, num_cells), bucketed_workspace_bytes(n, num_cells));
+  // The digit passes gather the payload through 32-byte records when there is room for them.
+  const size_t standard = with_payload ? standard_workspace_bytes_with_records(n, num_cells)
+                                       : standard_workspace_bytes(n, num_cells);
+  return std::max(standard, bucketed_workspace_bytes(n, num_cells));
 }
 
 extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const float* z,

@@ -190,6 +190,7 @@ struct SortArgs {
 };
 
 size_t standard_workspace_bytes(int64_t n, int64_t num_cells);
+size_t standard_workspace_bytes_with_records(int64_t n, int64_t num_cells);
 // `run_if`: device flag; when not null the kernels do nothing unless it is
 // nonzero (the hand-over from the bucketed path), and the first 8 bytes of the
 // workspace header (error code and that flag) are left as they are.

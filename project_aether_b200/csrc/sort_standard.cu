@@ -392,6 +392,51 @@ inline int grid_for(int64_t work_items, int per_block, int blocks_per_sm) {
   return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks, kSmCount * blocks_per_sm)));
 }
 
+// ------------------------------------------------------------------------
+// Payload gather through 32-byte records.  Gathering six arrays 4 bytes at a
+// time costs six scattered 32-byte sector reads per particle; packing the
+// payload into one 32-byte record per particle first (a streaming pass) makes
+// it one.  Used when the workspace has room for the records.
+// ------------------------------------------------------------------------
+constexpr int kRecordThreads = 256;
+
+__global__ void __launch_bounds__(kRecordThreads)
+record_build_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                    const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
+                    int64_t n, float4* __restrict__ records, const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kRecordThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kRecordThreads + threadIdx.x; i < n;
+       i += stride) {
+    const float vx = v ? __ldcs(v + i) : 0.f, vy = v ? __ldcs(v + padded + i) : 0.f;
+    const float vz = v ? __ldcs(v + 2 * padded + i) : 0.f;
+    records[2 * i] = make_float4(__ldcs(x + i), __ldcs(y + i), __ldcs(z + i), vx);
+    records[2 * i + 1] = make_float4(vy, vz, 0.f, 0.f);
+  }
+}
+
+__global__ void __launch_bounds__(kRecordThreads)
+record_gather_kernel(const int32_t* __restrict__ index, int64_t n,
+                     const float4* __restrict__ records, float* __restrict__ xs,
+                     float* __restrict__ ys, float* __restrict__ zs, float* __restrict__ vs,
+                     int64_t padded_sorted, const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kRecordThreads;
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * kRecordThreads + threadIdx.x; r < n;
+       r += stride) {
+    const int64_t i = __ldcs(index + r);
+    const float4 a = __ldg(records + 2 * i), b = __ldg(records + 2 * i + 1);
+    __stcs(xs + r, a.x);
+    __stcs(ys + r, a.y);
+    __stcs(zs + r, a.z);
+    if (vs) {
+      __stcs(vs + r, a.w);
+      __stcs(vs + padded_sorted + r, b.x);
+      __stcs(vs + 2 * padded_sorted + r, b.y);
+    }
+  }
+}
+
 struct StandardLayout {
   int passes;
   int64_t tiles;
@@ -414,6 +459,11 @@ StandardLayout standard_layout(int64_t n, int key_bits) {
 
 size_t standard_workspace_bytes(int64_t n, int64_t /*num_cells*/) {
   return standard_layout(n, 32).total;
+}
+
+// With room for one 32-byte payload record per particle behind the digit-pass arrays.
+size_t standard_workspace_bytes_with_records(int64_t n, int64_t num_cells) {
+  return standard_workspace_bytes(n, num_cells) + static_cast<size_t>(n) * 32;
 }
 
 cudaError_t launch_make_keys(const float* x, const float* y, const float* z, int64_t n,
@@ -538,8 +588,21 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   if (e != cudaSuccess) return e;
   if (a.xs) {
     stage_begin(kStageGather, a.stream);
-    e = launch_gather(a.index_out, a.n, a.x, a.y, a.z, a.velocity, a.padded, a.xs, a.ys, a.zs,
-                      a.vs, a.padded_sorted, a.stream, run_if);
+    // Key bits do not change the layout's size: the records start where a 32-bit layout ends.
+    const size_t records_off = standard_workspace_bytes(a.n, a.num_cells);
+    if (a.n > 0 && a.workspace_bytes >= records_off + static_cast<size_t>(a.n) * 32) {
+      float4* records = reinterpret_cast<float4*>(base + records_off);
+      const int grid = grid_for(a.n, kRecordThreads, 8);
+      record_build_kernel<<<grid, kRecordThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity,
+                                                                  a.padded, a.n, records, run_if);
+      record_gather_kernel<<<grid, kRecordThreads, 0, a.stream>>>(
+          a.index_out, a.n, records, a.xs, a.ys, a.zs, a.vs, a.padded_sorted, run_if);
+      count_launches(2);
+      e = cudaGetLastError();
+    } else {
+      e = launch_gather(a.index_out, a.n, a.x, a.y, a.z, a.velocity, a.padded, a.xs, a.ys, a.zs,
+                        a.vs, a.padded_sorted, a.stream, run_if);
+    }
     stage_end(kStageGather, a.stream);
   }
   return e;
