@@ -214,10 +214,11 @@ def run_single(args, workload):
         collisions = torch.zeros(cells, dtype=torch.int32, device=device)
 
     def step(s):
-        if steady:
+        if steady and args.separate_push:
             move(state)
+        fused = (steady_dt, w.grid.lo, w.grid.hi) if steady and not args.separate_push else None
         r = pa.sort_and_gather_particles(state['x'], state['y'], state['z'], state['v'], w.grid,
-                                         workloads.step_seed(1234, s), path=path)
+                                         workloads.step_seed(1234, s), path=path, push=fused)
         if steady:
             state.update(x=r.positions[0], y=r.positions[1], z=r.positions[2], v=r.velocity)
             if args.collide:  # the stage after the sort, on the sorted velocities in place
@@ -350,7 +351,8 @@ def run_single(args, workload):
         'config': {'workload': workload, 'particles': n, 'cells': list(w.grid.cells),
                    'path': args.path, 'l2': 'inputs larger than L2 (no flush needed)',
                    'steady_state': ({'dt': steady_dt, 'cell_crossing_fraction': crossing,
-                                     'step': ('push + re-sort of the previous sorted state' +
+                                     'step': (('push kernel, then' if args.separate_push else 'push fused into the')
+                                              + ' re-sort of the previous sorted state' +
                                               (' + collisions' if args.collide else ''))}
                                     if steady else None),
                    'seed_per_step': 'run_seed ^ (step << 20)'},
@@ -383,6 +385,9 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default=None)
+    ap.add_argument('--separate-push', action='store_true',
+                    help='steady-state workload only: run the move stage as its own kernel '
+                         'instead of inside the sort kernels')
     ap.add_argument('--collide', action='store_true',
                     help='steady-state workload only: run the collision stage after every sort')
     ap.add_argument('--path', default='auto', choices=['auto', 'digits', 'bucketed'])

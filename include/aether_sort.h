@@ -87,6 +87,13 @@ int AetherMakeKeys(const float* x, const float* y, const float* z, int64_t n,
  * `stream`, reads the code back and stores it in *status (0 = clean). */
 int AetherSortReadStatus(const void* workspace, void* stream, int32_t* status);
 
+/* Which path produced the last result in this workspace: synchronises `stream`
+ * and stores 1 in *used if the device handed the call from the bucketed path to
+ * the digit passes (a cell or a counter too full for shared memory), else 0.
+ * The results are the same either way; the digit passes are slower.  (New: the
+ * reference has a single path.) */
+int AetherSortReadUsedDigitPasses(const void* workspace, void* stream, int32_t* used);
+
 /* Multi-GPU step 1: stable partition of this rank's particles by destination
  * x-slab.  With `world` ranks (1..8, nx divisible by world) rank r owns global
  * ix in [r*nx/world, (r+1)*nx/world); ix is computed with the global grid as in
@@ -139,6 +146,24 @@ int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
  * pointers to three floats each. */
 int AetherParticlePush(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
                        float dt, const float* lo, const float* hi, void* stream);
+
+/* The move stage and the sort in one call: every particle is taken at
+ * x + v*dt with specular reflection at lo/hi (the arithmetic of AetherParticlePush),
+ * sorted by the cell of that moved position, and the sorted payload carries the
+ * moved positions and the reflected velocities.  The input arrays are not
+ * modified.  Replaces lines 101-109 of the reference's step
+ * (project_aether/src/physics_engine/dsmc_gpu_pipeline.py: fused_particle_push,
+ * sort_particles_by_cell and the four index_select gathers) and saves the move
+ * stage's own pass over positions and velocities (48 bytes per particle).
+ * Arguments as AetherSortAndGatherParticles plus dt and host pointers lo, hi to
+ * three floats each; velocity is required; the workspace must have the size
+ * AetherSortWorkspaceBytes(n, num_cells, 1) reports. */
+int AetherPushSortAndGatherParticles(
+    const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
+    int64_t n, float dt, const float* lo, const float* hi, const AetherGrid* grid, uint64_t seed,
+    uint32_t* keys_out, int32_t* index_out, int32_t* cell_counts, int32_t* cell_start,
+    float* x_sorted, float* y_sorted, float* z_sorted, float* velocity_sorted,
+    int64_t padded_sorted, int path, void* workspace, size_t workspace_bytes, void* stream);
 
 /* The stage that follows the sort in the DSMC step: No-Time-Counter collisions
  * on the cell-sorted velocities, in place.  Name, arguments and return value are

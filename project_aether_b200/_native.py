@@ -34,11 +34,18 @@ _SIGNATURES = {
                                                     ctypes.POINTER(AetherGrid), ctypes.c_uint64,
                                                     _P, _P, _P, _P, _P, _P, _P, _P, _I64,
                                                     ctypes.c_int, _P, ctypes.c_size_t, _P]),
+    'AetherPushSortAndGatherParticles': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.c_float,
+                                                        ctypes.POINTER(ctypes.c_float),
+                                                        ctypes.POINTER(ctypes.c_float),
+                                                        ctypes.POINTER(AetherGrid), ctypes.c_uint64,
+                                                        _P, _P, _P, _P, _P, _P, _P, _P, _I64,
+                                                        ctypes.c_int, _P, ctypes.c_size_t, _P]),
     'AetherGatherParticles': (ctypes.c_int, [_P, _I64, _P, _P, _P, _P, _I64, _P, _P, _P, _P,
                                              _I64, _P]),
     'AetherMakeKeys': (ctypes.c_int, [_P, _P, _P, _I64, ctypes.POINTER(AetherGrid),
                                       ctypes.c_uint64, _P, _P]),
     'AetherSortReadStatus': (ctypes.c_int, [_P, _P, ctypes.POINTER(ctypes.c_int32)]),
+    'AetherSortReadUsedDigitPasses': (ctypes.c_int, [_P, _P, ctypes.POINTER(ctypes.c_int32)]),
     'AetherSlabPartitionWorkspaceBytes': (ctypes.c_size_t, [_I64, ctypes.c_int]),
     'AetherSlabPartition': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.POINTER(AetherGrid),
                                            ctypes.c_int, _P, _P, _P, _P, _P, _P, _P, _P,

@@ -161,17 +161,20 @@ extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const f
   return run_sort(a, 0);
 }
 
-extern "C" int AetherSortAndGatherParticles(
-    const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
-    int64_t n, const AetherGrid* grid, uint64_t seed, uint32_t* keys_out, int32_t* index_out,
-    int32_t* cell_counts, int32_t* cell_start, float* x_sorted, float* y_sorted, float* z_sorted,
-    float* velocity_sorted, int64_t padded_sorted, int path, void* workspace,
-    size_t workspace_bytes, void* stream) {
+namespace aether {
+namespace {
+int sort_and_gather(const float* x, const float* y, const float* z, const float* velocity,
+                    int64_t padded, int64_t n, const AetherGrid* grid, uint64_t seed,
+                    uint32_t* keys_out, int32_t* index_out, int32_t* cell_counts,
+                    int32_t* cell_start, float* x_sorted, float* y_sorted, float* z_sorted,
+                    float* velocity_sorted, int64_t padded_sorted, int path, void* workspace,
+                    size_t workspace_bytes, void* stream, const PushSpec& push) {
   if (!grid) return cudaErrorInvalidValue;
   if (n > 0 && (!x_sorted || !y_sorted || !z_sorted)) return cudaErrorInvalidValue;
   if ((velocity == nullptr) != (velocity_sorted == nullptr)) return cudaErrorInvalidValue;
   if (velocity && (padded < n || padded_sorted < n)) return cudaErrorInvalidValue;
   if (path < 0 || path > 2) return cudaErrorInvalidValue;
+  if (push.enabled && !velocity) return cudaErrorInvalidValue;
   SortArgs a{};
   a.x = x; a.y = y; a.z = z; a.velocity = velocity; a.padded = padded; a.n = n;
   a.grid = *grid; a.seed = seed;
@@ -181,7 +184,40 @@ extern "C" int AetherSortAndGatherParticles(
   a.padded_sorted = padded_sorted;
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   a.stream = static_cast<cudaStream_t>(stream);
+  a.push = push;
   return run_sort(a, path);
+}
+}  // namespace
+}  // namespace aether
+
+extern "C" int AetherSortAndGatherParticles(
+    const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
+    int64_t n, const AetherGrid* grid, uint64_t seed, uint32_t* keys_out, int32_t* index_out,
+    int32_t* cell_counts, int32_t* cell_start, float* x_sorted, float* y_sorted, float* z_sorted,
+    float* velocity_sorted, int64_t padded_sorted, int path, void* workspace,
+    size_t workspace_bytes, void* stream) {
+  return sort_and_gather(x, y, z, velocity, padded, n, grid, seed, keys_out, index_out,
+                         cell_counts, cell_start, x_sorted, y_sorted, z_sorted, velocity_sorted,
+                         padded_sorted, path, workspace, workspace_bytes, stream, PushSpec{});
+}
+
+extern "C" int AetherPushSortAndGatherParticles(
+    const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
+    int64_t n, float dt, const float* lo, const float* hi, const AetherGrid* grid, uint64_t seed,
+    uint32_t* keys_out, int32_t* index_out, int32_t* cell_counts, int32_t* cell_start,
+    float* x_sorted, float* y_sorted, float* z_sorted, float* velocity_sorted,
+    int64_t padded_sorted, int path, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!lo || !hi) return cudaErrorInvalidValue;
+  PushSpec push{};
+  push.enabled = 1;
+  push.dt = dt;
+  for (int c = 0; c < 3; ++c) {
+    push.lo[c] = lo[c];
+    push.hi[c] = hi[c];
+  }
+  return sort_and_gather(x, y, z, velocity, padded, n, grid, seed, keys_out, index_out,
+                         cell_counts, cell_start, x_sorted, y_sorted, z_sorted, velocity_sorted,
+                         padded_sorted, path, workspace, workspace_bytes, stream, push);
 }
 
 extern "C" int AetherGatherParticles(const int32_t* index, int64_t n, const float* x,
@@ -211,6 +247,16 @@ extern "C" int AetherSortReadStatus(const void* workspace, void* stream, int32_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const Header* hdr = static_cast<const Header*>(workspace);
   cudaError_t e = cudaMemcpyAsync(status, &hdr->error, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return e;
+  return cudaStreamSynchronize(s);
+}
+
+extern "C" int AetherSortReadUsedDigitPasses(const void* workspace, void* stream, int32_t* used) {
+  if (!workspace || !used) return cudaErrorInvalidValue;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const Header* hdr = static_cast<const Header*>(workspace);
+  cudaError_t e = cudaMemcpyAsync(used, &hdr->use_standard, sizeof(int32_t),
+                                  cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return e;
   return cudaStreamSynchronize(s);
 }

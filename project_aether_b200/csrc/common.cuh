@@ -172,6 +172,26 @@ void count_launches(int kernels);
 
 // ---- host-side launchers of the kernels (one translation unit each) ----
 
+// Optional move stage fused into the sort: the sort sees every particle at
+// c + v*dt with specular reflection at lo/hi, and the sorted payload carries
+// the moved positions and the reflected velocities; the inputs stay as they are.
+struct PushSpec {
+  int enabled;
+  float dt;
+  float lo[3], hi[3];
+};
+
+// x += v*dt and reflection at the two walls of one axis, in float32 with a rounded
+// multiply and a rounded add (fused_particle_push.py:36-44, reference_push :95-108).
+// Both wall tests look at the moved coordinate before any reflection.
+__device__ __forceinline__ void push_axis(float& c, float& v, float dt, float lo, float hi) {
+  c = __fadd_rn(c, __fmul_rn(v, dt));
+  const bool below = c < lo, above = c > hi;
+  if (below) c = __fsub_rn(__fmul_rn(2.0f, lo), c);
+  if (above) c = __fsub_rn(__fmul_rn(2.0f, hi), c);
+  if (below || above) v = -v;
+}
+
 struct SortArgs {
   const float *x, *y, *z, *velocity;
   int64_t padded, n;
@@ -187,6 +207,7 @@ struct SortArgs {
   void* workspace;
   size_t workspace_bytes;
   cudaStream_t stream;
+  PushSpec push;
 };
 
 size_t standard_workspace_bytes(int64_t n, int64_t num_cells);

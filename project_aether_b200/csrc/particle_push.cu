@@ -12,16 +12,6 @@ namespace {
 
 constexpr int kPushThreads = 256;
 
-__device__ __forceinline__ void reflect(float& c, float& v, float dt, float lo, float hi) {
-  c = __fadd_rn(c, __fmul_rn(v, dt));
-  // Both wall tests look at the moved coordinate before any reflection
-  // (fused_particle_push.py:38-39); the two reflections are then applied in turn.
-  const bool below = c < lo, above = c > hi;
-  if (below) c = __fsub_rn(__fmul_rn(2.0f, lo), c);
-  if (above) c = __fsub_rn(__fmul_rn(2.0f, hi), c);
-  if (below || above) v = -v;
-}
-
 template <bool VEC>
 __global__ void __launch_bounds__(kPushThreads)
 push_kernel(float* __restrict__ x, float* __restrict__ y, float* __restrict__ z,
@@ -38,10 +28,10 @@ push_kernel(float* __restrict__ x, float* __restrict__ y, float* __restrict__ z,
       const float lo[3] = {x_lo, y_lo, z_lo}, hi[3] = {x_hi, y_hi, z_hi};
 #pragma unroll
       for (int a = 0; a < 3; ++a) {
-        reflect(c[a].x, w[a].x, dt, lo[a], hi[a]);
-        reflect(c[a].y, w[a].y, dt, lo[a], hi[a]);
-        reflect(c[a].z, w[a].z, dt, lo[a], hi[a]);
-        reflect(c[a].w, w[a].w, dt, lo[a], hi[a]);
+        push_axis(c[a].x, w[a].x, dt, lo[a], hi[a]);
+        push_axis(c[a].y, w[a].y, dt, lo[a], hi[a]);
+        push_axis(c[a].z, w[a].z, dt, lo[a], hi[a]);
+        push_axis(c[a].w, w[a].w, dt, lo[a], hi[a]);
       }
       *reinterpret_cast<float4*>(x + i0) = c[0];
       *reinterpret_cast<float4*>(y + i0) = c[1];
@@ -53,13 +43,13 @@ push_kernel(float* __restrict__ x, float* __restrict__ y, float* __restrict__ z,
       for (int k = 0; k < 4 && i0 + k < n; ++k) {
         const int64_t i = i0 + k;
         float c = x[i], w = vx[i];
-        reflect(c, w, dt, x_lo, x_hi);
+        push_axis(c, w, dt, x_lo, x_hi);
         x[i] = c; vx[i] = w;
         c = y[i]; w = vy[i];
-        reflect(c, w, dt, y_lo, y_hi);
+        push_axis(c, w, dt, y_lo, y_hi);
         y[i] = c; vy[i] = w;
         c = z[i]; w = vz[i];
-        reflect(c, w, dt, z_lo, z_hi);
+        push_axis(c, w, dt, z_lo, z_hi);
         z[i] = c; vz[i] = w;
       }
     }

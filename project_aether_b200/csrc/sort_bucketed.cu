@@ -58,7 +58,8 @@ constexpr int kNoChunkLog = 31;    // ... or one chunk for everything
 template <bool SHARED, bool VEC, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
-                    const float* __restrict__ z, int64_t n, AetherGrid g, int shift,
+                    const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
+                    PushSpec push, int64_t n, AetherGrid g, int shift,
                     int buckets, int chunks, int chunk_log, int parts, int64_t slice,
                     uint32_t* __restrict__ bucket_count) {
   extern __shared__ uint32_t hist[];
@@ -91,6 +92,29 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
           px[k] = ok ? x[i0 + k] : 0.f;
           py[k] = ok ? y[i0 + k] : 0.f;
           pz[k] = ok ? z[i0 + k] : 0.f;
+        }
+      }
+      if (push.enabled) {  // count the particles where the fused move stage puts them
+        float w[3][4];
+        if (VEC && i0 + 4 <= last) {
+          const float4 a = ldcs4(v + i0), b = ldcs4(v + padded + i0), c = ldcs4(v + 2 * padded + i0);
+          w[0][0] = a.x; w[0][1] = a.y; w[0][2] = a.z; w[0][3] = a.w;
+          w[1][0] = b.x; w[1][1] = b.y; w[1][2] = b.z; w[1][3] = b.w;
+          w[2][0] = c.x; w[2][1] = c.y; w[2][2] = c.z; w[2][3] = c.w;
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const bool ok = i0 + k < last;
+            w[0][k] = ok ? v[i0 + k] : 0.f;
+            w[1][k] = ok ? v[padded + i0 + k] : 0.f;
+            w[2][k] = ok ? v[2 * padded + i0 + k] : 0.f;
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          push_axis(px[k], w[0][k], push.dt, push.lo[0], push.hi[0]);
+          push_axis(py[k], w[1][k], push.dt, push.lo[1], push.hi[1]);
+          push_axis(pz[k], w[2][k], push.dt, push.lo[2], push.hi[2]);
         }
       }
 #pragma unroll
@@ -217,6 +241,7 @@ bucket_scan_kernel(const uint32_t* __restrict__ bucket_count, int buckets, int64
   if (tid == 0) {
     bucket_start[buckets] = static_cast<uint32_t>(n);
     hdr->max_bucket = biggest;
+    // A bucket above `capacity` cannot be finished at all: hand over before the scatter runs.
     if (biggest > capacity) hdr->use_standard = 1;
   }
 }
@@ -281,9 +306,9 @@ template <bool VEC, int ITEMS>
 __global__ void __launch_bounds__(kScatterThreads, 8 / ITEMS)
 bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                       const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
-                      int64_t n, AetherGrid g, uint32_t k0, uint32_t k1, int shift, int buckets,
-                      int chunk_log, uint32_t* __restrict__ cursor, uint32_t* __restrict__ records,
-                      const Header* __restrict__ hdr) {
+                      PushSpec push, int64_t n, AetherGrid g, uint32_t k0, uint32_t k1, int shift,
+                      int buckets, int chunk_log, uint32_t* __restrict__ cursor,
+                      uint32_t* __restrict__ records, const Header* __restrict__ hdr) {
   if (hdr->use_standard) return;
   const int64_t groups = (n + ITEMS - 1) / ITEMS;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kScatterThreads;
@@ -317,6 +342,14 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) f[3][k] = f[4][k] = f[5][k] = 0.f;
     }
+    if (push.enabled) {  // the fused move stage: the record carries the moved particle
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        push_axis(f[0][k], f[3][k], push.dt, push.lo[0], push.hi[0]);
+        push_axis(f[1][k], f[4][k], push.dt, push.lo[1], push.hi[1]);
+        push_axis(f[2][k], f[5][k], push.dt, push.lo[2], push.hi[2]);
+      }
+    }
     uint32_t key[ITEMS], slot[ITEMS];
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
@@ -346,6 +379,8 @@ constexpr int kHistWords = (1 << kMaxLowBits) / 4;         // byte counters, 4 p
 constexpr int kWordsPerThread = kHistWords / kFinishThreads;  // 8
 constexpr uint32_t kBulkChunkBytes = 32768;                // bytes per bulk copy
 constexpr uint32_t kBulkWaitLimit = 1u << 24;              // polls of the copy barrier
+constexpr int kMaxSegments = 32;                           // runs of cells an oversized bucket is cut into
+constexpr uint32_t kLargestBucket = kMaxSegments * kFinishCapacity;  // beyond this no cut can fit
 
 struct __align__(128) FinishSmem {
   uint32_t raw[kFinishCapacity * kRecordWords];  // the bucket's records as they lie in HBM
@@ -356,6 +391,9 @@ struct __align__(128) FinishSmem {
   uint32_t total;
   uint32_t gave_up;
   unsigned long long barrier;    // mbarrier of the bulk copy
+  uint32_t seg_begin[kMaxSegments + 1];  // oversized bucket: records before each run of cells
+  uint16_t seg_first[kMaxSegments + 1];  // ... and the first cell of each run
+  uint32_t fill;                         // ... and the records picked so far for the run at hand
 };
 static_assert(sizeof(FinishSmem) <= 227 * 1024, "finish kernel shared memory");
 
@@ -395,14 +433,282 @@ __device__ __forceinline__ bool bulk_load_wait(unsigned long long* barrier, uint
   return false;
 }
 
+// Output arrays of the finish kernel.
+struct FinishOut {
+  uint32_t* keys;
+  int32_t* index;
+  int32_t* cell_counts;
+  int32_t* cell_start;
+  float* xs;
+  float* ys;
+  float* zs;
+  float* vs;
+  int64_t padded_sorted;
+};
+
+// Sorts the `count` records staged in s.raw (any order) and writes them to the
+// output from slot `begin` on.  The records belong to the cells first_cell ..
+// first_cell + cells_here - 1; `low_base` is the low key (bits below the bucket
+// id) of the first of these cells.  s.hist must be zero over the counters used.
+// Returns false if a byte counter wrapped (more than 255 records on one counter).
+__device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out, int count,
+                                            uint32_t begin, int64_t first_cell, int cells_here,
+                                            uint32_t low_base, uint32_t low_mask, int drop) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t drop_mask = (1u << drop) - 1;
+  const int cell_words = 32 >> drop;  // counter words per cell
+  const int hist_words = max(8, cells_here * cell_words);
+
+  // Count the low key bits with byte-wide counters; the value an add returns
+  // is the record's rank among the records of its counter.
+  uint32_t packed[kFinishItems];  // counter id | rank << 16
+#pragma unroll
+  for (int k = 0; k < kFinishItems; ++k) {
+    const int r = tid + k * kFinishThreads;
+    packed[k] = 0;
+    if (r < count) {
+      const uint32_t low = ((s.raw[r * kRecordWords] & low_mask) - low_base) >> drop;
+      const int sh = 8 * (low & 3);
+      const uint32_t old = atomicAdd(&s.hist[low >> 2], 1u << sh);
+      packed[k] = low | (((old >> sh) & 0xffu) << 16);
+    }
+  }
+  __syncthreads();
+
+  // Exclusive scan of the counters (8 words = 32 counters per thread, fetched
+  // as two 128-bit loads so that neighbouring threads do not collide on banks).
+  uint32_t local[kWordsPerThread];
+  uint32_t sum = 0;
+  {
+    uint32_t w[kWordsPerThread];
+    const uint4 a = *reinterpret_cast<const uint4*>(&s.hist[tid * kWordsPerThread]);
+    const uint4 c = *reinterpret_cast<const uint4*>(&s.hist[tid * kWordsPerThread + 4]);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    w[4] = c.x; w[5] = c.y; w[6] = c.z; w[7] = c.w;
+#pragma unroll
+    for (int j = 0; j < kWordsPerThread; ++j) {
+      local[j] = sum;
+      sum += tid * kWordsPerThread + j < hist_words ? byte_sum(w[j]) : 0u;
+    }
+  }
+  uint32_t incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) s.warp_sum[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t w = s.warp_sum[lane];
+    uint32_t wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    s.warp_sum[lane] = wi - w;
+    if (lane == 31) s.total = wi;
+  }
+  __syncthreads();
+  const uint32_t thread_base = s.warp_sum[warp] + incl - sum;
+  if (tid * kWordsPerThread < hist_words) {  // hist_words is a multiple of 8
+    uint4 packed_prefix;
+    packed_prefix.x = (thread_base + local[0]) | ((thread_base + local[1]) << 16);
+    packed_prefix.y = (thread_base + local[2]) | ((thread_base + local[3]) << 16);
+    packed_prefix.z = (thread_base + local[4]) | ((thread_base + local[5]) << 16);
+    packed_prefix.w = (thread_base + local[6]) | ((thread_base + local[7]) << 16);
+    *reinterpret_cast<uint4*>(&s.word_prefix[tid * kWordsPerThread]) = packed_prefix;
+  }
+  // A byte counter that wrapped loses 256 from the total.
+  const bool wrapped = s.total != static_cast<uint32_t>(count);
+  __syncthreads();
+  if (wrapped) return false;
+
+  // Cell tables: every cell is 128 >> drop consecutive counters.
+  for (int c = tid; c < cells_here; c += kFinishThreads) {
+    const uint32_t lo = s.word_prefix[c * cell_words];
+    const uint32_t hi = (c + 1) * cell_words < hist_words ? s.word_prefix[(c + 1) * cell_words]
+                                                           : static_cast<uint32_t>(count);
+    out.cell_start[first_cell + c] = static_cast<int32_t>(begin + lo);
+    out.cell_counts[first_cell + c] = static_cast<int32_t>(hi - lo);
+  }
+
+  // Sorted slot of every record: start of its counter's run + arrival rank.  A
+  // counter held by one record only (the usual case) is final at once.
+  uint32_t run[kFinishItems];  // run start | run length << 16, for records that share a counter
+#pragma unroll
+  for (int k = 0; k < kFinishItems; ++k) {
+    const int r = tid + k * kFinishThreads;
+    run[k] = 0;
+    if (r < count) {
+      const uint32_t low = packed[k] & 0xffffu, rank = packed[k] >> 16;
+      const uint32_t word = s.hist[low >> 2];
+      const int sh = 8 * (low & 3);
+      const uint32_t start = s.word_prefix[low >> 2] + byte_sum(word & ((1u << sh) - 1u));
+      const uint32_t length = (word >> sh) & 0xffu;
+      s.order[start + rank] = static_cast<uint16_t>(r);
+      if (length > 1) run[k] = start | (length << 16);
+    }
+  }
+  __syncthreads();
+
+  // Records that share a counter must appear in ascending (dropped key bits,
+  // original index): a record inside such a run moves to (run start + number of
+  // smaller records in the run).  Indices stay below 2^30, so the dropped bits
+  // ride above them in one word.
+  uint32_t moved[kFinishItems];
+#pragma unroll
+  for (int k = 0; k < kFinishItems; ++k) {
+    moved[k] = 0xffffffffu;
+    if (run[k]) {
+      const int r = tid + k * kFinishThreads;
+      const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
+      const uint32_t mine = ((s.raw[r * kRecordWords] & drop_mask) << 30) | s.raw[r * kRecordWords + 1];
+      uint32_t smaller = 0;
+      for (uint32_t j = 0; j < length; ++j) {
+        const uint32_t* other = &s.raw[s.order[start + j] * kRecordWords];
+        smaller += (((other[0] & drop_mask) << 30) | other[1]) < mine;
+      }
+      moved[k] = start + smaller;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < kFinishItems; ++k)
+    if (moved[k] != 0xffffffffu) s.order[moved[k]] = static_cast<uint16_t>(tid + k * kFinishThreads);
+  __syncthreads();
+
+  // Coalesced output: each lane pulls one whole record out of shared memory
+  // and writes its eight words to the eight output arrays.  (128-bit stores of
+  // four consecutive slots per thread were measured: slower, 1.45 ms against
+  // 1.32 ms at 64 M particles.)
+  for (int d = tid; d < count; d += kFinishThreads) {
+    const int rec = s.order[d];
+    const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords]);
+    const uint4 c = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4]);
+    const size_t o = static_cast<size_t>(begin) + d;
+    __stcs(out.keys + o, a.x);
+    __stcs(out.index + o, static_cast<int32_t>(a.y));
+    if (out.xs) {  // keys-only calls leave the payload out
+      __stcs(out.xs + o, __uint_as_float(a.z));
+      __stcs(out.ys + o, __uint_as_float(a.w));
+      __stcs(out.zs + o, __uint_as_float(c.x));
+    }
+    if (out.vs) {
+      __stcs(out.vs + o, __uint_as_float(c.y));
+      __stcs(out.vs + out.padded_sorted + o, __uint_as_float(c.z));
+      __stcs(out.vs + 2 * out.padded_sorted + o, __uint_as_float(c.w));
+    }
+  }
+  __syncthreads();
+  return true;
+}
+
+// A bucket with more records than shared memory holds (a dense region: the
+// bucket width is planned from the average load).  The block counts the
+// bucket's records per cell, cuts the cells into up to kMaxSegments runs that
+// fit, and for every run picks the run's records out of the bucket (which it
+// reads from global memory once per run) and sorts them like a small bucket.
+// Returns false if it cannot (a single cell larger than shared memory, too many
+// runs, or a wrapped byte counter): the call then goes to the digit passes.
+__device__ bool finish_large_bucket(FinishSmem& s, const FinishOut& out,
+                                    const uint32_t* __restrict__ records,
+                                    const uint32_t* __restrict__ run_start,
+                                    const uint32_t* __restrict__ run_length, int chunks, int b,
+                                    uint32_t begin, int count, int64_t first_cell, int cells_here,
+                                    uint32_t low_mask, int drop) {
+  const int tid = threadIdx.x;
+  uint32_t* cell_count = s.hist;  // up to 1024 cells; s.hist is free until a run is sorted
+  for (int c = tid; c < cells_here; c += kFinishThreads) cell_count[c] = 0;
+  __syncthreads();
+  // Per-cell counts: one pass over the keys of the bucket's records.
+  for (int c = 0; c < chunks; ++c) {
+    const uint32_t start = chunks == 1 ? begin : run_start[static_cast<size_t>(b) * chunks + c];
+    const uint32_t length = chunks == 1 ? static_cast<uint32_t>(count)
+                                        : run_length[static_cast<size_t>(b) * chunks + c];
+    for (uint32_t i = tid; i < length; i += kFinishThreads) {
+      const uint32_t key = __ldg(records + static_cast<size_t>(start + i) * kRecordWords);
+      atomicAdd(&cell_count[(key & low_mask) >> kShuffleBits], 1u);
+    }
+  }
+  __syncthreads();
+  // Cut into runs of cells that fit (one thread; at most 1024 cells).
+  if (tid == 0) {
+    int segments = 0;
+    uint32_t load = 0, before = 0;
+    bool ok = true;
+    s.seg_first[0] = 0;
+    s.seg_begin[0] = 0;
+    for (int c = 0; c < cells_here && ok; ++c) {
+      const uint32_t here = cell_count[c];
+      if (here > static_cast<uint32_t>(kFinishCapacity)) ok = false;
+      if (load + here > static_cast<uint32_t>(kFinishCapacity)) {  // close the run before cell c
+        before += load;
+        load = 0;
+        ++segments;
+        if (segments >= kMaxSegments) { ok = false; break; }
+        s.seg_first[segments] = static_cast<uint16_t>(c);
+        s.seg_begin[segments] = before;
+      }
+      load += here;
+    }
+    if (ok) {
+      ++segments;
+      s.seg_first[segments] = static_cast<uint16_t>(cells_here);
+      s.seg_begin[segments] = before + load;
+    }
+    s.total = ok ? static_cast<uint32_t>(segments) : 0u;
+  }
+  __syncthreads();
+  const int segments = static_cast<int>(s.total);
+  __syncthreads();
+  if (segments == 0) return false;
+  const int cell_words = 32 >> drop;
+  for (int k = 0; k < segments; ++k) {
+    const int c0 = s.seg_first[k], c1 = s.seg_first[k + 1];
+    const uint32_t seg_begin = s.seg_begin[k];
+    const int seg_count = static_cast<int>(s.seg_begin[k + 1] - seg_begin);
+    // Zero the counters of this run and the fill cursor (cell_count is overwritten
+    // from here on; the cuts above are already in seg_first / seg_begin).
+    const int words = max(8, (c1 - c0) * cell_words);
+    for (int i = tid; i < words; i += kFinishThreads) s.hist[i] = 0;
+    if (tid == 0) s.fill = 0;
+    __syncthreads();
+    for (int c = 0; c < chunks; ++c) {
+      const uint32_t start = chunks == 1 ? begin : run_start[static_cast<size_t>(b) * chunks + c];
+      const uint32_t length = chunks == 1 ? static_cast<uint32_t>(count)
+                                          : run_length[static_cast<size_t>(b) * chunks + c];
+      for (uint32_t i = tid; i < length; i += kFinishThreads) {
+        const uint4* rec = reinterpret_cast<const uint4*>(records +
+                                                          static_cast<size_t>(start + i) * kRecordWords);
+        const uint4 lo = __ldg(rec);
+        const int cell = static_cast<int>((lo.x & low_mask) >> kShuffleBits);
+        if (cell >= c0 && cell < c1) {
+          const uint32_t slot = atomicAdd(&s.fill, 1u);
+          if (slot < static_cast<uint32_t>(kFinishCapacity)) {
+            *reinterpret_cast<uint4*>(&s.raw[slot * kRecordWords]) = lo;
+            *reinterpret_cast<uint4*>(&s.raw[slot * kRecordWords + 4]) = __ldg(rec + 1);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    const bool consistent = s.fill == static_cast<uint32_t>(seg_count);
+    __syncthreads();
+    if (!consistent) return false;
+    if (!sort_staged(s, out, seg_count, begin + seg_begin, first_cell + c0, c1 - c0,
+                     static_cast<uint32_t>(c0) << kShuffleBits, low_mask, drop))
+      return false;
+  }
+  return true;
+}
+
 __global__ void __launch_bounds__(kFinishThreads, 1)
 bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __restrict__ bucket_start,
                      const uint32_t* __restrict__ run_start, const uint32_t* __restrict__ run_length,
                      int chunks, int buckets, int shift, int64_t n, int64_t num_cells,
-                     uint32_t* __restrict__ keys_out, int32_t* __restrict__ index_out,
-                     int32_t* __restrict__ cell_counts, int32_t* __restrict__ cell_start,
-                     float* __restrict__ xs, float* __restrict__ ys, float* __restrict__ zs,
-                     float* __restrict__ vs, int64_t padded_sorted, Header* __restrict__ hdr) {
+                     FinishOut out, Header* __restrict__ hdr) {
   if (hdr->use_standard) return;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FinishSmem& s = *reinterpret_cast<FinishSmem*>(smem_raw);
@@ -413,9 +719,7 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
   const int low_bits = shift + kShuffleBits;
   const uint32_t low_mask = (1u << low_bits) - 1;
   const int drop = max(0, low_bits - kMaxLowBits);
-  const uint32_t drop_mask = (1u << drop) - 1;
-  const int hist_words = max(1, (1 << (low_bits - drop)) / 4);
-  const int cell_words = 32 >> drop;  // counter words per cell
+  const int hist_words = max(8, (1 << (low_bits - drop)) / 4);
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s.barrier)) : "memory");
@@ -453,8 +757,15 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
         }
       }
     }
-    if (count > kFinishCapacity) {  // cannot happen once the scan kernel has checked
-      if (tid == 0) hdr->use_standard = 1;
+    const int64_t first_cell = static_cast<int64_t>(b) << shift;
+    const int cells_here = static_cast<int>(
+        min(static_cast<long long>(1) << shift, static_cast<long long>(num_cells - first_cell)));
+    if (b == buckets - 1 && tid == 0) out.cell_start[num_cells] = static_cast<int32_t>(n);
+    if (count > kFinishCapacity) {
+      if (!finish_large_bucket(s, out, records, run_start, run_length, chunks, b, begin, count,
+                               first_cell, cells_here, low_mask, drop)) {
+        if (tid == 0) hdr->use_standard = 1;
+      }
       continue;
     }
     // The bucket lies in HBM as one contiguous run of 32-byte records per chunk
@@ -508,160 +819,9 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       if (tid == 0) atomicCAS(&hdr->error, 0, kErrBulkCopyTimeout);
       return;
     }
-
-    // Count the low key bits with byte-wide counters; the value an add returns
-    // is the record's rank among equal keys.
-    uint32_t packed[kFinishItems];  // low key | rank among equal keys << 16
-#pragma unroll
-    for (int k = 0; k < kFinishItems; ++k) {
-      const int r = tid + k * kFinishThreads;
-      packed[k] = 0;
-      if (r < count) {
-        const uint32_t low = (s.raw[r * kRecordWords] & low_mask) >> drop;
-        const int sh = 8 * (low & 3);
-        const uint32_t old = atomicAdd(&s.hist[low >> 2], 1u << sh);
-        packed[k] = low | (((old >> sh) & 0xffu) << 16);
-      }
-    }
-    __syncthreads();
-
-    // Exclusive scan of the counters (8 words = 32 counters per thread, fetched
-    // as two 128-bit loads so that neighbouring threads do not collide on banks).
-    uint32_t local[kWordsPerThread];
-    uint32_t sum = 0;
-    {
-      uint32_t w[kWordsPerThread];
-      const uint4 a = *reinterpret_cast<const uint4*>(&s.hist[tid * kWordsPerThread]);
-      const uint4 c = *reinterpret_cast<const uint4*>(&s.hist[tid * kWordsPerThread + 4]);
-      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-      w[4] = c.x; w[5] = c.y; w[6] = c.z; w[7] = c.w;
-#pragma unroll
-      for (int j = 0; j < kWordsPerThread; ++j) {
-        local[j] = sum;
-        sum += tid * kWordsPerThread + j < hist_words ? byte_sum(w[j]) : 0u;
-      }
-    }
-    uint32_t incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    if (lane == 31) s.warp_sum[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-      const uint32_t w = s.warp_sum[lane];
-      uint32_t wi = w;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-        if (lane >= o) wi += t;
-      }
-      s.warp_sum[lane] = wi - w;
-      if (lane == 31) s.total = wi;
-    }
-    __syncthreads();
-    const uint32_t thread_base = s.warp_sum[warp] + incl - sum;
-    if (tid * kWordsPerThread < hist_words) {  // hist_words is a multiple of 8
-      uint4 packed_prefix;
-      packed_prefix.x = (thread_base + local[0]) | ((thread_base + local[1]) << 16);
-      packed_prefix.y = (thread_base + local[2]) | ((thread_base + local[3]) << 16);
-      packed_prefix.z = (thread_base + local[4]) | ((thread_base + local[5]) << 16);
-      packed_prefix.w = (thread_base + local[6]) | ((thread_base + local[7]) << 16);
-      *reinterpret_cast<uint4*>(&s.word_prefix[tid * kWordsPerThread]) = packed_prefix;
-    }
-    // A byte counter that wrapped (more than 255 equal keys) loses 255 from the
-    // total: hand the whole call to the digit-pass path.
-    const bool wrapped = s.total != static_cast<uint32_t>(count);
-    __syncthreads();
-    if (wrapped) {
+    if (!sort_staged(s, out, count, begin, first_cell, cells_here, 0u, low_mask, drop)) {
       if (tid == 0) hdr->use_standard = 1;
-      continue;
     }
-
-    // Cell tables of this bucket: every cell is 128 >> drop consecutive counters.
-    {
-      const int64_t first_cell = static_cast<int64_t>(b) << shift;
-      const int cells_here = static_cast<int>(
-          min(static_cast<long long>(1) << shift, static_cast<long long>(num_cells - first_cell)));
-      for (int c = tid; c < cells_here; c += kFinishThreads) {
-        const uint32_t lo = s.word_prefix[c * cell_words];
-        const uint32_t hi = (c + 1) * cell_words < hist_words ? s.word_prefix[(c + 1) * cell_words]
-                                                               : static_cast<uint32_t>(count);
-        cell_start[first_cell + c] = static_cast<int32_t>(begin + lo);
-        cell_counts[first_cell + c] = static_cast<int32_t>(hi - lo);
-      }
-      if (b == buckets - 1 && tid == 0) cell_start[num_cells] = static_cast<int32_t>(n);
-    }
-
-    // Sorted slot of every record: start of its key's run + arrival rank.  A
-    // key held by one record only (the usual case) is final at once.
-    uint32_t run[kFinishItems];  // run start | run length << 16, for records that share their key
-#pragma unroll
-    for (int k = 0; k < kFinishItems; ++k) {
-      const int r = tid + k * kFinishThreads;
-      run[k] = 0;
-      if (r < count) {
-        const uint32_t low = packed[k] & 0xffffu, rank = packed[k] >> 16;
-        const uint32_t word = s.hist[low >> 2];
-        const int sh = 8 * (low & 3);
-        const uint32_t start = s.word_prefix[low >> 2] + byte_sum(word & ((1u << sh) - 1u));
-        const uint32_t length = (word >> sh) & 0xffu;
-        s.order[start + rank] = static_cast<uint16_t>(r);
-        if (length > 1) run[k] = start | (length << 16);
-      }
-    }
-    __syncthreads();
-
-    // Records that share a counter must appear in ascending (dropped key bits,
-    // original index): a record inside such a run moves to (run start + number of
-    // smaller records in the run).  Indices stay below 2^30, so the dropped bits
-    // ride above them in one word.
-    uint32_t moved[kFinishItems];
-#pragma unroll
-    for (int k = 0; k < kFinishItems; ++k) {
-      moved[k] = 0xffffffffu;
-      if (run[k]) {
-        const int r = tid + k * kFinishThreads;
-        const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
-        const uint32_t mine = ((s.raw[r * kRecordWords] & drop_mask) << 30) | s.raw[r * kRecordWords + 1];
-        uint32_t smaller = 0;
-        for (uint32_t j = 0; j < length; ++j) {
-          const uint32_t* other = &s.raw[s.order[start + j] * kRecordWords];
-          smaller += (((other[0] & drop_mask) << 30) | other[1]) < mine;
-        }
-        moved[k] = start + smaller;
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < kFinishItems; ++k)
-      if (moved[k] != 0xffffffffu) s.order[moved[k]] = static_cast<uint16_t>(tid + k * kFinishThreads);
-    __syncthreads();
-
-    // Coalesced output: each lane pulls one whole record out of shared memory
-    // and writes its eight words to the eight output arrays.  (128-bit stores of
-    // four consecutive slots per thread were measured: slower, 1.45 ms against
-    // 1.32 ms at 64 M particles.)
-    for (int d = tid; d < count; d += kFinishThreads) {
-      const int rec = s.order[d];
-      const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords]);
-      const uint4 c = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4]);
-      const size_t o = static_cast<size_t>(begin) + d;
-      __stcs(keys_out + o, a.x);
-      __stcs(index_out + o, static_cast<int32_t>(a.y));
-      if (xs) {  // keys-only calls leave the payload out
-        __stcs(xs + o, __uint_as_float(a.z));
-        __stcs(ys + o, __uint_as_float(a.w));
-        __stcs(zs + o, __uint_as_float(c.x));
-      }
-      if (vs) {
-        __stcs(vs + o, __uint_as_float(c.y));
-        __stcs(vs + padded_sorted + o, __uint_as_float(c.z));
-        __stcs(vs + 2 * padded_sorted + o, __uint_as_float(c.w));
-      }
-    }
-    __syncthreads();
   }
 }
 
@@ -776,14 +936,15 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
       e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(table_bytes));
       if (e != cudaSuccess) return e;
-      kernel<<<grid, threads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift,
-                                                       buckets, l.chunks, l.chunk_log, parts,
-                                                       slice, count);
+      kernel<<<grid, threads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push,
+                                                       a.n, a.grid, p.shift, buckets, l.chunks,
+                                                       l.chunk_log, parts, slice, count);
     } else {
       auto kernel = vec ? bucket_count_kernel<false, true, kCountThreads>
                         : bucket_count_kernel<false, false, kCountThreads>;
-      kernel<<<grid, threads, 0, a.stream>>>(a.x, a.y, a.z, a.n, a.grid, p.shift, buckets,
-                                             l.chunks, l.chunk_log, parts, slice, count);
+      kernel<<<grid, threads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push, a.n,
+                                             a.grid, p.shift, buckets, l.chunks, l.chunk_log,
+                                             parts, slice, count);
     }
   }
   stage_end(kStageBucketCount, a.stream);
@@ -799,7 +960,7 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
     run_start = words_at(l.run_start_off);
     run_length = words_at(l.run_length_off);
     bucket_total_kernel<<<(buckets + 255) / 256, 256, 0, a.stream>>>(count, buckets, l.chunks, total);
-    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, kFinishCapacity,
+    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, kLargestBucket,
                                                          start, nullptr, hdr);
     run_scan_local_kernel<<<l.scan_blocks, kFlatScanBlock, 0, a.stream>>>(count, l.entries, local,
                                                                           block_sum);
@@ -808,7 +969,7 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
         count, local, block_sum, buckets, l.chunks, cursor, run_start, run_length);
     count_launches(5);
   } else {
-    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(count, buckets, a.n, kFinishCapacity,
+    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(count, buckets, a.n, kLargestBucket,
                                                          start, cursor, hdr);
     count_launches(1);
   }
@@ -824,9 +985,9 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
         1, std::min<int64_t>((groups + kScatterThreads - 1) / kScatterThreads,
                              kSmCount * (8 / kItems) * 4)));
     auto kernel = vec ? bucket_scatter_kernel<true, kItems> : bucket_scatter_kernel<false, kItems>;
-    kernel<<<grid, kScatterThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.n,
-                                                    a.grid, k0, k1, p.shift, buckets, l.chunk_log,
-                                                    cursor, records, hdr);
+    kernel<<<grid, kScatterThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push,
+                                                    a.n, a.grid, k0, k1, p.shift, buckets,
+                                                    l.chunk_log, cursor, records, hdr);
   }
   stage_end(kStageBucketScatter, a.stream);
   e = cudaGetLastError();
@@ -837,11 +998,11 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   e = cudaFuncSetAttribute(bucket_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(sizeof(FinishSmem)));
   if (e != cudaSuccess) return e;
+  const FinishOut out{a.keys_out, a.index_out, a.cell_counts, a.cell_start, a.xs, a.ys, a.zs,
+                      a.vs, a.padded_sorted};
   bucket_finish_kernel<<<std::min(buckets, kSmCount), kFinishThreads, sizeof(FinishSmem),
                          a.stream>>>(records, start, run_start, run_length, l.chunks, buckets,
-                                     p.shift, a.n, a.num_cells, a.keys_out, a.index_out,
-                                     a.cell_counts, a.cell_start, a.xs, a.ys, a.zs, a.vs,
-                                     a.padded_sorted, hdr);
+                                     p.shift, a.n, a.num_cells, out, hdr);
   stage_end(kStageBucketFinish, a.stream);
   count_launches(1);
   return cudaGetLastError();

@@ -30,9 +30,9 @@ constexpr int kKeygenChunk = kKeygenThreads * kKeygenVec;
 template <int PASSES, bool VEC>
 __global__ void __launch_bounds__(kKeygenThreads)
 keygen_upsweep_kernel(const float* __restrict__ x, const float* __restrict__ y,
-                      const float* __restrict__ z, int64_t n, AetherGrid g, uint32_t k0,
-                      uint32_t k1, uint32_t* __restrict__ keys, uint32_t* __restrict__ global_hist,
-                      const int32_t* __restrict__ run_if) {
+                      const float* __restrict__ z, const float4* __restrict__ records, int64_t n,
+                      AetherGrid g, uint32_t k0, uint32_t k1, uint32_t* __restrict__ keys,
+                      uint32_t* __restrict__ global_hist, const int32_t* __restrict__ run_if) {
   if (run_if && *run_if == 0) return;
   __shared__ uint32_t hist[PASSES][kRadix];
   for (int i = threadIdx.x; i < PASSES * kRadix; i += kKeygenThreads) (&hist[0][0])[i] = 0;
@@ -42,7 +42,13 @@ keygen_upsweep_kernel(const float* __restrict__ x, const float* __restrict__ y,
     const int64_t i0 = c * kKeygenChunk + threadIdx.x * kKeygenVec;
     float px[kKeygenVec], py[kKeygenVec], pz[kKeygenVec];
     uint32_t key[kKeygenVec];
-    if (VEC && i0 + kKeygenVec <= n) {
+    if (records) {  // positions as the fused move stage left them in the payload records
+#pragma unroll
+      for (int k = 0; k < kKeygenVec; ++k) {
+        const float4 r = i0 + k < n ? __ldg(records + 2 * (i0 + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        px[k] = r.x; py[k] = r.y; pz[k] = r.z;
+      }
+    } else if (VEC && i0 + kKeygenVec <= n) {
       const float4 a = ldcs4(x + i0), b = ldcs4(y + i0), d = ldcs4(z + i0);
       px[0] = a.x; px[1] = a.y; px[2] = a.z; px[3] = a.w;
       py[0] = b.x; py[1] = b.y; py[2] = b.z; py[3] = b.w;
@@ -403,14 +409,21 @@ constexpr int kRecordThreads = 256;
 __global__ void __launch_bounds__(kRecordThreads)
 record_build_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
-                    int64_t n, float4* __restrict__ records, const int32_t* __restrict__ run_if) {
+                    PushSpec push, int64_t n, float4* __restrict__ records,
+                    const int32_t* __restrict__ run_if) {
   if (run_if && *run_if == 0) return;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kRecordThreads;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kRecordThreads + threadIdx.x; i < n;
        i += stride) {
-    const float vx = v ? __ldcs(v + i) : 0.f, vy = v ? __ldcs(v + padded + i) : 0.f;
-    const float vz = v ? __ldcs(v + 2 * padded + i) : 0.f;
-    records[2 * i] = make_float4(__ldcs(x + i), __ldcs(y + i), __ldcs(z + i), vx);
+    float vx = v ? __ldcs(v + i) : 0.f, vy = v ? __ldcs(v + padded + i) : 0.f;
+    float vz = v ? __ldcs(v + 2 * padded + i) : 0.f;
+    float px = __ldcs(x + i), py = __ldcs(y + i), pz = __ldcs(z + i);
+    if (push.enabled) {
+      push_axis(px, vx, push.dt, push.lo[0], push.hi[0]);
+      push_axis(py, vy, push.dt, push.lo[1], push.hi[1]);
+      push_axis(pz, vz, push.dt, push.lo[2], push.hi[2]);
+    }
+    records[2 * i] = make_float4(px, py, pz, vx);
     records[2 * i + 1] = make_float4(vy, vz, 0.f, 0.f);
   }
 }
@@ -508,16 +521,16 @@ cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t n
 }
 
 template <int PASSES>
-static void launch_keygen(const SortArgs& a, bool vec, uint32_t* keys, Header* hdr,
-                          const int32_t* run_if) {
+static void launch_keygen(const SortArgs& a, bool vec, const float4* records, uint32_t* keys,
+                          Header* hdr, const int32_t* run_if) {
   const int grid = grid_for(a.n, kKeygenChunk, 8);
   const uint32_t k0 = static_cast<uint32_t>(a.seed), k1 = static_cast<uint32_t>(a.seed >> 32);
   if (vec)
     keygen_upsweep_kernel<PASSES, true><<<grid, kKeygenThreads, 0, a.stream>>>(
-        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
+        a.x, a.y, a.z, records, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
   else
     keygen_upsweep_kernel<PASSES, false><<<grid, kKeygenThreads, 0, a.stream>>>(
-        a.x, a.y, a.z, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
+        a.x, a.y, a.z, records, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
 }
 
 cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
@@ -533,6 +546,23 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   const size_t keep = run_if ? 8 : 0;
   cudaError_t e = cudaMemsetAsync(base + keep, 0, l.keys_alt_off - keep, a.stream);
   if (e != cudaSuccess) return e;
+  // Payload records (one 32-byte sector per particle) behind the digit-pass arrays, when
+  // the workspace has room.  Key bits do not change where they start: a 32-bit layout's end.
+  const size_t records_off = standard_workspace_bytes(a.n, a.num_cells);
+  const bool have_records =
+      a.xs && a.n > 0 && a.workspace_bytes >= records_off + static_cast<size_t>(a.n) * 32;
+  float4* records = have_records ? reinterpret_cast<float4*>(base + records_off) : nullptr;
+  // With the fused move stage the records are built first and the keys come from them.
+  if (a.push.enabled && a.n > 0 && !have_records) return cudaErrorInvalidValue;
+  const float4* moved = nullptr;
+  if (a.push.enabled && a.n > 0) {
+    stage_begin(kStagePush, a.stream);
+    record_build_kernel<<<grid_for(a.n, kRecordThreads, 8), kRecordThreads, 0, a.stream>>>(
+        a.x, a.y, a.z, a.velocity, a.padded, a.push, a.n, records, run_if);
+    stage_end(kStagePush, a.stream);
+    count_launches(1);
+    moved = records;
+  }
 
   if (a.n > 0) {
     e = cudaFuncSetAttribute(onesweep_pass_kernel<true>,
@@ -551,10 +581,10 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
     const bool vec = aligned16(a.x) && aligned16(a.y) && aligned16(a.z) && aligned16(cur_k);
     stage_begin(kStageKeygen, a.stream);
     switch (l.passes) {
-      case 1: launch_keygen<1>(a, vec, cur_k, hdr, run_if); break;
-      case 2: launch_keygen<2>(a, vec, cur_k, hdr, run_if); break;
-      case 3: launch_keygen<3>(a, vec, cur_k, hdr, run_if); break;
-      default: launch_keygen<4>(a, vec, cur_k, hdr, run_if); break;
+      case 1: launch_keygen<1>(a, vec, moved, cur_k, hdr, run_if); break;
+      case 2: launch_keygen<2>(a, vec, moved, cur_k, hdr, run_if); break;
+      case 3: launch_keygen<3>(a, vec, moved, cur_k, hdr, run_if); break;
+      default: launch_keygen<4>(a, vec, moved, cur_k, hdr, run_if); break;
     }
     stage_end(kStageKeygen, a.stream);
     count_launches(1);
@@ -588,16 +618,16 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   if (e != cudaSuccess) return e;
   if (a.xs) {
     stage_begin(kStageGather, a.stream);
-    // Key bits do not change the layout's size: the records start where a 32-bit layout ends.
-    const size_t records_off = standard_workspace_bytes(a.n, a.num_cells);
-    if (a.n > 0 && a.workspace_bytes >= records_off + static_cast<size_t>(a.n) * 32) {
-      float4* records = reinterpret_cast<float4*>(base + records_off);
+    if (have_records) {
       const int grid = grid_for(a.n, kRecordThreads, 8);
-      record_build_kernel<<<grid, kRecordThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity,
-                                                                  a.padded, a.n, records, run_if);
+      if (!moved) {
+        record_build_kernel<<<grid, kRecordThreads, 0, a.stream>>>(
+            a.x, a.y, a.z, a.velocity, a.padded, a.push, a.n, records, run_if);
+        count_launches(1);
+      }
       record_gather_kernel<<<grid, kRecordThreads, 0, a.stream>>>(
           a.index_out, a.n, records, a.xs, a.ys, a.zs, a.vs, a.padded_sorted, run_if);
-      count_launches(2);
+      count_launches(1);
       e = cudaGetLastError();
     } else {
       e = launch_gather(a.index_out, a.n, a.x, a.y, a.z, a.velocity, a.padded, a.xs, a.ys, a.zs,

@@ -2,8 +2,8 @@
 
 Mirror of project_aether/src/physics_engine/dsmc_gpu_pipeline.py (`GpuDsmcState`
 :49-77, `GpuStepStats` :80-82, `gpu_dsmc_step` :85-113).  The three stages are
-this library's kernels; the sort and the payload gather of lines 105-109 are
-one call, and the sorted state of one step is written into the arrays the
+this library's kernels; the move stage, the sort and the payload gather of
+lines 101-109 are one call, and the sorted state of one step is written into the arrays the
 step before last used, so a stepping loop allocates nothing after its second
 step.
 """
@@ -14,7 +14,7 @@ from typing import List, NamedTuple, Optional
 import numpy as np
 import torch
 
-from . import ntc_collide, particle_push, particle_sort
+from . import ntc_collide, particle_sort
 from .cell_grid import CellGrid
 
 
@@ -71,8 +71,8 @@ def gpu_dsmc_step(state: GpuDsmcState, library, grid: CellGrid,
       the state's buffers and are overwritten two steps later.
     """
     n = state.num_particles
-    vel = [state.velocity[c, :n] for c in range(3)]
-    particle_push.fused_particle_push(state.positions, vel, dt, grid.lo, grid.hi)
+    # The move stage (dsmc_gpu_pipeline.py:101-104) runs inside the sort's kernels: they read
+    # x and v once, move the particle and carry the moved state into the sorted arrays.
     # The sort seed of a step (dsmc_gpu_pipeline.py:106).
     seed = params.seed ^ (params.step << 20)
     # Two sets of arrays alternate: the step writes the sorted state into the set the
@@ -88,7 +88,7 @@ def gpu_dsmc_step(state: GpuDsmcState, library, grid: CellGrid,
                               or spare.order.cell_counts.numel() != grid.num_cells):
         spare = None
     out = particle_sort.sort_and_gather_particles(*state.positions, state.velocity, grid, seed,
-                                                  out=spare)
+                                                  out=spare, push=(dt, grid.lo, grid.hi))
     if held.order is None:
         held = particle_sort.SortedParticles(
             particle_sort.SortResult(*(torch.empty_like(t) for t in out.order)),

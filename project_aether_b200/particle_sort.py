@@ -144,7 +144,8 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
                               ix_offset: int = 0, nx_local: Optional[int] = None,
                               path: int = PATH_AUTO,
                               padded_out: Optional[int] = None,
-                              out: Optional[SortedParticles] = None) -> SortedParticles:
+                              out: Optional[SortedParticles] = None,
+                              push: Optional[tuple] = None) -> SortedParticles:
     """Sorts by cell and returns the particle payload in sorted order.
 
     One call for lines 105-109 of the reference's DSMC step
@@ -160,6 +161,11 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
       padded_out: row stride of the sorted velocity (default: that of the input).
       out: result tensors of an earlier call with the same sizes to write into
         instead of allocating (a stepping loop alternates between two sets).
+      push: (dt, lo, hi) to fuse the move stage into the sort: particles are taken
+        at x + v*dt with specular reflection at the box faces lo, hi (three floats
+        each; the arithmetic of `fused_particle_push`), and the sorted payload
+        carries the moved positions and reflected velocities.  The inputs are
+        not modified.
 
     Returns:
       SortedParticles(order, (x, y, z) sorted, velocity sorted (3, padded) with
@@ -201,11 +207,22 @@ def sort_and_gather_particles(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor,
         nbytes = lib.AetherSortWorkspaceBytes(n, cells, 1)
         ws = _workspace(device, nbytes)
         stream = torch.cuda.current_stream(device).cuda_stream
-        _native.check(lib.AetherSortAndGatherParticles(
-            _ptr(x), _ptr(y), _ptr(z), _ptr(velocity), padded, n, ctypes.byref(g),
-            int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(keys), _ptr(index), _ptr(counts), _ptr(start),
-            _ptr(xs), _ptr(ys), _ptr(zs), _ptr(vs), padded_sorted, int(path), _ptr(ws), ws.numel(),
-            ctypes.c_void_p(stream)), 'AetherSortAndGatherParticles')
+        if push is None:
+            _native.check(lib.AetherSortAndGatherParticles(
+                _ptr(x), _ptr(y), _ptr(z), _ptr(velocity), padded, n, ctypes.byref(g),
+                int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(keys), _ptr(index), _ptr(counts),
+                _ptr(start), _ptr(xs), _ptr(ys), _ptr(zs), _ptr(vs), padded_sorted, int(path),
+                _ptr(ws), ws.numel(), ctypes.c_void_p(stream)), 'AetherSortAndGatherParticles')
+        else:
+            dt, lo, hi = push
+            _native.check(lib.AetherPushSortAndGatherParticles(
+                _ptr(x), _ptr(y), _ptr(z), _ptr(velocity), padded, n, float(dt),
+                (ctypes.c_float * 3)(*[float(v) for v in lo]),
+                (ctypes.c_float * 3)(*[float(v) for v in hi]), ctypes.byref(g),
+                int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(keys), _ptr(index), _ptr(counts),
+                _ptr(start), _ptr(xs), _ptr(ys), _ptr(zs), _ptr(vs), padded_sorted, int(path),
+                _ptr(ws), ws.numel(), ctypes.c_void_p(stream)),
+                'AetherPushSortAndGatherParticles')
     return SortedParticles(SortResult(keys, index, counts, start), (xs, ys, zs), vs)
 
 
@@ -224,3 +241,21 @@ def last_sort_status(device=None) -> int:
         _native.check(lib.AetherSortReadStatus(_ptr(ws), ctypes.c_void_p(key[1]),
                                                ctypes.byref(status)), 'AetherSortReadStatus')
     return status.value
+
+
+def last_sort_used_digit_passes(device=None) -> bool:
+    """Synchronises and tells whether the last sort on the current stream of
+    `device` was handed from the bucketed path to the digit passes on the device
+    (same results, slower)."""
+    device = torch.device('cuda', torch.cuda.current_device()) if device is None else device
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        return False
+    lib = _native.load_library()
+    used = ctypes.c_int32(0)
+    with torch.cuda.device(device):
+        _native.check(lib.AetherSortReadUsedDigitPasses(_ptr(ws), ctypes.c_void_p(key[1]),
+                                                        ctypes.byref(used)),
+                      'AetherSortReadUsedDigitPasses')
+    return bool(used.value)

@@ -150,6 +150,37 @@ def test_more_than_255_equal_keys_in_a_bucket(cuda):
     x[same], y[same], z[same] = 0.51, 0.52, 0.53  # one cell, one shuffle value
     got = _check_all(x, y, z, vel, grid, seed, pa.PATH_AUTO)
     assert int(got.order.cell_counts.max()) >= int(same.sum())
+    assert pa.last_sort_used_digit_passes(cuda)
+
+
+@pytest.mark.parametrize('n,cells,dense', [(600_000, (64, 64, 32), 0.02), (2_000_003, (128, 64, 64), 0.03),
+                                           (1_200_000, (16, 16, 16), 0.05)])
+def test_dense_layer_overfills_buckets_without_leaving_the_bucketed_path(cuda, n, cells, dense):
+    """Bucket widths are planned from the average load.  A density contrast across rows
+    (70 % of the particles in a thin y-layer) puts several times the shared-memory capacity
+    into the buckets of that layer; the finish kernel cuts such a bucket into runs of cells
+    that fit.  Results stay bit-exact and the digit passes are not needed."""
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), cells)
+    x, y, z, vel = _random_state(n, grid, cuda, seed=13)
+    layer = torch.rand(n, device=cuda, generator=torch.Generator(device=cuda).manual_seed(14)) < 0.7
+    y[layer] = 0.5 + dense * (y[layer] - 0.5)
+    got = _check_all(x, y, z, vel, grid, 77, pa.PATH_AUTO, big=True)
+    assert not pa.last_sort_used_digit_passes(cuda)
+    # The layer really overfills buckets: with the library's bucket width (the largest
+    # 2^s <= 1024 cells with an average of at most 4224 particles and at least 1024 buckets)
+    # some bucket holds more than the 5376 records of the finish kernel's shared memory.
+    counts = got.order.cell_counts.cpu().numpy().astype(np.int64)
+    shift = next(s for s in range(10, -1, -1)
+                 if s == 0 or (n <= 4224 * -(-counts.size >> s) and -(-counts.size >> s) >= 1024))
+    per_bucket = np.add.reduceat(counts, np.arange(0, counts.size, 1 << shift))
+    assert per_bucket.max() > 5376
+
+
+def test_uniform_input_does_not_use_the_digit_passes(cuda):
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (64, 64, 64))
+    x, y, z, vel = _random_state(1 << 20, grid, cuda, seed=3)
+    _check_all(x, y, z, vel, grid, 1, pa.PATH_AUTO, big=True)
+    assert not pa.last_sort_used_digit_passes(cuda)
 
 
 @pytest.mark.parametrize('path', PATHS)
