@@ -36,33 +36,44 @@ __device__ __forceinline__ void load8(const float* p, int64_t i0, int64_t n, boo
   }
 }
 
+// One warp counts one tile of 2048 particles: eight rounds of 32 lanes x 8
+// particles, per-lane counts of the eight destinations packed 16 bits apart
+// (at most 64 per lane, 2048 per warp), summed over the warp with four
+// hardware reductions.  No shared memory and no block barrier; a warp walks
+// over tiles grid-wide, so the kernel streams x at memory speed.
 __global__ void __launch_bounds__(kSlabThreads)
 slab_count_kernel(const float* __restrict__ x, int64_t n, AetherGrid g, int slab_width, int world,
-                  bool vec, uint32_t* __restrict__ tile_count) {
-  __shared__ uint32_t count[kMaxWorld];
-  if (threadIdx.x < kMaxWorld) count[threadIdx.x] = 0;
-  __syncthreads();
-  const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * kSlabThreads + threadIdx.x) * kSlabItems;
-  float px[kSlabItems];
-  load8(x, i0, n, vec, px);
-  uint32_t mine[kMaxWorld] = {0, 0, 0, 0, 0, 0, 0, 0};
+                  bool vec, int tiles, uint32_t* __restrict__ tile_count) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = kSlabThreads / 32;
+  const int warp_global = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int warp_stride = gridDim.x * warps_per_block;
+  for (int tile = warp_global; tile < tiles; tile += warp_stride) {
+    uint32_t packed[4] = {0, 0, 0, 0};  // destinations (0,1) (2,3) (4,5) (6,7)
+    const int64_t tile_first = static_cast<int64_t>(tile) * kSlabTile;
 #pragma unroll
-  for (int k = 0; k < kSlabItems; ++k)
-    if (i0 + k < n) {
-      const int d = slab_of(px[k], g, slab_width);
+    for (int round = 0; round < kSlabTile / (32 * kSlabItems); ++round) {
+      const int64_t i0 = tile_first + (static_cast<int64_t>(round) * 32 + lane) * kSlabItems;
+      if (i0 >= n) continue;
+      float px[kSlabItems];
+      load8(x, i0, n, vec, px);
 #pragma unroll
-      for (int w = 0; w < kMaxWorld; ++w) mine[w] += (d == w);
+      for (int k = 0; k < kSlabItems; ++k)
+        if (i0 + k < n) {
+          const int d = slab_of(px[k], g, slab_width);
+#pragma unroll
+          for (int w = 0; w < 4; ++w) packed[w] += (d >> 1) == w ? 1u << (16 * (d & 1)) : 0u;
+        }
     }
 #pragma unroll
-  for (int w = 0; w < kMaxWorld; ++w) {
-    uint32_t c = mine[w];
+    for (int w = 0; w < 4; ++w) packed[w] = __reduce_add_sync(0xffffffffu, packed[w]);
+    if (lane < world) {
+      uint32_t word = packed[0];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_down_sync(0xffffffffu, c, o);
-    if ((threadIdx.x & 31) == 0 && c) atomicAdd(&count[w], c);
+      for (int w = 1; w < 4; ++w) word = (lane >> 1) == w ? packed[w] : word;
+      tile_count[static_cast<size_t>(lane) * tiles + tile] = (word >> (16 * (lane & 1))) & 0xffffu;
+    }
   }
-  __syncthreads();
-  if (threadIdx.x < world)
-    tile_count[static_cast<size_t>(threadIdx.x) * gridDim.x + blockIdx.x] = count[threadIdx.x];
 }
 
 // tile_count is [world][tiles].  Its exclusive scan in that order is the output
@@ -302,7 +313,9 @@ cudaError_t slab_count(const float* x, int64_t n, const AetherGrid& g, int world
   const int blocks = static_cast<int>((entries + kScanBlock - 1) / kScanBlock);
   uint32_t* block_sum = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) +
                                                     align_up(entries * sizeof(uint32_t), 256));
-  slab_count_kernel<<<tiles, kSlabThreads, 0, stream>>>(x, n, g, g.nx / world, world, vec,
+  const int count_grid = std::max(1, std::min((tiles + kSlabThreads / 32 - 1) / (kSlabThreads / 32),
+                                              148 * 8));
+  slab_count_kernel<<<count_grid, kSlabThreads, 0, stream>>>(x, n, g, g.nx / world, world, vec, tiles,
                                                         tile_count);
   slab_scan_local_kernel<<<blocks, kScanBlock, 0, stream>>>(tile_count, entries, block_sum);
   slab_scan_blocks_kernel<<<1, kScanBlock, 0, stream>>>(tile_count, block_sum, blocks, tiles, world,

@@ -1,6 +1,7 @@
 """Runs a few sort calls on a small seeded case, for profiling under ncu.
 
     python -m project_aether_b200.profile_case --workload c3_64m_hypersonic --log2n 24 --calls 2
+    python -m project_aether_b200.profile_case --workload c5_128m_256 --log2n 24 --calls 2 --collide
 
 The case keeps the workload's grid shape but scales the z extent of the grid
 with the particle count so that particles per cell stay what the full
@@ -30,14 +31,26 @@ def main():
     ap.add_argument('--log2n', type=int, default=24)
     ap.add_argument('--calls', type=int, default=2)
     ap.add_argument('--path', default='auto', choices=['auto', 'digits'])
+    ap.add_argument('--collide', action='store_true',
+                    help='also run the collision stage on the sorted output of every call')
     args = ap.parse_args()
     w = scaled_case(args.workload, args.log2n)
     device = torch.device('cuda', 0)
     x, y, z, v = workloads.make_particles(w, device, seed=0)
     path = particle_sort.PATH_AUTO if args.path == 'auto' else particle_sort.PATH_DIGIT_PASSES
+    if args.collide:
+        # Unit thermal speed: sigma*g = g^0.46 below the majorant 3; about one candidate pair
+        # per two cells at 8 particles per cell.
+        from . import ntc_collide
+        lib = ntc_collide.load_library()
+        sigma_g_max = torch.full((w.grid.num_cells,), 3.0, dtype=torch.float32, device=device)
+        collisions = torch.zeros(w.grid.num_cells, dtype=torch.int32, device=device)
     for s in range(args.calls):
         out = particle_sort.sort_and_gather_particles(x, y, z, v, w.grid, workloads.step_seed(1234, s),
                                                       path=path)
+        if args.collide:
+            ntc_collide.collide(lib, out.velocity, out.order.cell_start, sigma_g_max, collisions,
+                                w.n, ntc_collide.CollisionParams(0.006, 1.0, 0.46, 1234, s))
     torch.cuda.synchronize()
     status = particle_sort.last_sort_status(device)
     print(f'{w.name} n={w.n} cells={w.grid.cells} status={status} '
