@@ -9,6 +9,7 @@ fixture share.
 
 import ctypes
 import os
+import subprocess
 from typing import NamedTuple
 
 import numpy as np
@@ -31,7 +32,11 @@ class CollideCase(NamedTuple):
 def _clib():
     global _LIB
     if _LIB is None:
-        lib = ctypes.CDLL(os.path.join(_HERE, 'libcollide_oracle.so'))
+        path = os.path.join(_HERE, 'libcollide_oracle.so')
+        if not os.path.exists(path):  # a fresh checkout: build it (gcc, a second)
+            subprocess.run(['make', '-C', _HERE, 'libcollide_oracle.so'], check=True,
+                           capture_output=True)
+        lib = ctypes.CDLL(path)
         lib.collide_cells.restype = None
         lib.collide_cells.argtypes = ([ctypes.c_void_p] * 4 + [ctypes.c_int32, ctypes.c_int64] +
                                       [ctypes.c_float] * 3 + [ctypes.c_uint64] * 2 + [ctypes.c_void_p])
