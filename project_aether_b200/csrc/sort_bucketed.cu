@@ -451,9 +451,14 @@ struct FinishOut {
 // first_cell + cells_here - 1; `low_base` is the low key (bits below the bucket
 // id) of the first of these cells.  s.hist must be zero over the counters used.
 // Returns false if a byte counter wrapped (more than 255 records on one counter).
+// DROP: the number of low key bits the counters leave out, fixed at compile time
+// (0, 1, 2) or -1 to take it from `drop_at_run_time`.
+template <int DROP>
 __device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out, int count,
                                             uint32_t begin, int64_t first_cell, int cells_here,
-                                            uint32_t low_base, uint32_t low_mask, int drop) {
+                                            uint32_t low_base, uint32_t low_mask,
+                                            int drop_at_run_time) {
+  const int drop = DROP >= 0 ? DROP : drop_at_run_time;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t drop_mask = (1u << drop) - 1;
   const int cell_words = 32 >> drop;  // counter words per cell
@@ -697,13 +702,14 @@ __device__ bool finish_large_bucket(FinishSmem& s, const FinishOut& out,
     const bool consistent = s.fill == static_cast<uint32_t>(seg_count);
     __syncthreads();
     if (!consistent) return false;
-    if (!sort_staged(s, out, seg_count, begin + seg_begin, first_cell + c0, c1 - c0,
-                     static_cast<uint32_t>(c0) << kShuffleBits, low_mask, drop))
+    if (!sort_staged<-1>(s, out, seg_count, begin + seg_begin, first_cell + c0, c1 - c0,
+                         static_cast<uint32_t>(c0) << kShuffleBits, low_mask, drop))
       return false;
   }
   return true;
 }
 
+template <int DROP>
 __global__ void __launch_bounds__(kFinishThreads, 1)
 bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __restrict__ bucket_start,
                      const uint32_t* __restrict__ run_start, const uint32_t* __restrict__ run_length,
@@ -718,7 +724,7 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
   // 1024 cells) are left to the tie step, which orders by (those bits, index).
   const int low_bits = shift + kShuffleBits;
   const uint32_t low_mask = (1u << low_bits) - 1;
-  const int drop = max(0, low_bits - kMaxLowBits);
+  constexpr int drop = DROP;  // max(0, low_bits - kMaxLowBits), chosen by the launcher
   const int hist_words = max(8, (1 << (low_bits - drop)) / 4);
 
   if (tid == 0) {
@@ -761,13 +767,7 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
     const int cells_here = static_cast<int>(
         min(static_cast<long long>(1) << shift, static_cast<long long>(num_cells - first_cell)));
     if (b == buckets - 1 && tid == 0) out.cell_start[num_cells] = static_cast<int32_t>(n);
-    if (count > kFinishCapacity) {
-      if (!finish_large_bucket(s, out, records, run_start, run_length, chunks, b, begin, count,
-                               first_cell, cells_here, low_mask, drop)) {
-        if (tid == 0) hdr->use_standard = 1;
-      }
-      continue;
-    }
+    if (count > kFinishCapacity) continue;  // bucket_finish_large_kernel's job
     // The bucket lies in HBM as one contiguous run of 32-byte records per chunk
     // (a single run when there is one chunk): fetch the runs back to back into
     // shared memory with bulk copies while the counters are cleared.  Warp 0
@@ -819,8 +819,38 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
       if (tid == 0) atomicCAS(&hdr->error, 0, kErrBulkCopyTimeout);
       return;
     }
-    if (!sort_staged(s, out, count, begin, first_cell, cells_here, 0u, low_mask, drop)) {
+    if (!sort_staged<DROP>(s, out, count, begin, first_cell, cells_here, 0u, low_mask, drop)) {
       if (tid == 0) hdr->use_standard = 1;
+    }
+  }
+}
+
+// The buckets the kernel above skipped: those with more records than its shared
+// memory holds.  Usually there are none and every block returns after a look at
+// its share of the bucket table.
+__global__ void __launch_bounds__(kFinishThreads, 1)
+bucket_finish_large_kernel(const uint32_t* __restrict__ records,
+                           const uint32_t* __restrict__ bucket_start,
+                           const uint32_t* __restrict__ run_start,
+                           const uint32_t* __restrict__ run_length, int chunks, int buckets,
+                           int shift, int64_t num_cells, FinishOut out, Header* __restrict__ hdr) {
+  if (hdr->use_standard || hdr->max_bucket <= static_cast<uint32_t>(kFinishCapacity)) return;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  FinishSmem& s = *reinterpret_cast<FinishSmem*>(smem_raw);
+  const int low_bits = shift + kShuffleBits;
+  const uint32_t low_mask = (1u << low_bits) - 1;
+  const int drop = max(0, low_bits - kMaxLowBits);
+  for (int b = blockIdx.x; b < buckets; b += gridDim.x) {
+    const uint32_t begin = bucket_start[b], end = bucket_start[b + 1];
+    const int count = static_cast<int>(end - begin);
+    if (count <= kFinishCapacity) continue;
+    const int64_t first_cell = static_cast<int64_t>(b) << shift;
+    const int cells_here = static_cast<int>(
+        min(static_cast<long long>(1) << shift, static_cast<long long>(num_cells - first_cell)));
+    if (!finish_large_bucket(s, out, records, run_start, run_length, chunks, b, begin, count,
+                             first_cell, cells_here, low_mask, drop)) {
+      if (threadIdx.x == 0) hdr->use_standard = 1;
+      return;
     }
   }
 }
@@ -995,16 +1025,27 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   count_launches(2);
 
   stage_begin(kStageBucketFinish, a.stream);
-  e = cudaFuncSetAttribute(bucket_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(sizeof(FinishSmem)));
-  if (e != cudaSuccess) return e;
   const FinishOut out{a.keys_out, a.index_out, a.cell_counts, a.cell_start, a.xs, a.ys, a.zs,
                       a.vs, a.padded_sorted};
-  bucket_finish_kernel<<<std::min(buckets, kSmCount), kFinishThreads, sizeof(FinishSmem),
-                         a.stream>>>(records, start, run_start, run_length, l.chunks, buckets,
-                                     p.shift, a.n, a.num_cells, out, hdr);
+  {
+    const int drop = std::max(0, p.shift + kShuffleBits - kMaxLowBits);
+    auto kernel = drop == 0 ? bucket_finish_kernel<0>
+                            : drop == 1 ? bucket_finish_kernel<1> : bucket_finish_kernel<2>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(sizeof(FinishSmem)));
+    if (e != cudaSuccess) return e;
+    kernel<<<std::min(buckets, kSmCount), kFinishThreads, sizeof(FinishSmem), a.stream>>>(
+        records, start, run_start, run_length, l.chunks, buckets, p.shift, a.n, a.num_cells, out,
+        hdr);
+  }
+  e = cudaFuncSetAttribute(bucket_finish_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(sizeof(FinishSmem)));
+  if (e != cudaSuccess) return e;
+  bucket_finish_large_kernel<<<std::min(buckets, kSmCount), kFinishThreads, sizeof(FinishSmem),
+                               a.stream>>>(records, start, run_start, run_length, l.chunks,
+                                           buckets, p.shift, a.num_cells, out, hdr);
   stage_end(kStageBucketFinish, a.stream);
-  count_launches(1);
+  count_launches(2);
   return cudaGetLastError();
 }
 
