@@ -233,3 +233,17 @@ def test_gpu_dsmc_step_runs_the_three_stages(cuda):
         px = [p.cpu().numpy() for p in state.positions]
         pv = [state.velocity[c, :n].cpu().numpy() for c in range(3)]
         sigma = state.sigma_g_max.cpu().numpy()
+
+
+@pytest.mark.gpu
+def test_phase2_benchmark_cli(cuda, capsys):
+    """The command-line benchmark of the reference (scripts/phase2_triton_sort_benchmark.py)
+    on a small case: counts equal the CPU pipeline's, collisions equal the CPU replay's."""
+    from project_aether_b200 import phase2_benchmark
+    rc = phase2_benchmark.main(['--particles', '400000', '--cells', '25', '25', '16',
+                                '--cpu-threads', '4', '--repeats', '2', '--collisions',
+                                '--fnum', '3e14'])
+    out = capsys.readouterr().out
+    assert rc == 0
+    assert 'Per-cell counts identical: True' in out
+    assert 'Mean collisions per cell: GPU' in out and 'z = 0.0' in out
