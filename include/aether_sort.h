@@ -43,9 +43,12 @@ int AetherSortAbiVersion(void);
 
 /* Bytes of workspace needed by the sort entry points for `n` particles and
  * `num_cells` (slab-local) cells; `with_payload` != 0 when positions and
- * velocities are to be carried.  Replaces the per-call tensor allocations of
- * the reference driver (fused_radix_sort.py:245-248,257-263).  Returns 0 if the
- * arguments are out of range (n < 0, n >= 2^30, key wider than 32 bits). */
+ * velocities are to be carried (about 40 bytes per particle, 32 without).
+ * Replaces the per-call tensor allocations of the reference driver
+ * (fused_radix_sort.py:245-248,257-263).  A smaller workspace is accepted as
+ * long as the digit passes fit (8 bytes per particle plus status words); the
+ * call then runs the slower of its paths.  Returns 0 if the arguments are out
+ * of range (n < 0, n >= 2^30, key wider than 32 bits). */
 size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload);
 
 /* sort_particles_by_cell (fused_radix_sort.py:221-280): sorted keys,
