@@ -1,8 +1,14 @@
 """The N > 1 leg of bench.py: one rank per GPU, x-slab decomposition.
 
-Every rank starts with a random 1/G share of all particles drawn over the whole
-box (generator seed 0 + rank), so (G-1)/G of them must leave in the exchange.
-One step = partition by slab, count exchange, all-to-all, local sort.
+Default workload (256 M particles): every rank starts with a random 1/G share of
+all particles drawn over the whole box (generator seed 0 + rank), so (G-1)/G of
+them must leave in the exchange.  One step = partition by slab, count exchange,
+all-to-all, local sort.
+
+Steady-state workload (`c5...`): every rank starts with the cell-sorted
+particles of its own slab; one step = move stage (x += v*dt, specular walls),
+then the same distributed sort, whose output is the next step's input.  Only
+the particles that crossed a slab face travel.
 """
 
 import ctypes
@@ -33,10 +39,31 @@ def run(args, workload: str) -> None:
     x, y, z, v = workloads.make_particles(w, device, seed=rank, n=n_local)
 
     exchange = os.environ.get('AETHER_EXCHANGE', 'peer')  # 'peer' (NVLink stores) or 'nccl'
+    steady = workload.startswith('c5')
+    steady_dt = 8.2e-5  # about 5 % of the particles change cell per step
+    state = {'x': x, 'y': y, 'z': z, 'v': v}
+    if steady:
+        # Squeeze this rank's share into its own slab, then sort it once: the loop starts
+        # from a cell-sorted state in which every particle is at home.
+        lo, hi = w.grid.lo[0], w.grid.hi[0]
+        width = (hi - lo) / world
+        x.sub_(lo).div_(world).add_(lo + rank * width).clamp_(max=lo + (rank + 1) * width * (1 - 1e-7))
+        first = slab_sort.distributed_sort(x, y, z, v, w.grid, 99, exchange=exchange)
+        state = {'x': first.positions[0], 'y': first.positions[1], 'z': first.positions[2],
+                 'v': first.velocity}
+        del first
 
     def step(s):
-        return slab_sort.distributed_sort(x, y, z, v, w.grid, workloads.step_seed(1234, s),
-                                          exchange=exchange)
+        if steady:
+            m = state['x'].numel()
+            pa.fused_particle_push([state['x'], state['y'], state['z']],
+                                   [state['v'][k, :m] for k in range(3)], steady_dt,
+                                   w.grid.lo, w.grid.hi)
+        r = slab_sort.distributed_sort(state['x'], state['y'], state['z'], state['v'], w.grid,
+                                       workloads.step_seed(1234, s), exchange=exchange)
+        if steady:
+            state.update(x=r.positions[0], y=r.positions[1], z=r.positions[2], v=r.velocity)
+        return r
 
     warmup = max(3, args.warmup)
     for s in range(warmup):
@@ -73,8 +100,13 @@ def run(args, workload: str) -> None:
               if stage_ms[i] >= 0}
     # Phase times of one more step (events on the stream; the count exchange includes a host wait).
     marks = []
-    slab_sort.distributed_sort(x, y, z, v, w.grid, workloads.step_seed(1234, 999), marks=marks,
-                               exchange=exchange)
+    if steady:
+        m = state['x'].numel()
+        pa.fused_particle_push([state['x'], state['y'], state['z']],
+                               [state['v'][k, :m] for k in range(3)], steady_dt,
+                               w.grid.lo, w.grid.hi)
+    slab_sort.distributed_sort(state['x'], state['y'], state['z'], state['v'], w.grid,
+                               workloads.step_seed(1234, 999), marks=marks, exchange=exchange)
     torch.cuda.synchronize()
     phases = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) for i in range(1, len(marks))}
     received = torch.tensor([out.order.keys.numel()], device=device, dtype=torch.int64)
@@ -83,6 +115,10 @@ def run(args, workload: str) -> None:
 
     # End to end: pinned host inputs in, results back to the host, every step.
     e2e_steps = max(1, min(args.steps, 3))
+    if steady:
+        m = state['x'].numel()
+        x, y, z = state['x'], state['y'], state['z']
+        v = state['v'][:, :m].contiguous()
     hx, hy, hz, hv = (t.cpu().pin_memory() for t in (x, y, z, v))
     d2h = [0]
     pinned = {}
@@ -118,7 +154,7 @@ def run(args, workload: str) -> None:
     # Strong-scaling denominator: the same workload, whole, on one GPU (rank 0 alone).
     single = None
     del hx, hy, hz, hv
-    if rank == 0:
+    if rank == 0 and not steady:  # (the steady-state loop at one GPU is `bench.py --workload c5...`)
         ax, ay, az, av = workloads.make_particles(w, device, seed=0)
         for s in range(2):
             pa.sort_and_gather_particles(ax, ay, az, av, w.grid, workloads.step_seed(1234, s))
@@ -168,7 +204,9 @@ def run(args, workload: str) -> None:
                        'exchange': ('partition kernel stores into the peers\' receive buffers '
                                     'over NVLink' if exchange == 'peer'
                                     else 'one NCCL all-to-all per payload array'),
-                       'initial_share': 'random 1/G of all particles per rank',
+                       'initial_share': ('cell-sorted particles of the rank\'s own slab; every step '
+                                         'moves them (dt %g) and re-sorts' % steady_dt if steady
+                                         else 'random 1/G of all particles per rank'),
                        'l2': 'inputs larger than L2 (no flush needed)'},
             'clocks': {'sm_mhz': clocks['sm_mhz'], 'sm_max_mhz': clocks['sm_max_mhz'],
                        'reasons': clocks['reasons'], 'samples': clocks['samples']},
