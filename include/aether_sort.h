@@ -142,6 +142,24 @@ int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
                               const int64_t* count_matrix, int32_t* error_out, void* workspace,
                               size_t workspace_bytes, void* stream);
 
+/* The two exchange calls with the move stage fused in: particles are counted
+ * and sent as they are after x += v*dt with specular reflection at lo/hi (the
+ * arithmetic of AetherParticlePush; `vx` is the first row of the velocity
+ * array, `lo`, `hi` host pointers to three floats).  The receiving rank's sort
+ * then needs no move.  The input arrays are not modified.  (New, like the
+ * exchange itself.) */
+int AetherSlabExchangeCountMoved(const float* x, const float* vx, int64_t n, float dt,
+                                 const float* lo, const float* hi, const AetherGrid* grid,
+                                 int world, int64_t* counts_out, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+int AetherSlabExchangeScatterMoved(const float* x, const float* y, const float* z,
+                                   const float* velocity, int64_t padded, int64_t n, float dt,
+                                   const float* lo, const float* hi, const AetherGrid* grid,
+                                   int world, int rank, float* const* peer_buffers,
+                                   int64_t capacity, const int64_t* count_matrix,
+                                   int32_t* error_out, void* workspace, size_t workspace_bytes,
+                                   void* stream);
+
 /* The move stage that precedes the sort in the DSMC step: x += v*dt, specular
  * reflection at the six walls, in place (fused_particle_push,
  * project_aether/src/custom_kernels/triton/fused_particle_push.py:75-92; arithmetic

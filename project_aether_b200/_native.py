@@ -56,6 +56,17 @@ _SIGNATURES = {
                                                  ctypes.POINTER(AetherGrid), ctypes.c_int,
                                                  ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
                                                  _I64, _P, _P, _P, ctypes.c_size_t, _P]),
+    'AetherSlabExchangeCountMoved': (ctypes.c_int, [_P, _P, _I64, ctypes.c_float,
+                                                    ctypes.POINTER(ctypes.c_float),
+                                                    ctypes.POINTER(ctypes.c_float),
+                                                    ctypes.POINTER(AetherGrid), ctypes.c_int, _P, _P,
+                                                    ctypes.c_size_t, _P]),
+    'AetherSlabExchangeScatterMoved': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.c_float,
+                                                      ctypes.POINTER(ctypes.c_float),
+                                                      ctypes.POINTER(ctypes.c_float),
+                                                      ctypes.POINTER(AetherGrid), ctypes.c_int,
+                                                      ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                                      _I64, _P, _P, _P, ctypes.c_size_t, _P]),
     'AetherParticlePush': (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _I64, ctypes.c_float,
                                           ctypes.POINTER(ctypes.c_float),
                                           ctypes.POINTER(ctypes.c_float), _P]),

@@ -300,13 +300,49 @@ extern "C" int AetherDsmcCollideTma(float* velocity, const int* cell_start, floa
                        vhs_speed_exponent, seed, step, static_cast<cudaStream_t>(stream));
 }
 
+namespace aether {
+namespace {
+PushSpec push_spec(float dt, const float* lo, const float* hi) {
+  PushSpec push{};
+  push.enabled = 1;
+  push.dt = dt;
+  for (int c = 0; c < 3; ++c) {
+    push.lo[c] = lo[c];
+    push.hi[c] = hi[c];
+  }
+  return push;
+}
+
+int exchange_count(const float* x, const float* vx, const PushSpec& push, int64_t n,
+                   const AetherGrid* grid, int world, int64_t* counts_out, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+  if (!count_ok(n) || !grid_ok(grid) || !counts_out || !workspace) return cudaErrorInvalidValue;
+  if (n > 0 && !x) return cudaErrorInvalidValue;
+  return slab_exchange_count(x, vx, push, n, *grid, world, counts_out, workspace, workspace_bytes,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int exchange_scatter(const float* x, const float* y, const float* z, const float* velocity,
+                     int64_t padded, int64_t n, const AetherGrid* grid, int world, int rank,
+                     float* const* peer_buffers, int64_t capacity, const int64_t* count_matrix,
+                     int32_t* error_out, const PushSpec& push, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  if (!count_ok(n) || !grid_ok(grid) || !peer_buffers || !count_matrix || !error_out || !workspace)
+    return cudaErrorInvalidValue;
+  if (capacity <= 0 || capacity % 4 != 0 || world < 1 || world > 8) return cudaErrorInvalidValue;
+  if (n > 0 && (!x || !y || !z || !velocity || padded < n)) return cudaErrorInvalidValue;
+  return slab_exchange_scatter(x, y, z, velocity, padded, n, *grid, world, rank, peer_buffers,
+                               capacity, count_matrix, error_out, push, workspace,
+                               workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+}  // namespace aether
+
 extern "C" int AetherSlabExchangeCount(const float* x, int64_t n, const AetherGrid* grid, int world,
                                        int64_t* counts_out, void* workspace,
                                        size_t workspace_bytes, void* stream) {
-  if (!count_ok(n) || !grid_ok(grid) || !counts_out || !workspace) return cudaErrorInvalidValue;
-  if (n > 0 && !x) return cudaErrorInvalidValue;
-  return slab_exchange_count(x, n, *grid, world, counts_out, workspace, workspace_bytes,
-                             static_cast<cudaStream_t>(stream));
+  return exchange_count(x, nullptr, PushSpec{}, n, grid, world, counts_out, workspace,
+                        workspace_bytes, stream);
 }
 
 extern "C" int AetherSlabExchangeScatter(const float* x, const float* y, const float* z,
@@ -315,11 +351,27 @@ extern "C" int AetherSlabExchangeScatter(const float* x, const float* y, const f
                                          float* const* peer_buffers, int64_t capacity,
                                          const int64_t* count_matrix, int32_t* error_out,
                                          void* workspace, size_t workspace_bytes, void* stream) {
-  if (!count_ok(n) || !grid_ok(grid) || !peer_buffers || !count_matrix || !error_out || !workspace)
-    return cudaErrorInvalidValue;
-  if (capacity <= 0 || capacity % 4 != 0 || world < 1 || world > 8) return cudaErrorInvalidValue;
-  if (n > 0 && (!x || !y || !z || !velocity || padded < n)) return cudaErrorInvalidValue;
-  return slab_exchange_scatter(x, y, z, velocity, padded, n, *grid, world, rank, peer_buffers,
-                               capacity, count_matrix, error_out, workspace, workspace_bytes,
-                               static_cast<cudaStream_t>(stream));
+  return exchange_scatter(x, y, z, velocity, padded, n, grid, world, rank, peer_buffers, capacity,
+                          count_matrix, error_out, PushSpec{}, workspace, workspace_bytes, stream);
+}
+
+extern "C" int AetherSlabExchangeCountMoved(const float* x, const float* vx, int64_t n, float dt,
+                                            const float* lo, const float* hi,
+                                            const AetherGrid* grid, int world,
+                                            int64_t* counts_out, void* workspace,
+                                            size_t workspace_bytes, void* stream) {
+  if (!lo || !hi || (n > 0 && !vx)) return cudaErrorInvalidValue;
+  return exchange_count(x, vx, push_spec(dt, lo, hi), n, grid, world, counts_out, workspace,
+                        workspace_bytes, stream);
+}
+
+extern "C" int AetherSlabExchangeScatterMoved(
+    const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
+    int64_t n, float dt, const float* lo, const float* hi, const AetherGrid* grid, int world,
+    int rank, float* const* peer_buffers, int64_t capacity, const int64_t* count_matrix,
+    int32_t* error_out, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!lo || !hi) return cudaErrorInvalidValue;
+  return exchange_scatter(x, y, z, velocity, padded, n, grid, world, rank, peer_buffers, capacity,
+                          count_matrix, error_out, push_spec(dt, lo, hi), workspace,
+                          workspace_bytes, stream);
 }

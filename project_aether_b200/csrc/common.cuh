@@ -243,14 +243,15 @@ cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t n
                                int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream,
                                const int32_t* run_if = nullptr);
 
-cudaError_t slab_exchange_count(const float* x, int64_t n, const AetherGrid& g, int world,
-                                int64_t* totals, void* workspace, size_t workspace_bytes,
-                                cudaStream_t stream);
+cudaError_t slab_exchange_count(const float* x, const float* vx, const PushSpec& push, int64_t n,
+                                const AetherGrid& g, int world, int64_t* totals, void* workspace,
+                                size_t workspace_bytes, cudaStream_t stream);
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
                                   int64_t padded, int64_t n, const AetherGrid& g, int world,
                                   int rank, float* const* peer_buffers, int64_t capacity,
-                                  const int64_t* count_matrix, int32_t* error, void* workspace,
-                                  size_t workspace_bytes, cudaStream_t stream);
+                                  const int64_t* count_matrix, int32_t* error,
+                                  const PushSpec& push, void* workspace, size_t workspace_bytes,
+                                  cudaStream_t stream);
 cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
                           float dt, const float* lo, const float* hi, cudaStream_t stream);
 cudaError_t collide_cells(float* velocity, const int* cell_start, float* sigma_g_max,

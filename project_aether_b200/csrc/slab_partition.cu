@@ -42,8 +42,9 @@ __device__ __forceinline__ void load8(const float* p, int64_t i0, int64_t n, boo
 // hardware reductions.  No shared memory and no block barrier; a warp walks
 // over tiles grid-wide, so the kernel streams x at memory speed.
 __global__ void __launch_bounds__(kSlabThreads)
-slab_count_kernel(const float* __restrict__ x, int64_t n, AetherGrid g, int slab_width, int world,
-                  bool vec, int tiles, uint32_t* __restrict__ tile_count) {
+slab_count_kernel(const float* __restrict__ x, const float* __restrict__ vx, PushSpec push,
+                  int64_t n, AetherGrid g, int slab_width, int world, bool vec, int tiles,
+                  uint32_t* __restrict__ tile_count) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = kSlabThreads / 32;
   const int warp_global = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -57,6 +58,12 @@ slab_count_kernel(const float* __restrict__ x, int64_t n, AetherGrid g, int slab
       if (i0 >= n) continue;
       float px[kSlabItems];
       load8(x, i0, n, vec, px);
+      if (push.enabled) {  // the destination of the particle as the fused move stage leaves it
+        float w[kSlabItems];
+        load8(vx, i0, n, vec, w);
+#pragma unroll
+        for (int k = 0; k < kSlabItems; ++k) push_axis(px[k], w[k], push.dt, push.lo[0], push.hi[0]);
+      }
 #pragma unroll
       for (int k = 0; k < kSlabItems; ++k)
         if (i0 + k < n) {
@@ -149,7 +156,7 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                     int64_t n, AetherGrid g, int slab_width, int world, bool vec,
                     const uint32_t* __restrict__ tile_offset,
-                    const uint32_t* __restrict__ block_sum, SlabTargets tg) {
+                    const uint32_t* __restrict__ block_sum, SlabTargets tg, PushSpec push) {
   extern __shared__ float stage_raw[];  // [6][kSlabTile]
   float (*stage)[kSlabTile] = reinterpret_cast<float (*)[kSlabTile]>(stage_raw);
   __shared__ unsigned long long warp_lo[8], warp_hi[8];
@@ -166,6 +173,14 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   load8(v, i0, n, vec && padded % 4 == 0, f[3]);
   load8(v + padded, i0, n, vec && padded % 4 == 0, f[4]);
   load8(v + 2 * padded, i0, n, vec && padded % 4 == 0, f[5]);
+  if (push.enabled) {  // fused move stage: the particle travels as it is after the move
+#pragma unroll
+    for (int k = 0; k < kSlabItems; ++k) {
+      push_axis(f[0][k], f[3][k], push.dt, push.lo[0], push.hi[0]);
+      push_axis(f[1][k], f[4][k], push.dt, push.lo[1], push.hi[1]);
+      push_axis(f[2][k], f[5][k], push.dt, push.lo[2], push.hi[2]);
+    }
+  }
   int dest[kSlabItems];
   // Per-thread counts of the eight destinations, 16 bits each in two words.
   unsigned long long lo = 0, hi = 0;
@@ -305,8 +320,9 @@ namespace {
 
 // Counts and scans: leaves the (destination, tile) offsets in the workspace and
 // the per-destination totals in `totals`.
-cudaError_t slab_count(const float* x, int64_t n, const AetherGrid& g, int world, bool vec,
-                       int64_t* totals, void* workspace, cudaStream_t stream) {
+cudaError_t slab_count(const float* x, const float* vx, const PushSpec& push, int64_t n,
+                       const AetherGrid& g, int world, bool vec, int64_t* totals, void* workspace,
+                       cudaStream_t stream) {
   const int tiles = static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
   uint32_t* tile_count = static_cast<uint32_t*>(workspace);
   const int64_t entries = static_cast<int64_t>(tiles) * world;
@@ -315,8 +331,8 @@ cudaError_t slab_count(const float* x, int64_t n, const AetherGrid& g, int world
                                                     align_up(entries * sizeof(uint32_t), 256));
   const int count_grid = std::max(1, std::min((tiles + kSlabThreads / 32 - 1) / (kSlabThreads / 32),
                                               148 * 8));
-  slab_count_kernel<<<count_grid, kSlabThreads, 0, stream>>>(x, n, g, g.nx / world, world, vec, tiles,
-                                                        tile_count);
+  slab_count_kernel<<<count_grid, kSlabThreads, 0, stream>>>(x, vx, push, n, g, g.nx / world, world,
+                                                             vec, tiles, tile_count);
   slab_scan_local_kernel<<<blocks, kScanBlock, 0, stream>>>(tile_count, entries, block_sum);
   slab_scan_blocks_kernel<<<1, kScanBlock, 0, stream>>>(tile_count, block_sum, blocks, tiles, world,
                                                         n, totals);
@@ -326,7 +342,8 @@ cudaError_t slab_count(const float* x, int64_t n, const AetherGrid& g, int world
 
 cudaError_t slab_scatter(const float* x, const float* y, const float* z, const float* v,
                          int64_t padded, int64_t n, const AetherGrid& g, int world, bool vec,
-                         const SlabTargets& tg, void* workspace, cudaStream_t stream) {
+                         const SlabTargets& tg, const PushSpec& push, void* workspace,
+                         cudaStream_t stream) {
   const int tiles = static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
   uint32_t* tile_count = static_cast<uint32_t*>(workspace);
   const int64_t entries = static_cast<int64_t>(tiles) * world;
@@ -337,7 +354,7 @@ cudaError_t slab_scatter(const float* x, const float* y, const float* z, const f
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
   if (e != cudaSuccess) return e;
   slab_scatter_kernel<<<tiles, kSlabThreads, kStageBytes, stream>>>(
-      x, y, z, v, padded, n, g, g.nx / world, world, vec, tile_count, block_sum, tg);
+      x, y, z, v, padded, n, g, g.nx / world, world, vec, tile_count, block_sum, tg, push);
   count_launches(1);
   return cudaGetLastError();
 }
@@ -353,7 +370,7 @@ cudaError_t slab_partition(const float* x, const float* y, const float* z, const
   if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
   stage_begin(kStageSlabPartition, stream);
-  cudaError_t e = slab_count(x, n, g, world, vec, totals, workspace, stream);
+  cudaError_t e = slab_count(x, nullptr, PushSpec{}, n, g, world, vec, totals, workspace, stream);
   if (e != cudaSuccess) return e;
   SlabTargets tg{};
   for (int d = 0; d < world; ++d) {
@@ -362,20 +379,22 @@ cudaError_t slab_partition(const float* x, const float* y, const float* z, const
   }
   tg.aligned = aligned16(ox) && aligned16(oy) && aligned16(oz) && aligned16(ovx) &&
                aligned16(ovy) && aligned16(ovz);
-  e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, workspace, stream);
+  e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, PushSpec{}, workspace, stream);
   stage_end(kStageSlabPartition, stream);
   return e;
 }
 
 // The two halves of the fused partition + exchange: count, then (after the
 // ranks have exchanged their counts) scatter straight into the peers' buffers.
-cudaError_t slab_exchange_count(const float* x, int64_t n, const AetherGrid& g, int world,
-                                int64_t* totals, void* workspace, size_t workspace_bytes,
-                                cudaStream_t stream) {
+cudaError_t slab_exchange_count(const float* x, const float* vx, const PushSpec& push, int64_t n,
+                                const AetherGrid& g, int world, int64_t* totals, void* workspace,
+                                size_t workspace_bytes, cudaStream_t stream) {
+  if (push.enabled && n > 0 && !vx) return cudaErrorInvalidValue;
   if (world < 1 || world > kMaxWorld || g.nx % world != 0) return cudaErrorInvalidValue;
   if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
   stage_begin(kStageSlabPartition, stream);
-  cudaError_t e = slab_count(x, n, g, world, aligned16(x), totals, workspace, stream);
+  const bool vec = aligned16(x) && (!push.enabled || aligned16(vx));
+  cudaError_t e = slab_count(x, vx, push, n, g, world, vec, totals, workspace, stream);
   stage_end(kStageSlabPartition, stream);
   return e;
 }
@@ -383,8 +402,9 @@ cudaError_t slab_exchange_count(const float* x, int64_t n, const AetherGrid& g, 
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
                                   int64_t padded, int64_t n, const AetherGrid& g, int world,
                                   int rank, float* const* peer_buffers, int64_t capacity,
-                                  const int64_t* count_matrix, int32_t* error, void* workspace,
-                                  size_t workspace_bytes, cudaStream_t stream) {
+                                  const int64_t* count_matrix, int32_t* error,
+                                  const PushSpec& push, void* workspace, size_t workspace_bytes,
+                                  cudaStream_t stream) {
   if (world < 1 || world > kMaxWorld || g.nx % world != 0) return cudaErrorInvalidValue;
   if (rank < 0 || rank >= world || !count_matrix || !error) return cudaErrorInvalidValue;
   if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
@@ -401,7 +421,7 @@ cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z
   }
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
   stage_begin(kStageSlabExchange, stream);
-  cudaError_t e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, workspace, stream);
+  cudaError_t e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, push, workspace, stream);
   stage_end(kStageSlabExchange, stream);
   return e;
 }

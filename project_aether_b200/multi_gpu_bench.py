@@ -6,8 +6,9 @@ them must leave in the exchange.  One step = partition by slab, count exchange,
 all-to-all, local sort.
 
 Steady-state workload (`c5...`): every rank starts with the cell-sorted
-particles of its own slab; one step = move stage (x += v*dt, specular walls),
-then the same distributed sort, whose output is the next step's input.  Only
+particles of its own slab; one step = the same distributed sort with the move
+stage (x += v*dt, specular walls) fused into its exchange kernels; its output
+is the next step's input.  Only
 the particles that crossed a slab face travel.
 """
 
@@ -53,14 +54,11 @@ def run(args, workload: str) -> None:
                  'v': first.velocity}
         del first
 
+    move = (steady_dt, w.grid.lo, w.grid.hi) if steady else None
+
     def step(s):
-        if steady:
-            m = state['x'].numel()
-            pa.fused_particle_push([state['x'], state['y'], state['z']],
-                                   [state['v'][k, :m] for k in range(3)], steady_dt,
-                                   w.grid.lo, w.grid.hi)
         r = slab_sort.distributed_sort(state['x'], state['y'], state['z'], state['v'], w.grid,
-                                       workloads.step_seed(1234, s), exchange=exchange)
+                                       workloads.step_seed(1234, s), exchange=exchange, push=move)
         if steady:
             state.update(x=r.positions[0], y=r.positions[1], z=r.positions[2], v=r.velocity)
         return r
@@ -100,13 +98,9 @@ def run(args, workload: str) -> None:
               if stage_ms[i] >= 0}
     # Phase times of one more step (events on the stream; the count exchange includes a host wait).
     marks = []
-    if steady:
-        m = state['x'].numel()
-        pa.fused_particle_push([state['x'], state['y'], state['z']],
-                               [state['v'][k, :m] for k in range(3)], steady_dt,
-                               w.grid.lo, w.grid.hi)
     slab_sort.distributed_sort(state['x'], state['y'], state['z'], state['v'], w.grid,
-                               workloads.step_seed(1234, 999), marks=marks, exchange=exchange)
+                               workloads.step_seed(1234, 999), marks=marks, exchange=exchange,
+                               push=move)
     torch.cuda.synchronize()
     phases = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) for i in range(1, len(marks))}
     received = torch.tensor([out.order.keys.numel()], device=device, dtype=torch.int64)

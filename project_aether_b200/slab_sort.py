@@ -134,12 +134,15 @@ def _buffers_for(capacity: int, device: torch.device, group) -> PeerBuffers:
 
 
 def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
-                       path: int = PATH_AUTO, mark=lambda name: None) -> SortedParticles:
+                       path: int = PATH_AUTO, mark=lambda name: None,
+                       push: Optional[tuple] = None) -> SortedParticles:
     """distributed_sort with the partition and the exchange fused: one kernel reads the
     rank's particles once and stores each into its destination GPU's receive buffer over
     NVLink.  The count all-gather before it and a one-word all-reduce after it are the only
     collectives.  The kernel reads the gathered counts on the device, so the host waits for
-    them (it needs its own receive count to launch the local sort) while the exchange runs."""
+    them (it needs its own receive count to launch the local sort) while the exchange runs.
+    With `push` = (dt, lo, hi) the count and exchange kernels take every particle as it is
+    after the move stage, so the particles arrive moved and the inputs stay untouched."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     ix_offset, nx_local = slab_range(grid, world, rank)
     n, device = x.numel(), x.device
@@ -154,9 +157,18 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
         counts = torch.zeros(world, dtype=torch.int64, device=device)
         part_ws = torch.empty(lib.AetherSlabPartitionWorkspaceBytes(n, world), dtype=torch.uint8,
                               device=device)
-        _native.check(lib.AetherSlabExchangeCount(
-            x.data_ptr(), n, ctypes.byref(g), world, counts.data_ptr(), part_ws.data_ptr(),
-            part_ws.numel(), stream), 'AetherSlabExchangeCount')
+        if push is None:
+            _native.check(lib.AetherSlabExchangeCount(
+                x.data_ptr(), n, ctypes.byref(g), world, counts.data_ptr(), part_ws.data_ptr(),
+                part_ws.numel(), stream), 'AetherSlabExchangeCount')
+        else:
+            dt = float(push[0])
+            lo = (ctypes.c_float * 3)(*[float(c) for c in push[1]])
+            hi = (ctypes.c_float * 3)(*[float(c) for c in push[2]])
+            _native.check(lib.AetherSlabExchangeCountMoved(
+                x.data_ptr(), velocity.data_ptr(), n, dt, lo, hi, ctypes.byref(g), world,
+                counts.data_ptr(), part_ws.data_ptr(), part_ws.numel(), stream),
+                'AetherSlabExchangeCountMoved')
         mark('partition')
         # The all-gather also orders this step after the peers' previous sort.
         matrix_dev = torch.empty((world, world), dtype=torch.int64, device=device)
@@ -169,11 +181,19 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             if buffers is not None:
                 pointers = (ctypes.c_void_p * world)(*buffers.pointers)
                 error = torch.zeros(1, dtype=torch.int32, device=device)
-                _native.check(lib.AetherSlabExchangeScatter(
-                    x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
-                    velocity.stride(0), n, ctypes.byref(g), world, rank, pointers,
-                    buffers.capacity, matrix_dev.data_ptr(), error.data_ptr(), part_ws.data_ptr(),
-                    part_ws.numel(), stream), 'AetherSlabExchangeScatter')
+                if push is None:
+                    _native.check(lib.AetherSlabExchangeScatter(
+                        x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
+                        velocity.stride(0), n, ctypes.byref(g), world, rank, pointers,
+                        buffers.capacity, matrix_dev.data_ptr(), error.data_ptr(),
+                        part_ws.data_ptr(), part_ws.numel(), stream), 'AetherSlabExchangeScatter')
+                else:
+                    _native.check(lib.AetherSlabExchangeScatterMoved(
+                        x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
+                        velocity.stride(0), n, dt, lo, hi, ctypes.byref(g), world, rank, pointers,
+                        buffers.capacity, matrix_dev.data_ptr(), error.data_ptr(),
+                        part_ws.data_ptr(), part_ws.numel(), stream),
+                        'AetherSlabExchangeScatterMoved')
                 # Every rank's stores must have landed before anyone reads its buffer.
                 dist.all_reduce(buffers.flag, group=group)
             # Fetch the counts on a side stream so that the copy does not queue behind the
@@ -215,7 +235,8 @@ def _side_stream(device: torch.device) -> torch.cuda.Stream:
 
 def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity: torch.Tensor,
                      grid: CellGrid, seed: int, group=None, path: int = PATH_AUTO,
-                     marks: Optional[list] = None, exchange: str = 'peer') -> SortedParticles:
+                     marks: Optional[list] = None, exchange: str = 'peer',
+                     push: Optional[tuple] = None) -> SortedParticles:
     """Sorts the particles of all ranks by cell; every rank ends with its slab's
     particles, cell-sorted, with slab-local `cell_counts` / `cell_start`.
 
@@ -223,11 +244,14 @@ def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity
     receive buffers over NVLink); 'nccl' partitions locally and calls one NCCL all-to-all per
     payload array.  Same result either way.
     `marks`, if given, receives (name, cuda event) pairs recorded on the current stream
-    after each phase (partition, counts, exchange, sort), for phase timing."""
+    after each phase (partition, counts, exchange, sort), for phase timing.
+    `push` = (dt, lo, hi) fuses the move stage (x += v*dt, specular walls) into the step: the
+    'peer' exchange moves the particles inside its count and exchange kernels; the 'nccl'
+    form moves a copy first.  The inputs are not modified."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     ix_offset, nx_local = slab_range(grid, world, rank)
     if world == 1:
-        return sort_and_gather_particles(x, y, z, velocity, grid, seed, path=path)
+        return sort_and_gather_particles(x, y, z, velocity, grid, seed, path=path, push=push)
 
     def mark(name):
         if marks is not None:
@@ -237,7 +261,12 @@ def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity
 
     mark('begin')
     if exchange == 'peer':
-        return peer_exchange_sort(x, y, z, velocity, grid, seed, group, path, mark)
+        return peer_exchange_sort(x, y, z, velocity, grid, seed, group, path, mark, push)
+    if push is not None:
+        from .particle_push import fused_particle_push
+        n_in = x.numel()
+        x, y, z, velocity = x.clone(), y.clone(), z.clone(), velocity.clone()
+        fused_particle_push([x, y, z], [velocity[k, :n_in] for k in range(3)], *push)
     parts = partition_by_slab(x, y, z, velocity, grid, world)
     mark('partition')
     matrix = exchange_counts(parts.counts, group)

@@ -166,6 +166,28 @@ def _nccl_worker(rank, world, port, result_dir):
             np.testing.assert_array_equal(got.velocity.cpu().numpy()[2, :want.keys.size],
                                           mine[5][want.particle_index])
             assert got.velocity.shape[1] == -(-want.keys.size // 4) * 4
+        # The move stage fused into the step: equal to moving every share first.
+        dt = 0.07
+        moved = []
+        for h in host:
+            p, w = so.push_particles(list(h[:3]), list(h[3:]), dt, grid.lo, grid.hi)
+            moved.append(tuple(p) + tuple(w))
+        mine = so.exchange_replay(moved, ogrid, world)[rank]
+        want = so.sort_particles(*mine[:3], ogrid, 92, ix_offset=off, nx_local=width)
+        before = [t.clone() for t in (x, y, z, v)]
+        for exchange in ('peer', 'nccl'):
+            got = slab_sort.distributed_sort(x, y, z, v, grid, 92, exchange=exchange,
+                                             push=(dt, grid.lo, grid.hi))
+            np.testing.assert_array_equal(got.order.keys.cpu().numpy().view(np.uint32), want.keys)
+            np.testing.assert_array_equal(got.order.particle_index.cpu().numpy(),
+                                          want.particle_index)
+            for k in range(3):
+                np.testing.assert_array_equal(got.positions[k].cpu().numpy(),
+                                              mine[k][want.particle_index])
+                np.testing.assert_array_equal(got.velocity.cpu().numpy()[k, :want.keys.size],
+                                              mine[3 + k][want.particle_index])
+            for t, b in zip((x, y, z, v), before):
+                assert torch.equal(t, b)
         open(os.path.join(result_dir, f'ok{rank}'), 'w').close()
     finally:
         dist.destroy_process_group()
