@@ -80,11 +80,15 @@ def run(args, workload: str) -> None:
     dist.barrier()
     torch.cuda.synchronize()
     begin.record()
+    ticks = []
     for s in range(args.steps):
         out = step(100 + s)
+        ticks.append(torch.cuda.Event(enable_timing=True))
+        ticks[-1].record()
     end.record()
     torch.cuda.synchronize()
     dist.barrier()
+    step_ms = [a.elapsed_time(b) for a, b in zip([begin] + ticks[:-1], ticks)]
     clocks = sampler.stop() if rank == 0 else None
     elapsed = torch.tensor([begin.elapsed_time(end)], device=device)
     dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
@@ -208,7 +212,7 @@ def run(args, workload: str) -> None:
                     'h2d_bytes_per_step': int(bytes_io[0]), 'd2h_bytes_per_step': int(bytes_io[1]),
                     'ms_per_step': e2e_ms, 'steps': e2e_steps},
             'gpu_launches': launches, 'roofline': roofline, 'stage_ms_rank0': stages,
-            'phase_ms_rank0': phases,
+            'phase_ms_rank0': phases, 'step_ms_rank0': step_ms,
             'single_gpu_same_workload': single,
             'cpu_baseline': None,
         }
