@@ -151,7 +151,7 @@ struct SlabTargets {
 // Stages the tile in shared memory grouped by destination (stable inside a
 // destination), then writes every destination's run with coalesced stores:
 // plain stores, to local memory or straight into a peer GPU's memory.
-__global__ void __launch_bounds__(kSlabThreads)
+__global__ void __launch_bounds__(kSlabThreads, 4)
 slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                     int64_t n, AetherGrid g, int slab_width, int world, bool vec,
@@ -166,27 +166,23 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t tile_first = static_cast<int64_t>(blockIdx.x) * kSlabTile;
   const int64_t i0 = tile_first + static_cast<int64_t>(tid) * kSlabItems;
-  float f[6][kSlabItems];
-  load8(x, i0, n, vec, f[0]);
-  load8(y, i0, n, vec, f[1]);
-  load8(z, i0, n, vec, f[2]);
-  load8(v, i0, n, vec && padded % 4 == 0, f[3]);
-  load8(v + padded, i0, n, vec && padded % 4 == 0, f[4]);
-  load8(v + 2 * padded, i0, n, vec && padded % 4 == 0, f[5]);
+  // One axis at a time (a coordinate and its velocity component) passes through the
+  // registers, so that four blocks fit an SM; the x pair comes first because the
+  // destination depends on it.
+  const bool vec_v = vec && padded % 4 == 0;
+  float pc[kSlabItems], pw[kSlabItems];
+  load8(x, i0, n, vec, pc);
+  load8(v, i0, n, vec_v, pw);
   if (push.enabled) {  // fused move stage: the particle travels as it is after the move
 #pragma unroll
-    for (int k = 0; k < kSlabItems; ++k) {
-      push_axis(f[0][k], f[3][k], push.dt, push.lo[0], push.hi[0]);
-      push_axis(f[1][k], f[4][k], push.dt, push.lo[1], push.hi[1]);
-      push_axis(f[2][k], f[5][k], push.dt, push.lo[2], push.hi[2]);
-    }
+    for (int k = 0; k < kSlabItems; ++k) push_axis(pc[k], pw[k], push.dt, push.lo[0], push.hi[0]);
   }
   int dest[kSlabItems];
   // Per-thread counts of the eight destinations, 16 bits each in two words.
   unsigned long long lo = 0, hi = 0;
 #pragma unroll
   for (int k = 0; k < kSlabItems; ++k) {
-    dest[k] = i0 + k < n ? slab_of(f[0][k], g, slab_width) : -1;
+    dest[k] = i0 + k < n ? slab_of(pc[k], g, slab_width) : -1;
     if (dest[k] >= 0) {
       if (dest[k] < 4) lo += 1ull << (16 * dest[k]);
       else hi += 1ull << (16 * (dest[k] - 4));
@@ -240,15 +236,36 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   for (int w = 0; w < kMaxWorld; ++w)
     next[w] = local_base[w] +
               static_cast<uint32_t>(((w < 4 ? base_lo : base_hi) >> (16 * (w & 3))) & 0xffffu);
+  int pos[kSlabItems];  // place of each particle in the staged tile, -1 past the end
 #pragma unroll
   for (int k = 0; k < kSlabItems; ++k) {
+    pos[k] = -1;
     if (dest[k] < 0) continue;
-    uint32_t p = 0;
 #pragma unroll
     for (int w = 0; w < kMaxWorld; ++w)
-      if (dest[k] == w) p = next[w]++;
+      if (dest[k] == w) pos[k] = static_cast<int>(next[w]++);
+  }
 #pragma unroll
-    for (int c = 0; c < 6; ++c) stage[c][p] = f[c][k];
+  for (int k = 0; k < kSlabItems; ++k)
+    if (pos[k] >= 0) {
+      stage[0][pos[k]] = pc[k];
+      stage[3][pos[k]] = pw[k];
+    }
+#pragma unroll
+  for (int axis = 1; axis < 3; ++axis) {
+    load8(axis == 1 ? y : z, i0, n, vec, pc);
+    load8(v + axis * padded, i0, n, vec_v, pw);
+    if (push.enabled) {
+#pragma unroll
+      for (int k = 0; k < kSlabItems; ++k)
+        push_axis(pc[k], pw[k], push.dt, push.lo[axis], push.hi[axis]);
+    }
+#pragma unroll
+    for (int k = 0; k < kSlabItems; ++k)
+      if (pos[k] >= 0) {
+        stage[axis][pos[k]] = pc[k];
+        stage[3 + axis][pos[k]] = pw[k];
+      }
   }
   __syncthreads();
   // Write every destination's run: 16-byte stores over the part of the run whose

@@ -57,11 +57,15 @@ _workspaces = {}
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """One cached scratch buffer per device and stream, grown on demand."""
+    """One cached scratch buffer per device and stream, grown on demand (with an eighth
+    of headroom, so that a particle count that creeps up from call to call does not
+    reallocate gigabytes every time)."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = None
+        _workspaces.pop(key, None)  # release the old buffer before asking for the new one
+        buf = torch.empty(max(nbytes + nbytes // 8, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
 

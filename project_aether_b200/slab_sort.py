@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from . import _native
 from .cell_grid import CellGrid
-from .particle_sort import (PATH_AUTO, SortedParticles, _workspace, native_grid,
+from .particle_sort import (PATH_AUTO, SortedParticles, SortResult, _workspace, native_grid,
                             sort_and_gather_particles)
 
 
@@ -155,7 +155,8 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
         current = torch.cuda.current_stream(device)
         stream = ctypes.c_void_p(current.cuda_stream)
         counts = torch.zeros(world, dtype=torch.int64, device=device)
-        part_ws = torch.empty(lib.AetherSlabPartitionWorkspaceBytes(n, world), dtype=torch.uint8,
+        part_bytes = lib.AetherSlabPartitionWorkspaceBytes(n, world)
+        part_ws = torch.empty(-(-part_bytes // (1 << 20)) * (1 << 20), dtype=torch.uint8,
                               device=device)
         if push is None:
             _native.check(lib.AetherSlabExchangeCount(
@@ -215,9 +216,26 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
         mark('exchange')
         m = int(received[rank])
         rx, ry, rz, rv = buffers.views(m)
+        # The results are cut out of allocations of the buffers' capacity: the number of
+        # particles a rank holds changes a little from step to step, and allocations whose
+        # size changes every step defeat torch's caching allocator (a stall of tens of
+        # milliseconds whenever it has to return its cache to the driver).
+        cap, padded_out = buffers.capacity, -(-m // 4) * 4
+        cells = nx_local * grid.cells[1] * grid.cells[2]
+
+        def cut(dtype):
+            return torch.empty(cap, dtype=dtype, device=device)[:m]
+
+        order = SortResult(cut(torch.int32), cut(torch.int32),
+                           torch.empty(cells, dtype=torch.int32, device=device),
+                           torch.empty(cells + 1, dtype=torch.int32, device=device))
+        vs = torch.empty(3 * cap, dtype=torch.float32, device=device)[:3 * padded_out].view(
+            3, padded_out)
+        results = SortedParticles(order, (cut(torch.float32), cut(torch.float32),
+                                          cut(torch.float32)), vs)
         out = sort_and_gather_particles(rx, ry, rz, rv, grid, seed, ix_offset=ix_offset,
-                                        nx_local=nx_local, path=path,
-                                        padded_out=-(-m // 4) * 4)
+                                        nx_local=nx_local, path=path, padded_out=padded_out,
+                                        out=results)
         mark('sort')
     return out
 
