@@ -120,3 +120,23 @@ def test_workloads_are_seeded_and_shaped():
     v2 = workloads.make_particles(w2, 'cpu', seed=0, n=20_000)[3]
     assert 4.9 < float(v2[0, :20_000].mean()) < 5.1
     assert workloads.step_seed(1234, 5000) == 1234 ^ (5000 << 20)
+
+
+def test_cpu_binning_pipeline_counts_equal_the_oracle():
+    """The CPU pipeline of the command-line benchmark (torch on host threads) bins particles
+    into the same cells as the oracle; its shuffle bits come from another generator, so only
+    the counts and the sortedness are comparable (phase2_triton_sort_benchmark.py:161-162)."""
+    import numpy as np
+    import torch
+    from oracle import sort_oracle as so
+    from project_aether_b200 import phase2_benchmark
+    from project_aether_b200.cell_grid import CellGrid
+    grid = CellGrid((0.0, 0.0, 0.0), (1.0, 1.0, 0.64), (25, 25, 16))
+    gen = torch.Generator().manual_seed(5)
+    pos = [torch.rand(20_000, generator=gen) * h for h in grid.hi]
+    keys, order, counts = phase2_benchmark.cpu_binning(*pos, grid, torch.Generator().manual_seed(0))
+    want = so.sort_particles(*(p.numpy() for p in pos), so.Grid(grid.lo, grid.hi, grid.cells), 3)
+    np.testing.assert_array_equal(counts.numpy(), want.cell_counts)
+    assert bool((keys[1:] >= keys[:-1]).all())
+    np.testing.assert_array_equal(np.sort(order.numpy()), np.arange(20_000))
+    np.testing.assert_array_equal((keys >> 7).numpy(), want.keys >> 7)
