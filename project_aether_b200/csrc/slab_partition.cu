@@ -21,9 +21,20 @@ constexpr int kSlabThreads = 256;
 constexpr int kSlabItems = 8;
 constexpr int kSlabTile = kSlabThreads * kSlabItems;  // 2048 particles, blocked per thread
 
+// Destination rank of a particle: ix / slab_width, as a chain of compares (at
+// most eight slabs; an integer division costs several times more).
 __device__ __forceinline__ int slab_of(float x, const AetherGrid& g, int slab_width) {
-  return axis_index(x, g.x0, g.inv_dx, g.nx) / slab_width;
+  const int ix = axis_index(x, g.x0, g.inv_dx, g.nx);
+  int d = 0;
+#pragma unroll
+  for (int w = 1; w < kMaxWorld; ++w) d += ix >= w * slab_width;
+  return d;
 }
+
+// Staged tiles are written eight consecutive places per thread, which would put
+// eight lanes of a warp on every bank; flipping the low three bits of a place by
+// bits 5-7 spreads them over all 32 banks, for the quad reads as well.
+__device__ __forceinline__ int swizzle(int p) { return p ^ ((p >> 5) & 7); }
 
 __device__ __forceinline__ void load8(const float* p, int64_t i0, int64_t n, bool vec, float* out) {
   if (vec && i0 + kSlabItems <= n) {
@@ -166,6 +177,28 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t tile_first = static_cast<int64_t>(blockIdx.x) * kSlabTile;
   const int64_t i0 = tile_first + static_cast<int64_t>(tid) * kSlabItems;
+  // Where this tile's runs go (global reads: started before anything waits on them).
+  if (tid < world) {
+    const size_t entry = static_cast<size_t>(tid) * gridDim.x + blockIdx.x;
+    uint32_t base = tile_offset[entry] + block_sum[entry / kScanBlock];
+    if (tg.exchange) {
+      // Receive position: what lower ranks send to destination tid, then this rank's block.
+      int64_t lower = 0, all = 0;
+      for (int s = 0; s < world; ++s) {
+        const int64_t c = tg.count_matrix[s * world + tid];
+        if (s < tg.rank) lower += c;
+        all += c;
+      }
+      const size_t first = static_cast<size_t>(tid) * gridDim.x;  // this rank's first tile for tid
+      base = base - (tile_offset[first] + block_sum[first / kScanBlock]) +
+             static_cast<uint32_t>(lower);
+      if (all > tg.capacity) {  // never store past a peer's buffer
+        base = 0xffffffffu;
+        if (blockIdx.x == 0) atomicCAS(tg.error, 0, kErrReceiveOverflow);
+      }
+    }
+    out_base[tid] = base;
+  }
   // One axis at a time (a coordinate and its velocity component) passes through the
   // registers, so that four blocks fit an SM; the x pair comes first because the
   // destination depends on it.
@@ -209,27 +242,6 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     }
     local_base[kMaxWorld] = run;
   }
-  if (tid < world) {
-    const size_t entry = static_cast<size_t>(tid) * gridDim.x + blockIdx.x;
-    uint32_t base = tile_offset[entry] + block_sum[entry / kScanBlock];
-    if (tg.exchange) {
-      // Receive position: what lower ranks send to destination tid, then this rank's block.
-      int64_t lower = 0, all = 0;
-      for (int s = 0; s < world; ++s) {
-        const int64_t c = tg.count_matrix[s * world + tid];
-        if (s < tg.rank) lower += c;
-        all += c;
-      }
-      const size_t first = static_cast<size_t>(tid) * gridDim.x;  // this rank's first tile for tid
-      base = base - (tile_offset[first] + block_sum[first / kScanBlock]) +
-             static_cast<uint32_t>(lower);
-      if (all > tg.capacity) {  // never store past a peer's buffer
-        base = 0xffffffffu;
-        if (blockIdx.x == 0) atomicCAS(tg.error, 0, kErrReceiveOverflow);
-      }
-    }
-    out_base[tid] = base;
-  }
   __syncthreads();
   uint32_t next[kMaxWorld];
 #pragma unroll
@@ -248,8 +260,8 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 #pragma unroll
   for (int k = 0; k < kSlabItems; ++k)
     if (pos[k] >= 0) {
-      stage[0][pos[k]] = pc[k];
-      stage[3][pos[k]] = pw[k];
+      stage[0][swizzle(pos[k])] = pc[k];
+      stage[3][swizzle(pos[k])] = pw[k];
     }
 #pragma unroll
   for (int axis = 1; axis < 3; ++axis) {
@@ -263,8 +275,8 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 #pragma unroll
     for (int k = 0; k < kSlabItems; ++k)
       if (pos[k] >= 0) {
-        stage[axis][pos[k]] = pc[k];
-        stage[3 + axis][pos[k]] = pw[k];
+        stage[axis][swizzle(pos[k])] = pc[k];
+        stage[3 + axis][swizzle(pos[k])] = pw[k];
       }
   }
   __syncthreads();
@@ -300,7 +312,8 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 #pragma unroll
     for (int c = 0; c < 6; ++c)
       *reinterpret_cast<float4*>(tg.array[d][c] + o) =
-          make_float4(stage[c][j], stage[c][j + 1], stage[c][j + 2], stage[c][j + 3]);
+          make_float4(stage[c][swizzle(j)], stage[c][swizzle(j + 1)], stage[c][swizzle(j + 2)],
+                      stage[c][swizzle(j + 3)]);
   }
   // Heads and tails: at most three elements each per destination when aligned;
   // the whole run when the buffers are not 16-byte aligned.
@@ -312,11 +325,11 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     const int tail_first = lb + head + 4 * run_quads[d];
     for (int i = tid; i < head; i += kSlabThreads) {
 #pragma unroll
-      for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + i] = stage[c][lb + i];
+      for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + i] = stage[c][swizzle(lb + i)];
     }
     for (int j = tail_first + tid; j < le; j += kSlabThreads) {
 #pragma unroll
-      for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + (j - lb)] = stage[c][j];
+      for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + (j - lb)] = stage[c][swizzle(j)];
     }
   }
 }

@@ -2,6 +2,8 @@
 
     python -m project_aether_b200.profile_case --workload c3_64m_hypersonic --log2n 24 --calls 2
     python -m project_aether_b200.profile_case --workload c5_128m_256 --log2n 24 --calls 2 --collide
+    python -m project_aether_b200.profile_case --log2n 24 --calls 2 --path digits
+    python -m project_aether_b200.profile_case --log2n 24 --calls 1 --extras
 
 The case keeps the workload's grid shape but scales the z extent of the grid
 with the particle count so that particles per cell stay what the full
@@ -31,6 +33,8 @@ def main():
     ap.add_argument('--log2n', type=int, default=24)
     ap.add_argument('--calls', type=int, default=2)
     ap.add_argument('--path', default='auto', choices=['auto', 'digits'])
+    ap.add_argument('--extras', action='store_true',
+                    help='also run the move stage and the 8-way slab partition once per call')
     ap.add_argument('--collide', action='store_true',
                     help='also run the collision stage on the sorted output of every call')
     args = ap.parse_args()
@@ -48,6 +52,12 @@ def main():
     for s in range(args.calls):
         out = particle_sort.sort_and_gather_particles(x, y, z, v, w.grid, workloads.step_seed(1234, s),
                                                       path=path)
+        if args.extras:
+            from . import particle_push, slab_sort
+            moved = [t.clone() for t in (x, y, z, v)]
+            particle_push.fused_particle_push(moved[:3], [moved[3][k, :w.n] for k in range(3)],
+                                              8.2e-5, w.grid.lo, w.grid.hi)
+            slab_sort.partition_by_slab(x, y, z, v, w.grid, 8)
         if args.collide:
             ntc_collide.collide(lib, out.velocity, out.order.cell_start, sigma_g_max, collisions,
                                 w.n, ntc_collide.CollisionParams(0.006, 1.0, 0.46, 1234, s))
