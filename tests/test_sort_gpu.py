@@ -154,7 +154,7 @@ def test_more_than_255_equal_keys_in_a_bucket(cuda):
 
 
 @pytest.mark.parametrize('n,cells,dense', [(600_000, (64, 64, 32), 0.02), (2_000_003, (128, 64, 64), 0.03),
-                                           (1_200_000, (16, 16, 16), 0.05)])
+                                           (2_400_000, (16, 16, 16), 0.05)])
 def test_dense_layer_overfills_buckets_without_leaving_the_bucketed_path(cuda, n, cells, dense):
     """Bucket widths are planned from the average load.  A density contrast across rows
     (70 % of the particles in a thin y-layer) puts several times the shared-memory capacity
@@ -167,11 +167,11 @@ def test_dense_layer_overfills_buckets_without_leaving_the_bucketed_path(cuda, n
     got = _check_all(x, y, z, vel, grid, 77, pa.PATH_AUTO, big=True)
     assert not pa.last_sort_used_digit_passes(cuda)
     # The layer really overfills buckets: with the library's bucket width (the largest
-    # 2^s <= 1024 cells with an average of at most 4224 particles and at least 1024 buckets)
+    # 2^s <= 1024 cells with an average of at most 4224 particles and at least 2048 buckets)
     # some bucket holds more than the 5376 records of the finish kernel's shared memory.
     counts = got.order.cell_counts.cpu().numpy().astype(np.int64)
     shift = next(s for s in range(10, -1, -1)
-                 if s == 0 or (n <= 4224 * -(-counts.size >> s) and -(-counts.size >> s) >= 1024))
+                 if s == 0 or (n <= 4224 * -(-counts.size >> s) and -(-counts.size >> s) >= 2048))
     per_bucket = np.add.reduceat(counts, np.arange(0, counts.size, 1 << shift))
     assert per_bucket.max() > 5376
 
