@@ -143,8 +143,9 @@ def run_reference(args, workload):
     cpu_reference_step(host, w.grid, workloads.step_seed(1234, 0))
     first = time.perf_counter() - t0
     sample = n
-    if first * (args.steps + args.warmup) > 240:  # keep the whole run within a few minutes
-        sample = max(1 << 20, int(n * 240 / (first * (args.steps + args.warmup))))
+    budget = min(240.0, 15.0 * (args.steps + args.warmup))  # seconds for the whole run
+    if first * (args.steps + args.warmup) > budget:  # keep the run within a few minutes
+        sample = max(1 << 20, int(n * budget / (first * (args.steps + args.warmup))))
         x, y, z, v = workloads.make_particles(w, 'cpu', seed=0, n=sample)
         host = [t.numpy() for t in (x, y, z, v)]
     for s in range(max(0, args.warmup - 1)):
