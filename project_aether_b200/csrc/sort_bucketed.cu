@@ -860,7 +860,15 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // The chunk-major record layout pays when the scatter is bound by scattered
 // stores and a bucket's runs stay long: up to 32 K buckets.  With more buckets
 // (few particles per bucket and chunk) one chunk holds everything.
-inline int chunk_log_for(int64_t buckets) { return buckets <= 32768 ? kChunkLog : kNoChunkLog; }
+// Smaller inputs take smaller chunks (fewer particles contend for a slot counter, and the
+// chunk's records stay deeper inside L2): measured best 2^20 at 4 M particles, 2^21 at 16 M,
+// 2^22 from 32 M on.
+inline int chunk_log_for(int64_t buckets, int64_t n) {
+  if (buckets > 32768) return kNoChunkLog;
+  if (n <= (int64_t{1} << 22)) return kChunkLog - 2;
+  if (n <= (int64_t{1} << 24)) return kChunkLog - 1;
+  return kChunkLog;
+}
 
 struct BucketLayout {
   int chunk_log;
@@ -873,7 +881,7 @@ struct BucketLayout {
 
 BucketLayout bucket_layout(int64_t n, int64_t buckets) {
   BucketLayout l;
-  l.chunk_log = chunk_log_for(buckets);
+  l.chunk_log = chunk_log_for(buckets, n);
   l.chunks = static_cast<int>(
       std::max<int64_t>(1, (n + (int64_t{1} << l.chunk_log) - 1) >> l.chunk_log));
   l.entries = static_cast<int64_t>(l.chunks) * buckets;
