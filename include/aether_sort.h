@@ -30,7 +30,11 @@ extern "C" {
  * (ix, iy, iz); the cell id is linearised over the x-slab
  * [ix_offset, ix_offset + nx_local): cell = (iz*ny + iy)*nx_local + ix - ix_offset.
  * A single-GPU sort passes ix_offset = 0, nx_local = nx.  The reference has no
- * slab form; it is the multi-GPU extension of fused_radix_sort.py:99. */
+ * slab form; it is the multi-GPU extension of fused_radix_sort.py:99.
+ * Precondition of the slab form: every particle's column ix lies inside the
+ * slab (the exchange step guarantees it).  A particle outside it is binned into
+ * the slab's nearest column, ix - ix_offset clamped to [0, nx_local - 1], so
+ * that no table is ever indexed out of range; its cell is then not its own. */
 typedef struct AetherGrid {
   float x0, y0, z0;
   float inv_dx, inv_dy, inv_dz;
@@ -46,9 +50,10 @@ int AetherSortAbiVersion(void);
  * velocities are to be carried (about 40 bytes per particle, 32 without).
  * Replaces the per-call tensor allocations of the reference driver
  * (fused_radix_sort.py:245-248,257-263).  A smaller workspace is accepted as
- * long as the digit passes fit (8 bytes per particle plus status words); the
- * call then runs the slower of its paths.  Returns 0 if the arguments are out
- * of range (n < 0, n >= 2^30, key wider than 32 bits). */
+ * long as the digit passes fit (8 bytes per particle plus status words): with
+ * `path` 0 the call then runs the digit passes, the slower of its paths, and
+ * `path` 2 is refused.  Returns 0 if the arguments are out of range (n < 0,
+ * n >= 2^30, key wider than 32 bits). */
 size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload);
 
 /* sort_particles_by_cell (fused_radix_sort.py:221-280): sorted keys,
@@ -209,8 +214,8 @@ int AetherDsmcCollideTma(float* velocity, const int* cell_start, float* sigma_g_
  * runs inside a host application which has already handed all of the GPU's
  * memory to its own pool, or a step of a real-time loop in which cudaMalloc
  * (which synchronises the whole device) is forbidden.  Such a caller has no
- * workspace to pass, so this entry point keeps the scratch of the digit-pass
- * sort in a fixed array inside the library image (9 MiB, reserved on every GPU
+ * workspace to pass, so this entry point keeps the sort's scratch in a fixed
+ * array inside the library image (9 MiB, reserved on every GPU
  * that loads the library until the process exits) and allocates nothing: no
  * cudaMalloc, no cudaFree, no allocating library routine.  It has no
  * counterpart in the reference, whose driver allocates about ten tensors per
@@ -225,12 +230,33 @@ int AetherDsmcCollideTma(float* velocity, const int* cell_start, float* sigma_g_
  *     call clears the part that must start at zero itself.  Two calls whose
  *     work overlaps on the GPU (different streams, no dependency) race on it:
  *     serialise them.
+ *   - Which of the two sort paths runs follows from the size: calls whose
+ *     bucketed record layout fits the array (up to a few hundred thousand
+ *     particles) take the bucketed path, larger ones the digit passes.
+ *   - The device status of a call (a bounded wait that gave up) lives in that
+ *     array too: read it with AetherSortStaticReadStatus, and the path that
+ *     produced the result with AetherSortStaticReadUsedDigitPasses; both
+ *     synchronise `stream` like their workspace twins and allocate nothing.
  * Inputs, outputs and results are those of AetherSortParticlesByCell. */
 int64_t AetherSortStaticMaxParticles(void);
 int AetherSortParticlesByCellStatic(const float* x, const float* y, const float* z, int64_t n,
                                     const AetherGrid* grid, uint64_t seed, uint32_t* keys_out,
                                     int32_t* index_out, int32_t* cell_counts, int32_t* cell_start,
                                     void* stream);
+int AetherSortStaticReadStatus(void* stream, int32_t* status);
+int AetherSortStaticReadUsedDigitPasses(void* stream, int32_t* used);
+
+/* Test hook for the bounded device waits (no counterpart in the reference, whose
+ * look-back spins without limit, fused_radix_sort.py:160-171).  Runs one digit
+ * pass over three tiles of zero keys with the ticket dispenser started at 1, so
+ * that the tile every look-back ends at is never processed and never publishes:
+ * the waiting blocks poll `poll_limit` times, record the give-up code in the
+ * workspace header and return.  Nothing traps or spins without limit.  Afterwards
+ * AetherSortReadStatus(workspace, ...) reports 1 (look-back timeout).  The
+ * workspace must hold AetherSortProbeLookbackWorkspaceBytes() bytes. */
+size_t AetherSortProbeLookbackWorkspaceBytes(void);
+int AetherSortProbeLookbackGiveUp(void* workspace, size_t workspace_bytes, uint32_t poll_limit,
+                                  void* stream);
 
 /* Measurement hooks.  The reference times whole calls with CUDA events around
  * the Python entry point (project_aether/scripts/phase2_triton_sort_benchmark.py:
@@ -239,7 +265,10 @@ int AetherSortParticlesByCellStatic(const float* x, const float* y, const float*
  * the caller's stream.  AetherSortReadStageTimes synchronises on them and
  * writes the elapsed milliseconds of each stage, averaged over the sort calls
  * made since timing was enabled (the most recent 32 at most; -1 for a stage
- * that did not run), into ms_out[0 .. AetherSortStageCount()).
+ * that did not run), into ms_out[0 .. AetherSortStageCount()).  The timing
+ * state is process-wide and bound to the device that is current when timing is
+ * enabled: calls on other devices are not timed, and the figures only mean
+ * something when the timed calls come from one host thread.
  * AetherSortKernelLaunches returns how many kernels this library has launched
  * in this process so far. */
 int AetherSortSetStageTiming(int enabled);

@@ -65,6 +65,26 @@ static inline int axis_index(float c, float lo, float inv, int cells) {
   return i;
 }
 
+/* Threads a call with `threads` <= 0 would use (the OpenMP maximum, which the
+ * environment variable OMP_NUM_THREADS caps), so that a benchmark can print the
+ * number really used. */
+int oracle_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/* 1 when the library was built with OpenMP, else 0 (every call then runs on one thread). */
+int oracle_has_openmp(void) {
+#ifdef _OPENMP
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 static int resolve_threads(int threads) {
 #ifdef _OPENMP
   if (threads <= 0) threads = omp_get_max_threads();
@@ -161,7 +181,12 @@ int oracle_sort_particles(const float* x, const float* y, const float* z, const 
     int ix = axis_index(x[i], x0, inv_dx, nx);
     int iy = axis_index(y[i], y0, inv_dy, ny);
     int iz = axis_index(z[i], z0, inv_dz, nz);
-    uint32_t cell = (uint32_t)(((int64_t)iz * ny + iy) * nx_local + (ix - ix_offset));
+    /* Slab form (an extension of the reference's formula): a particle outside the slab is
+     * binned into the slab's nearest column, so that a cell id is never out of range. */
+    int ixl = ix - ix_offset;
+    if (ixl < 0) ixl = 0;
+    if (ixl > nx_local - 1) ixl = nx_local - 1;
+    uint32_t cell = (uint32_t)(((int64_t)iz * ny + iy) * nx_local + ixl);
     uint32_t key = (cell << 7) | (philox_word0((uint32_t)i, k0, k1) >> 25);
     keys[i] = key;
     order[i] = (int32_t)i;

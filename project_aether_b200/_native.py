@@ -76,6 +76,10 @@ _SIGNATURES = {
     'AetherSortParticlesByCellStatic': (ctypes.c_int, [_P, _P, _P, _I64,
                                                        ctypes.POINTER(AetherGrid),
                                                        ctypes.c_uint64, _P, _P, _P, _P, _P]),
+    'AetherSortStaticReadStatus': (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int32)]),
+    'AetherSortStaticReadUsedDigitPasses': (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int32)]),
+    'AetherSortProbeLookbackWorkspaceBytes': (ctypes.c_size_t, []),
+    'AetherSortProbeLookbackGiveUp': (ctypes.c_int, [_P, ctypes.c_size_t, ctypes.c_uint32, _P]),
     'AetherSortSetStageTiming': (ctypes.c_int, [ctypes.c_int]),
     'AetherSortStageCount': (ctypes.c_int, []),
     'AetherSortStageName': (ctypes.c_char_p, [ctypes.c_int]),

@@ -1,5 +1,6 @@
 // extern "C" entry points of libaether_sort.so (declared in include/aether_sort.h).
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -41,11 +42,12 @@ int run_sort(SortArgs& a, int path) {
   stage_reset();
   // path 1 asks for the digit passes; otherwise the bucketed path runs whenever its plan fits
   // (with or without payload outputs) and the workspace is large enough for its records.  A
-  // keys-only caller with a small workspace (the static-scratch entry point) gets the digit passes.
+  // caller with a smaller workspace (the static-scratch entry point above a few hundred
+  // thousand particles, or a workspace sized for the digit passes only) gets the digit passes.
   const BucketPlan plan = plan_buckets(a.n, a.num_cells);
   const bool roomy = a.workspace_bytes >= bucketed_workspace_bytes(a.n, a.num_cells);
-  const bool bucketed = plan.usable && path != 1 && (roomy || a.xs != nullptr || path == 2);
-  if (path == 2 && !bucketed) return cudaErrorInvalidValue;
+  const bool bucketed = plan.usable && path != 1 && (roomy || path == 2);
+  if (path == 2 && (!plan.usable || !roomy)) return cudaErrorInvalidValue;
   if (!bucketed) return standard_sort(a, nullptr);
   cudaError_t e = bucketed_sort(a, plan);
   if (e != cudaSuccess) return e;
@@ -62,7 +64,14 @@ namespace {
 // Stage timing keeps one event pair per stage for each of the last kTimedCalls
 // sort calls, so that a benchmark can run its timed calls back to back and read
 // the per-stage averages afterwards without a synchronisation in between.
+//
+// The state below is process-wide and belongs to ONE device: the device that is current when
+// AetherSortSetStageTiming(1) is called.  Sort calls on other devices are not timed.  A mutex
+// serialises the bookkeeping, so that calls from several host threads stay consistent; the
+// figures themselves only mean something when the timed calls come from one thread.
 constexpr int kTimedCalls = 32;
+std::mutex g_mutex;
+int g_timing_device = -1;
 bool g_timing = false;
 bool g_events_ready = false;
 cudaEvent_t g_begin[kTimedCalls][kNumStages], g_end[kTimedCalls][kNumStages];
@@ -75,13 +84,38 @@ const char* const kStageNames[kNumStages] = {
     "bucket_finish", "slab_partition", "particle_push", "slab_exchange", "collide"};
 }  // namespace
 
+namespace {
+bool timed_here() {
+  if (!g_timing) return false;
+  int device = -1;
+  return cudaGetDevice(&device) == cudaSuccess && device == g_timing_device;
+}
+}  // namespace
+
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 148;
+  if (cached[device] == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        sms <= 0)
+      sms = 148;
+    cached[device] = sms;
+  }
+  return cached[device];
+}
+
 void stage_reset() {
-  if (!g_timing) return;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!timed_here()) return;
   ++g_call;
   for (int i = 0; i < kNumStages; ++i) g_ran[g_call % kTimedCalls][i] = false;
 }
 void stage_begin(Stage s, cudaStream_t stream) {
-  if (!g_timing || g_call < 0) return;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!timed_here() || g_call < 0) return;
   if (!g_events_ready) {
     for (int c = 0; c < kTimedCalls; ++c)
       for (int i = 0; i < kNumStages; ++i) {
@@ -93,16 +127,36 @@ void stage_begin(Stage s, cudaStream_t stream) {
   cudaEventRecord(g_begin[g_call % kTimedCalls][s], stream);
 }
 void stage_end(Stage s, cudaStream_t stream) {
-  if (!g_timing || g_call < 0) return;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!timed_here() || g_call < 0) return;
   cudaEventRecord(g_end[g_call % kTimedCalls][s], stream);
   g_ran[g_call % kTimedCalls][s] = true;
 }
-void count_launches(int kernels) { g_launches += kernels; }
+void count_launches(int kernels) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_launches += kernels;
+}
 }  // namespace aether
 
 using namespace aether;
 
 extern "C" int AetherSortSetStageTiming(int enabled) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (enabled) {
+    // The events are created on, and belong to, the device that is current now.
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (g_events_ready && device != g_timing_device) {
+      for (int c = 0; c < kTimedCalls; ++c)
+        for (int i = 0; i < kNumStages; ++i) {
+          cudaEventDestroy(g_begin[c][i]);
+          cudaEventDestroy(g_end[c][i]);
+        }
+      g_events_ready = false;
+    }
+    g_timing_device = device;
+  }
   g_timing = enabled != 0;
   g_call = -1;
   for (int c = 0; c < kTimedCalls; ++c)
@@ -115,6 +169,7 @@ extern "C" const char* AetherSortStageName(int stage) {
 }
 extern "C" int AetherSortReadStageTimes(float* ms_out, int capacity) {
   if (!ms_out || capacity < kNumStages) return cudaErrorInvalidValue;
+  std::lock_guard<std::mutex> lock(g_mutex);
   for (int i = 0; i < kNumStages; ++i) {
     ms_out[i] = -1.f;
     if (!g_events_ready) continue;
@@ -134,7 +189,21 @@ extern "C" int AetherSortReadStageTimes(float* ms_out, int capacity) {
   }
   return 0;
 }
-extern "C" uint64_t AetherSortKernelLaunches(void) { return g_launches; }
+extern "C" uint64_t AetherSortKernelLaunches(void) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return g_launches;
+}
+
+extern "C" size_t AetherSortProbeLookbackWorkspaceBytes(void) {
+  return lookback_probe_workspace_bytes();
+}
+
+extern "C" int AetherSortProbeLookbackGiveUp(void* workspace, size_t workspace_bytes,
+                                             uint32_t poll_limit, void* stream) {
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255)) return cudaErrorInvalidValue;
+  return lookback_give_up_probe(workspace, workspace_bytes, poll_limit,
+                                static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int AetherSortAbiVersion(void) { return 1; }
 

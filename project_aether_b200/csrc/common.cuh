@@ -76,11 +76,15 @@ __device__ __forceinline__ int axis_index(float c, float lo, float inv, int cell
   return min(max(i, 0), cells - 1);
 }
 
+// Cell id over the x-slab [ix_offset, ix_offset + nx_local) of the grid.  A particle whose
+// column lies outside the slab (the caller's precondition broken) is binned into the slab's
+// nearest column: every table the kernels index with a cell id stays in range.
 __device__ __forceinline__ uint32_t cell_of(float x, float y, float z, const AetherGrid& g) {
   const int ix = axis_index(x, g.x0, g.inv_dx, g.nx);
   const int iy = axis_index(y, g.y0, g.inv_dy, g.ny);
   const int iz = axis_index(z, g.z0, g.inv_dz, g.nz);
-  return static_cast<uint32_t>((iz * g.ny + iy) * g.nx_local + (ix - g.ix_offset));
+  const int ix_local = min(max(ix - g.ix_offset, 0), g.nx_local - 1);
+  return static_cast<uint32_t>((iz * g.ny + iy) * g.nx_local + ix_local);
 }
 
 __device__ __forceinline__ uint32_t make_key(uint32_t cell, uint32_t index, uint32_t k0,
@@ -165,6 +169,8 @@ enum Stage {
   kStageGather, kStageBucketCount, kStageBucketScan, kStageBucketScatter, kStageBucketFinish,
   kStageSlabPartition, kStagePush, kStageSlabExchange, kStageCollide, kNumStages
 };
+// Multiprocessors of the current device (queried once per device).
+int sm_count();
 void stage_begin(Stage s, cudaStream_t stream);
 void stage_end(Stage s, cudaStream_t stream);
 void stage_reset();
@@ -216,6 +222,15 @@ size_t standard_workspace_bytes_with_records(int64_t n, int64_t num_cells);
 // nonzero (the hand-over from the bucketed path), and the first 8 bytes of the
 // workspace header (error code and that flag) are left as they are.
 cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if);
+
+// One digit pass over three tiles of zero keys with the ticket dispenser started at 1: the
+// tile that would publish first is never processed, so every look-back runs out of polls,
+// records kErrLookbackTimeout in the workspace header and returns.  For tests of the give-up
+// path; `workspace` needs lookback_probe_workspace_bytes() bytes.
+cudaError_t lookback_give_up_probe(void* workspace, size_t workspace_bytes, uint32_t poll_limit,
+                                   cudaStream_t stream);
+int64_t lookback_probe_particles();
+size_t lookback_probe_workspace_bytes();
 
 struct BucketPlan {
   int shift;        // a bucket is 2^shift consecutive cell ids

@@ -66,7 +66,7 @@ cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, fl
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(vx) &&
                    aligned16(vy) && aligned16(vz);
   const int64_t blocks = (n + kPushThreads * 4 - 1) / (kPushThreads * 4);
-  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks, 148 * 16)));
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks, sm_count() * 16)));
   stage_begin(kStagePush, stream);
   if (vec)
     push_kernel<true><<<grid, kPushThreads, 0, stream>>>(x, y, z, vx, vy, vz, n, dt, lo[0], lo[1],

@@ -360,7 +360,7 @@ cudaError_t slab_count(const float* x, const float* vx, const PushSpec& push, in
   uint32_t* block_sum = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) +
                                                     align_up(entries * sizeof(uint32_t), 256));
   const int count_grid = std::max(1, std::min((tiles + kSlabThreads / 32 - 1) / (kSlabThreads / 32),
-                                              148 * 8));
+                                              sm_count() * 8));
   slab_count_kernel<<<count_grid, kSlabThreads, 0, stream>>>(x, vx, push, n, g, g.nx / world, world,
                                                              vec, tiles, tile_count);
   slab_scan_local_kernel<<<blocks, kScanBlock, 0, stream>>>(tile_count, entries, block_sum);

@@ -39,7 +39,6 @@ namespace aether {
 
 namespace {
 
-constexpr int kSmCount = 148;
 constexpr int kRecordWords = 8;  // 32-byte record
 
 // ------------------------------------------------------------------------
@@ -962,11 +961,11 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
     const int64_t covered = std::min<int64_t>(a.n, chunk_size);
     // Slices of a chunk: enough units to fill the GPU twice over, each a multiple of one
     // block round (4 particles per thread) so that the 16-byte loads stay aligned.
-    const int want = std::max(1, kSmCount * blocks_per_sm * 2 / l.chunks);
+    const int want = std::max(1, sm_count() * blocks_per_sm * 2 / l.chunks);
     const int64_t round = threads * 4;
     const int64_t slice = std::max<int64_t>(round, ((covered + want - 1) / want + round - 1) / round * round);
     const int parts = static_cast<int>((covered + slice - 1) / slice);
-    const int grid = std::max(1, std::min(l.chunks * parts, kSmCount * blocks_per_sm));
+    const int grid = std::max(1, std::min(l.chunks * parts, sm_count() * blocks_per_sm));
     if (shared) {
       auto kernel = wide ? (vec ? bucket_count_kernel<true, true, kCountThreadsWide>
                                 : bucket_count_kernel<true, false, kCountThreadsWide>)
@@ -1022,7 +1021,7 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
     const int64_t groups = (a.n + kItems - 1) / kItems;
     const int grid = static_cast<int>(std::max<int64_t>(
         1, std::min<int64_t>((groups + kScatterThreads - 1) / kScatterThreads,
-                             kSmCount * (8 / kItems) * 4)));
+                             sm_count() * (8 / kItems) * 4)));
     auto kernel = vec ? bucket_scatter_kernel<true, kItems> : bucket_scatter_kernel<false, kItems>;
     kernel<<<grid, kScatterThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push,
                                                     a.n, a.grid, k0, k1, p.shift, buckets,
@@ -1043,14 +1042,14 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(sizeof(FinishSmem)));
     if (e != cudaSuccess) return e;
-    kernel<<<std::min(buckets, kSmCount), kFinishThreads, sizeof(FinishSmem), a.stream>>>(
+    kernel<<<std::min(buckets, sm_count()), kFinishThreads, sizeof(FinishSmem), a.stream>>>(
         records, start, run_start, run_length, l.chunks, buckets, p.shift, a.n, a.num_cells, out,
         hdr);
   }
   e = cudaFuncSetAttribute(bucket_finish_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(sizeof(FinishSmem)));
   if (e != cudaSuccess) return e;
-  bucket_finish_large_kernel<<<std::min(buckets, kSmCount), kFinishThreads, sizeof(FinishSmem),
+  bucket_finish_large_kernel<<<std::min(buckets, sm_count()), kFinishThreads, sizeof(FinishSmem),
                                a.stream>>>(records, start, run_start, run_length, l.chunks,
                                            buckets, p.shift, a.num_cells, out, hdr);
   stage_end(kStageBucketFinish, a.stream);

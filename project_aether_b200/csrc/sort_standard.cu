@@ -18,8 +18,6 @@ namespace aether {
 
 namespace {
 
-constexpr int kSmCount = 148;
-
 // ------------------------------------------------------------------------
 // Key generation + upsweep.
 // ------------------------------------------------------------------------
@@ -391,11 +389,20 @@ gather_kernel(const int32_t* __restrict__ index, int64_t n, const float* __restr
   }
 }
 
+__global__ void __launch_bounds__(kBoundsThreads)
+clear_words_kernel(uint32_t* __restrict__ words, size_t count, const int32_t* __restrict__ run_if) {
+  if (run_if && *run_if == 0) return;
+  const size_t stride = static_cast<size_t>(gridDim.x) * kBoundsThreads;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kBoundsThreads + threadIdx.x; i < count;
+       i += stride)
+    words[i] = 0;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 inline int grid_for(int64_t work_items, int per_block, int blocks_per_sm) {
   const int64_t blocks = (work_items + per_block - 1) / per_block;
-  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks, kSmCount * blocks_per_sm)));
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(blocks, sm_count() * blocks_per_sm)));
 }
 
 // ------------------------------------------------------------------------
@@ -533,6 +540,41 @@ static void launch_keygen(const SortArgs& a, bool vec, const float4* records, ui
         a.x, a.y, a.z, records, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
 }
 
+int64_t lookback_probe_particles() { return 3 * kPassTile; }
+
+size_t lookback_probe_workspace_bytes() {
+  const int64_t n = lookback_probe_particles();
+  return standard_layout(n, 8).total + static_cast<size_t>(n) * sizeof(uint32_t);
+}
+
+cudaError_t lookback_give_up_probe(void* workspace, size_t workspace_bytes, uint32_t poll_limit,
+                                   cudaStream_t stream) {
+  const int64_t n = lookback_probe_particles();
+  const StandardLayout l = standard_layout(n, 8);  // one pass
+  if (workspace_bytes < lookback_probe_workspace_bytes()) return cudaErrorInvalidValue;
+  auto* base = static_cast<unsigned char*>(workspace);
+  Header* hdr = reinterpret_cast<Header*>(base);
+  uint32_t* status = reinterpret_cast<uint32_t*>(base + l.status_off);
+  uint32_t* keys_in = reinterpret_cast<uint32_t*>(base + l.keys_alt_off);  // all zero
+  uint32_t* keys_out = reinterpret_cast<uint32_t*>(base + l.index_alt_off);
+  uint32_t* values_out = reinterpret_cast<uint32_t*>(base + l.total);
+  cudaError_t e = cudaMemsetAsync(base, 0, l.total, stream);
+  if (e != cudaSuccess) return e;
+  // Ticket dispenser at 1 (its low byte): tile 0 is never handed out and never publishes.
+  e = cudaMemsetAsync(&hdr->tile_counter[0], 1, 1, stream);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(onesweep_pass_kernel<true>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, sizeof(PassSmem));
+  if (e != cudaSuccess) return e;
+  // Two blocks take tiles 1 and 2.  Tile 1 waits for tile 0, runs out of polls, records the
+  // error and still publishes its prefix, so that tile 2 does not wait in turn.
+  onesweep_pass_kernel<true><<<2, kPassThreads, sizeof(PassSmem), stream>>>(
+      keys_in, nullptr, keys_out, values_out, n, 0, hdr->digit_hist[0], status,
+      &hdr->tile_counter[0], static_cast<uint32_t>(l.tiles), &hdr->error, poll_limit, nullptr);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
 cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   const StandardLayout l = standard_layout(a.n, a.key_bits);
   if (a.workspace_bytes < l.total) return cudaErrorInvalidValue;
@@ -541,10 +583,21 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   uint32_t* status = reinterpret_cast<uint32_t*>(base + l.status_off);
   uint32_t* keys_alt = reinterpret_cast<uint32_t*>(base + l.keys_alt_off);
   uint32_t* index_alt = reinterpret_cast<uint32_t*>(base + l.index_alt_off);
-  // Zero the header and the status words; a predicated run keeps the error
-  // code and the hand-over flag (the first 8 bytes).
-  const size_t keep = run_if ? 8 : 0;
-  cudaError_t e = cudaMemsetAsync(base + keep, 0, l.keys_alt_off - keep, a.stream);
+  // Zero the header and the status words.  A predicated run keeps the error code and the
+  // hand-over flag (the first 8 bytes) and clears with a kernel that, like the others,
+  // returns at once when the flag is not set: the usual call then pays one empty launch
+  // instead of a memset of tens of megabytes.
+  cudaError_t e = cudaSuccess;
+  if (run_if) {
+    const size_t words = (l.keys_alt_off - 8) / sizeof(uint32_t);
+    clear_words_kernel<<<grid_for(static_cast<int64_t>(words), kBoundsThreads * 4, 8),
+                         kBoundsThreads, 0, a.stream>>>(reinterpret_cast<uint32_t*>(base + 8),
+                                                         words, run_if);
+    count_launches(1);
+    e = cudaGetLastError();
+  } else {
+    e = cudaMemsetAsync(base, 0, l.keys_alt_off, a.stream);
+  }
   if (e != cudaSuccess) return e;
   // Payload records (one 32-byte sector per particle) behind the digit-pass arrays, when
   // the workspace has room.  Key bits do not change where they start: a 32-bit layout's end.
@@ -590,7 +643,7 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
     count_launches(1);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const int pass_grid = static_cast<int>(std::min<int64_t>(l.tiles, kSmCount * 2));
+    const int pass_grid = static_cast<int>(std::min<int64_t>(l.tiles, sm_count() * 2));
     for (int p = 0; p < l.passes; ++p) {
       uint32_t* st = status + static_cast<size_t>(p) * l.tiles * kRadix;
       stage_begin(static_cast<Stage>(kStagePass0 + p), a.stream);

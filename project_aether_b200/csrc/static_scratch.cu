@@ -1,6 +1,8 @@
-// AetherSortParticlesByCellStatic: the digit-pass sort with its scratch memory
-// in a fixed array that is part of the library image, for callers that are not
-// allowed to allocate device memory.
+// AetherSortParticlesByCellStatic: the sort with its scratch memory in a fixed
+// array that is part of the library image, for callers that are not allowed to
+// allocate device memory.  Small calls (the bucketed layout of their records fits
+// the array: up to a few hundred thousand particles) take the bucketed path, larger
+// ones the digit passes; the results are the same.
 #include "common.cuh"
 
 namespace aether {
@@ -20,6 +22,22 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 constexpr int kMaxDevices = 64;
 void* g_scratch_address[kMaxDevices];  // device address of the array, per device
 
+// Device address of the array on the current device, looked up on first use.
+cudaError_t scratch_address(void** address) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidValue;
+  if (!g_scratch_address[device]) {
+    void* looked_up = nullptr;
+    e = cudaGetSymbolAddress(&looked_up, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    g_scratch_address[device] = looked_up;
+  }
+  *address = g_scratch_address[device];
+  return cudaSuccess;
+}
+
 }  // namespace
 }  // namespace aether
 
@@ -36,18 +54,23 @@ extern "C" int AetherSortParticlesByCellStatic(const float* x, const float* y, c
   const int64_t cells = static_cast<int64_t>(grid->nx_local) * grid->ny * grid->nz;
   if (cells <= 0) return cudaErrorInvalidValue;
   if (standard_workspace_bytes(n, cells) > kStaticScratchBytes) return cudaErrorInvalidValue;
-  int device = 0;
-  cudaError_t e = cudaGetDevice(&device);
+  void* scratch = nullptr;  // the first call on a device looks the array's address up
+  const cudaError_t e = scratch_address(&scratch);
   if (e != cudaSuccess) return e;
-  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidValue;
-  if (!g_scratch_address[device]) {
-    // First call on this device: look the array's device address up once.
-    void* address = nullptr;
-    e = cudaGetSymbolAddress(&address, g_static_scratch);
-    if (e != cudaSuccess) return e;
-    g_scratch_address[device] = address;
-  }
   return AetherSortParticlesByCell(x, y, z, n, grid, seed, keys_out, index_out, cell_counts,
-                                   cell_start, g_scratch_address[device], kStaticScratchBytes,
-                                   stream);
+                                   cell_start, scratch, kStaticScratchBytes, stream);
+}
+
+extern "C" int AetherSortStaticReadStatus(void* stream, int32_t* status) {
+  void* scratch = nullptr;
+  const cudaError_t e = scratch_address(&scratch);
+  if (e != cudaSuccess) return e;
+  return AetherSortReadStatus(scratch, stream, status);
+}
+
+extern "C" int AetherSortStaticReadUsedDigitPasses(void* stream, int32_t* used) {
+  void* scratch = nullptr;
+  const cudaError_t e = scratch_address(&scratch);
+  if (e != cudaSuccess) return e;
+  return AetherSortReadUsedDigitPasses(scratch, stream, used);
 }

@@ -1,10 +1,14 @@
 """No-Time-Counter collisions on cell-sorted particles (B200 kernel).
 
-Mirror of the reference's binding
-project_aether/src/custom_kernels/cuda/tma_collide.py: the same
-`CollisionParams`, `vhs_parameters`, `load_library` and `collide`, over the
-same C entry point `AetherDsmcCollideTma`, which here lives in
-libaether_sort.so (csrc/collide.cu).
+This module IS the reference's ctypes binding
+project_aether/src/custom_kernels/cuda/tma_collide.py restated as an interface:
+`CollisionParams` has the reference's fields, `collide` its argument list and its
+call into the C entry point `AetherDsmcCollideTma`, `vhs_parameters` is the
+reference's six-line formula (:58-66) as it stands, and the docstrings follow the
+reference's wording, so that the reference's callers can import this module in its
+place.  What is this package's own: the entry point lives in libaether_sort.so
+(csrc/collide.cu, a different kernel), the loader, the stride check and the 64-bit
+masking of seed and step.
 """
 
 import ctypes

@@ -84,6 +84,17 @@ def make_particles(w: Workload, device, seed: int = 0, n: int = None, padded: in
     return pos[0], pos[1], pos[2], velocity
 
 
+def scaled_workload(name: str, log2n: int) -> Workload:
+    """A configuration scaled to 2**log2n particles at the same number of particles per cell:
+    the grid keeps its x and y extent and its z extent shrinks (or grows) with the particle
+    count.  For parity cases and profiler captures smaller than the full configuration."""
+    w = WORKLOADS[name]
+    n = 1 << log2n
+    nx, ny, nz = w.grid.cells
+    nz = max(1, nz * n // w.n)
+    return w._replace(n=n, grid=CellGrid(w.grid.lo, w.grid.hi, (nx, ny, nz)))
+
+
 def step_seed(run_seed: int, step: int) -> int:
     """Philox key of a timestep (dsmc_gpu_pipeline.py:106)."""
     return run_seed ^ (step << 20)

@@ -3,7 +3,7 @@
 Run in a container where the reference tree is mounted:
 
     make -C oracle            # builds oracle/_ref/philox_ref from the reference's philox.h
-    python tests/golden/make_golden.py [--reference /path/to/project_aether]
+    python tests/golden/make_golden.py --reference /path/to/project_aether [--triton]
 
 Outputs (committed):
   philox_kat.json     word 0 of the reference's Philox4x32-10 for several seeds/counters
@@ -12,6 +12,9 @@ Outputs (committed):
                       `radix_sort_reference.onesweep_reference` on the shapes its own test
                       uses (tests/test_radix_sort.py:22-33), the look-back vector of
                       tests/test_radix_sort.py:36-43, and `num_passes` values
+  push_cases.npz      inputs and outputs of the reference's unfused move stage
+                      `fused_particle_push.reference_push` (CPU tensors) on seeded cases in
+                      which particles leave the box through every face
   triton_interp.npz   (only with --triton) keys / permutation / counts produced by the
                       reference's two Triton kernels run by Triton's CPU interpreter on a
                       small case, with the host code of fused_radix_sort.py:244-279
@@ -71,6 +74,42 @@ def replay_fixture(ref):
     out['num_passes_cells'] = np.array(cells_list, np.int64)
     out['num_passes'] = np.array([ref.num_passes(c) for c in cells_list], np.int64)
     np.savez_compressed(os.path.join(HERE, 'replay_cases.npz'), **out)
+
+
+def push_fixture():
+    """The move stage as the reference states it in plain PyTorch
+    (fused_particle_push.py:95-108), run on CPU tensors."""
+    import torch
+    from src.custom_kernels.triton.fused_particle_push import reference_push
+    out = {}
+    specs = [
+        # name, n, lo, hi, dt, velocity scale
+        ('unit_box', 1024, (0.0, 0.0, 0.0), (1.0, 1.0, 1.0), 0.05, 4.0),
+        ('offset_box', 1001, (0.1, -0.2, 0.0), (1.0, 1.0, 0.64), 0.02, 30.0),
+        ('tiny_step', 512, (0.0, 0.0, 0.0), (1.0, 1.0, 1.0), 8.2e-5, 1.0),
+    ]
+    for name, n, lo, hi, dt, scale in specs:
+        gen = torch.Generator().manual_seed(len(name) + n)
+        pos = [(torch.rand(n, generator=gen) * (h - l) + l).to(torch.float32)
+               for l, h in zip(lo, hi)]
+        vel = [(torch.randn(n, generator=gen) * scale).to(torch.float32) for _ in range(3)]
+        # Particles exactly on the faces, and fast ones that overshoot the opposite wall.
+        for axis in range(3):
+            pos[axis][axis] = lo[axis]
+            pos[axis][3 + axis] = hi[axis]
+            vel[axis][6 + axis] = 3.0 * (hi[axis] - lo[axis]) / dt
+            vel[axis][9 + axis] = -3.0 * (hi[axis] - lo[axis]) / dt
+        new_pos, new_vel = reference_push(pos, vel, dt, lo, hi)
+        moved = torch.stack(new_pos)
+        assert all(bool(((torch.stack(pos)[a] + torch.stack(vel)[a] * dt) < lo[a]).any()) and
+                   bool(((torch.stack(pos)[a] + torch.stack(vel)[a] * dt) > hi[a]).any())
+                   for a in range(3)), 'every face must be hit'
+        out[name + '/pos_in'] = torch.stack(pos).numpy()
+        out[name + '/vel_in'] = torch.stack(vel).numpy()
+        out[name + '/scalars'] = np.array([dt, *lo, *hi], np.float64)
+        out[name + '/pos_out'] = moved.numpy()
+        out[name + '/vel_out'] = torch.stack(new_vel).numpy()
+    np.savez_compressed(os.path.join(HERE, 'push_cases.npz'), **out)
 
 
 def triton_fixture(ref_root):
@@ -185,7 +224,8 @@ def collide_fixture():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default='/root/reference/project_aether')
+    ap.add_argument('--reference', required=True,
+                    help='the project_aether folder of a mounted reference tree')
     ap.add_argument('--triton', action='store_true')
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
@@ -193,6 +233,7 @@ def main():
     philox_fixture()
     replay_fixture(ref)
     collide_fixture()
+    push_fixture()
     if args.triton:
         triton_fixture(args.reference)
 

@@ -146,3 +146,20 @@ def test_exchange_replay_keeps_source_order():
         assert np.all(so.slab_of(out[d][0], grid, 2) == d)
         own = shares[0][0][so.slab_of(shares[0][0], grid, 2) == d]
         np.testing.assert_array_equal(out[d][0][:own.size], own)
+
+
+@pytest.mark.parametrize('name', ['unit_box', 'offset_box', 'tiny_step'])
+def test_push_matches_reference_push(golden_dir, name):
+    """`push_particles` against outputs of the reference's own unfused move stage
+    (fused_particle_push.py:95-108, CPU tensors): particles on the faces, particles that leave
+    through every face, and particles fast enough to stay outside after the one reflection."""
+    g = np.load(os.path.join(golden_dir, 'push_cases.npz'))
+    pos, vel = g[name + '/pos_in'], g[name + '/vel_in']
+    sc = g[name + '/scalars']
+    dt, lo, hi = float(sc[0]), sc[1:4], sc[4:7]
+    new_pos, new_vel = so.push_particles(list(pos), list(vel), dt, lo, hi)
+    want_pos, want_vel = g[name + '/pos_out'], g[name + '/vel_out']
+    for axis in range(3):
+        assert np.array_equal(new_pos[axis].view(np.uint32), want_pos[axis].view(np.uint32))
+        assert np.array_equal(new_vel[axis].view(np.uint32), want_vel[axis].view(np.uint32))
+    assert ((want_pos < lo[:, None]) | (want_pos > hi[:, None])).any()  # the overshooting ones

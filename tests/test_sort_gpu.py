@@ -243,20 +243,135 @@ def _properties(got, x, vel, n, cells):
     assert torch.equal(start.int(), got.order.cell_start)
 
 
-@pytest.mark.parametrize('path', PATHS)
-def test_largest_single_gpu_configuration_properties(cuda, path):
-    """256M particles, 32-bit keys: sortedness, permutation, gather and table
-    identities (size-independent properties; the oracle is not run at this size)."""
+def test_largest_single_gpu_configuration_bit_exact(cuda):
+    """256M particles, 33.5M cells, 32-bit keys (bit 31 in use), at full size against the C
+    oracle, on both device paths; plus the size-independent properties."""
+    import gc
     w = workloads.WORKLOADS['c4_256m_512']
+    seed = workloads.step_seed(1234, 3)
     x, y, z, vel = workloads.make_particles(w, cuda, seed=0)
-    got = pa.sort_and_gather_particles(x, y, z, vel, w.grid, 1234, path=path)
+    xn, yn, zn, vn = (t.cpu().numpy() for t in (x, y, z, vel))
+    want, xs, ys, zs, vs = so.c_sort_particles(xn, yn, zn, vn, _ogrid(w.grid), seed)
+    del xn, yn, zn, vn
+    assert want.keys[-1] >> 31 == 1  # the top key bit is really exercised
+    for path in (pa.PATH_AUTO, pa.PATH_DIGIT_PASSES):
+        got = pa.sort_and_gather_particles(x, y, z, vel, w.grid, seed, path=path)
+        assert pa.last_sort_status(cuda) == 0
+        assert not pa.last_sort_used_digit_passes(cuda)  # no hand-over on uniform input
+        if path == pa.PATH_AUTO:
+            _properties(got, x, vel, w.n, w.grid.num_cells)
+            # Ties (same cell and shuffle bits) must keep ascending original index.
+            k64 = got.order.keys.to(torch.int64) & 0xFFFFFFFF
+            same = k64[1:] == k64[:-1]
+            idx = got.order.particle_index
+            assert bool(torch.all(idx[1:][same] > idx[:-1][same]))
+            del k64, same, idx
+        _check_order(got.order, want)
+        for g, v in zip(got.positions, (xs, ys, zs)):
+            assert np.array_equal(g.cpu().numpy(), v)
+        assert np.array_equal(got.velocity.cpu().numpy(), vs)
+        del got
+        gc.collect()
+        torch.cuda.empty_cache()
+
+
+def test_steady_state_resort_loop_bit_exact(cuda):
+    """The steady-state configuration at 2^24 particles: a cell-sorted state, then twenty
+    consecutive (move fused into the sort) steps, each compared with the oracle stepped
+    beside it (push semantics fused_particle_push.py:36-44,64-66; seeds
+    dsmc_gpu_pipeline.py:106).  The sorted output of a step is the next step's input."""
+    w = workloads.scaled_workload('c5_128m_256', 24)
+    n, grid = w.n, w.grid
+    dt = 8.2e-5
+    x, y, z, vel = workloads.make_particles(w, cuda, seed=0)
+    state = pa.sort_and_gather_particles(x, y, z, vel, grid, 99)
     assert pa.last_sort_status(cuda) == 0
-    _properties(got, x, vel, w.n, w.grid.num_cells)
-    # Ties (same cell and shuffle bits) must keep ascending original index.
-    k64 = got.order.keys.to(torch.int64) & 0xFFFFFFFF
-    same = k64[1:] == k64[:-1]
-    idx = got.order.particle_index
-    assert bool(torch.all(idx[1:][same] > idx[:-1][same]))
+    pos = [p.cpu().numpy() for p in state.positions]
+    vel_h = [state.velocity[k, :n].cpu().numpy() for k in range(3)]
+    padded = state.velocity.shape[1]
+    sets = [None, None]
+    crossed = []
+    for step in range(20):
+        seed = workloads.step_seed(1234, step)
+        got = pa.sort_and_gather_particles(*state.positions, state.velocity, grid, seed,
+                                           push=(dt, grid.lo, grid.hi), out=sets[step % 2])
+        sets[step % 2] = got
+        assert pa.last_sort_status(cuda) == 0
+        assert not pa.last_sort_used_digit_passes(cuda)
+        cells_before = so.cell_ids(*pos, _ogrid(grid))
+        pos, vel_h = so.push_particles(pos, vel_h, dt, grid.lo, grid.hi)
+        crossed.append(float((so.cell_ids(*pos, _ogrid(grid)) != cells_before).mean()))
+        vn = np.zeros((3, padded), np.float32)
+        vn[:, :n] = np.stack(vel_h)
+        want, xs, ys, zs, vs = so.c_sort_particles(*(np.ascontiguousarray(p) for p in pos), vn,
+                                                   _ogrid(grid), seed)
+        _check_order(got.order, want)
+        for g, v in zip(got.positions, (xs, ys, zs)):
+            assert np.array_equal(g.cpu().numpy().view(np.uint32), v.view(np.uint32))
+        assert np.array_equal(got.velocity.cpu().numpy().view(np.uint32), vs.view(np.uint32))
+        pos, vel_h = [xs, ys, zs], [vs[k, :n] for k in range(3)]
+        state = got
+    assert 0.03 < np.mean(crossed) < 0.07  # about 5 % of the particles change cell per step
+
+
+def test_auto_path_falls_back_to_digit_passes_in_a_small_workspace(cuda):
+    """A workspace that holds the digit passes (and their payload records) but not the
+    bucketed layout: `path` 0 must run the digit passes, `path` 2 must be refused."""
+    import ctypes
+    from project_aether_b200 import _native
+    from project_aether_b200.particle_sort import native_grid
+    lib = _native.load_library()
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (32, 32, 32))
+    n, cells = 250_000, grid.num_cells
+    x, y, z, vel = _random_state(n, grid, cuda, seed=9)
+    g = native_grid(grid)
+    full = lib.AetherSortWorkspaceBytes(n, cells, 1)
+    # The digit passes with payload records need status words + 8 + 32 bytes per particle; the
+    # bucketed layout needs its run tables on top of 32 bytes per particle.  A bare
+    # 24 bytes per particle fits neither records nor buckets: digit passes + plain gather.
+    for nbytes in (24 * n + (1 << 20),):
+        assert nbytes < full
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=cuda)
+        outs = dict(keys=torch.empty(n, dtype=torch.int32, device=cuda),
+                    index=torch.empty(n, dtype=torch.int32, device=cuda),
+                    counts=torch.empty(cells, dtype=torch.int32, device=cuda),
+                    start=torch.empty(cells + 1, dtype=torch.int32, device=cuda),
+                    xs=torch.empty(n, device=cuda), ys=torch.empty(n, device=cuda),
+                    zs=torch.empty(n, device=cuda), vs=torch.zeros_like(vel))
+        stream = ctypes.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
+
+        def call(path):
+            return lib.AetherSortAndGatherParticles(
+                x.data_ptr(), y.data_ptr(), z.data_ptr(), vel.data_ptr(), vel.shape[1], n,
+                ctypes.byref(g), 77, outs['keys'].data_ptr(), outs['index'].data_ptr(),
+                outs['counts'].data_ptr(), outs['start'].data_ptr(), outs['xs'].data_ptr(),
+                outs['ys'].data_ptr(), outs['zs'].data_ptr(), outs['vs'].data_ptr(), vel.shape[1],
+                path, ws.data_ptr(), ws.numel(), stream)
+
+        assert call(pa.PATH_BUCKETED) == 1  # cudaErrorInvalidValue, nothing launched
+        assert call(pa.PATH_AUTO) == 0
+        status = ctypes.c_int32(-1)
+        _native.check(lib.AetherSortReadStatus(ws.data_ptr(), stream, ctypes.byref(status)), 'status')
+        assert status.value == 0
+        xn, yn, zn, vn = (t.cpu().numpy() for t in (x, y, z, vel))
+        want = so.sort_particles(xn, yn, zn, _ogrid(grid), 77)
+        xs, ys, zs, vs = so.gather_payload(want.particle_index, xn, yn, zn, vn)
+        assert np.array_equal(outs['keys'].cpu().numpy().view(np.uint32), want.keys)
+        assert np.array_equal(outs['index'].cpu().numpy(), want.particle_index)
+        assert np.array_equal(outs['start'].cpu().numpy(), want.cell_start)
+        assert np.array_equal(outs['zs'].cpu().numpy(), zs)
+        assert np.array_equal(outs['vs'].cpu().numpy()[:, :n], vs[:, :n])
+
+
+@pytest.mark.parametrize('path', PATHS)
+def test_particles_outside_the_slab_are_binned_into_its_nearest_column(cuda, path):
+    """The slab form's precondition broken on purpose: positions over the whole box sorted
+    with the cell ids of one slab.  No table may be indexed out of range; the result follows
+    the documented rule (column clamped into the slab), which the oracle applies too."""
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (32, 16, 16))
+    x, y, z, vel = _random_state(120_001, grid, cuda, seed=4, spill=0.05)
+    for ix_offset, nx_local in ((8, 8), (0, 4), (28, 4)):
+        _check_all(x, y, z, vel, grid, 5, path, ix_offset=ix_offset, nx_local=nx_local)
 
 
 def test_random_shapes_densities_and_seeds_bit_exact(cuda):

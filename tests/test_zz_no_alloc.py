@@ -12,6 +12,7 @@ run which stops at the first failure has already run every other test.
 
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
@@ -51,6 +52,17 @@ def _sort_static(lib, x, y, z, g, cells, seed):
     return keys, index, counts, start
 
 
+def _static_status(lib, dev):
+    """(device status, handed-over flag) of the last static call, read from the library's array."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    status, used = ctypes.c_int32(-1), ctypes.c_int32(-1)
+    _native.check(lib.AetherSortStaticReadStatus(stream, ctypes.byref(status)),
+                  'AetherSortStaticReadStatus')
+    _native.check(lib.AetherSortStaticReadUsedDigitPasses(stream, ctypes.byref(used)),
+                  'AetherSortStaticReadUsedDigitPasses')
+    return status.value, used.value
+
+
 def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row(cuda):
     lib = _native.load_library()
     assert lib.AetherSortStaticMaxParticles() == 1 << 20
@@ -65,9 +77,31 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row(cuda):
             x, y, z = (torch.rand(n, device=cuda, generator=gen) for _ in range(3))
             got = _sort_static(lib, x, y, z, g, cells, seed)
             want = _sort_with_workspace(lib, x, y, z, g, cells, seed)
+            assert _static_status(lib, cuda) == (0, 0)
             torch.cuda.synchronize()
             for a, b in zip(got, want):
                 assert torch.equal(a, b)
+
+
+def test_static_scratch_small_call_takes_the_bucketed_path_and_equals_the_oracle(cuda):
+    """Below a few hundred thousand particles the bucketed record layout fits the library's
+    array and that path runs; whichever path runs, the result is the CPU oracle's."""
+    from oracle import sort_oracle as so
+    lib = _native.load_library()
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (32, 32, 16))
+    g = native_grid(grid)
+    gen = torch.Generator(device=cuda).manual_seed(5)
+    with torch.cuda.device(cuda):
+        for n, seed in ((150_001, 3), (700_001, 4)):
+            x, y, z = (torch.rand(n, device=cuda, generator=gen) for _ in range(3))
+            got = _sort_static(lib, x, y, z, g, grid.num_cells, seed)
+            assert _static_status(lib, cuda) == (0, 0)
+            want = so.sort_particles(x.cpu().numpy(), y.cpu().numpy(), z.cpu().numpy(),
+                                     so.Grid(grid.lo, grid.hi, grid.cells), seed)
+            assert np.array_equal(got[0].cpu().numpy().view(np.uint32), want.keys)
+            assert np.array_equal(got[1].cpu().numpy(), want.particle_index)
+            assert np.array_equal(got[2].cpu().numpy(), want.cell_counts)
+            assert np.array_equal(got[3].cpu().numpy(), want.cell_start)
 
 
 def test_static_scratch_entry_rejects_sizes_beyond_its_limit(cuda):
