@@ -233,9 +233,10 @@ int64_t lookback_probe_particles();
 size_t lookback_probe_workspace_bytes();
 
 struct BucketPlan {
-  int shift;        // a bucket is 2^shift consecutive cell ids
+  int shift;          // a bucket is 2^shift consecutive cell ids
   int64_t buckets;
-  bool usable;      // false when even single-cell buckets would be too full on average
+  bool usable;        // false when even single-cell buckets would be too full on average
+  bool small_blocks;  // finish kernel shape: two small blocks per multiprocessor, or one large
 };
 BucketPlan plan_buckets(int64_t n, int64_t num_cells);
 size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells);

@@ -12,13 +12,16 @@
 //                          shuffle bits, fused_radix_sort.py:93-103) and writes
 //                          one 32-byte record {key, index, x, y, z, vx, vy, vz}
 //                          into the particle's bucket
-//   bucket_finish_kernel   one thread block per bucket: a counting sort on the
-//                          low key bits in shared memory, ties put in index
-//                          order, then coalesced SoA output of keys, indices,
-//                          positions, velocities and the bucket's rows of
-//                          cell_counts / cell_start (replaces the digit passes,
-//                          the last-pass count atomics, torch.cumsum and the
-//                          payload gather: fused_radix_sort.py:116-203,277-279,
+//   bucket_finish_kernel   a thread block takes a GROUP of consecutive buckets
+//                          that fits its shared memory (cut on the device from
+//                          the bucket totals, so dense and thin regions both
+//                          fill a block): a counting sort on the low key bits
+//                          in shared memory, ties put in index order, then
+//                          coalesced SoA output of keys, indices, positions,
+//                          velocities and the group's rows of cell_counts /
+//                          cell_start (replaces the digit passes, the last-pass
+//                          count atomics, torch.cumsum and the payload gather:
+//                          fused_radix_sort.py:116-203,277-279,
 //                          dsmc_gpu_pipeline.py:107-109)
 //
 // The result equals the stable sort by key: the records of a bucket arrive in
@@ -30,7 +33,9 @@
 // runs are laid out [chunk][bucket].  While chunk c is being scattered all
 // stores fall into its 128 MB region instead of the whole record array: B200
 // serves scattered 32-byte stores about 1.6 times faster that way (measured).
-// The finish kernel collects a bucket from its runs, one bulk copy per chunk.
+// Consecutive buckets are neighbours inside a chunk's region, so a group of
+// buckets is still one contiguous run per chunk: the finish kernel collects a
+// group with one bulk copy per chunk.
 #include <algorithm>
 
 #include "common.cuh"
@@ -48,13 +53,49 @@ constexpr int kCountThreads = 512;       // blocks that share an SM (table up to
 constexpr int kCountThreadsWide = 1024;  // one block per SM (table up to 200 KB)
 
 constexpr int kChunkLog = 22;      // particles per chunk of the record layout (2^22; 2^21, 2^23
-                                   // and 2^24 measured slower end to end) ...
-constexpr int kNoChunkLog = 31;    // ... or one chunk for everything
+                                   // and 2^24 measured slower end to end)
 
-// Work unit = one slice of one chunk; a block counts the slice into a table
-// (shared memory, or the global counts directly when the table does not fit)
-// and adds the table to the chunk's row of counts, count[chunk * buckets + b].
-template <bool SHARED, bool VEC, int THREADS>
+// Where a block keeps its counts while it works through a slice.
+enum CountTable {
+  kTableGlobal = 0,    // no table: adds go straight to the chunk's row of counts
+  kTableShared32 = 1,  // 32-bit counters in shared memory (up to 200 KB: 51,200 buckets)
+  kTableShared16 = 2,  // 16-bit counters, two per word (up to 102,400 buckets); a slice holds
+                       // fewer than 65,536 particles, so no counter can carry into its neighbour
+};
+constexpr int kSlice16 = 61440;  // particles per slice with 16-bit counters (15 rounds of 4096)
+
+template <int TABLE>
+__device__ __forceinline__ void table_add(uint32_t* table, uint32_t bin, uint32_t count) {
+  if (TABLE == kTableShared16) atomicAdd(&table[bin >> 1], count << (16 * (bin & 1)));
+  else atomicAdd(&table[bin], count);
+}
+
+// One count per lane into `table`; lanes that hit the same bin share one add when the whole
+// warp agrees or (through match.any) when neighbouring lanes do.
+template <int TABLE>
+__device__ __forceinline__ void count_add(uint32_t* table, uint32_t bin, bool valid) {
+  const uint32_t active = __ballot_sync(0xffffffffu, valid);
+  if (active == 0) return;
+  const int first = __ffs(active) - 1;
+  const uint32_t first_bin = __shfl_sync(0xffffffffu, bin, first);
+  const bool uniform = __all_sync(0xffffffffu, !valid || bin == first_bin);
+  if (uniform) {
+    if (static_cast<int>(lane_id()) == first) table_add<TABLE>(table, first_bin, __popc(active));
+    return;
+  }
+  const uint32_t next_bin = __shfl_down_sync(0xffffffffu, bin, 1);
+  const bool clustered = __any_sync(0xffffffffu, valid && lane_id() < 31 && next_bin == bin);
+  if (clustered) {
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? bin : 0xffffffffu) & active;
+    if (valid && (peers & lanemask_lt()) == 0) table_add<TABLE>(table, bin, __popc(peers));
+  } else if (valid) {
+    table_add<TABLE>(table, bin, 1u);
+  }
+}
+
+// Work unit = one slice of one chunk; a block counts the slice into its table and adds the
+// table to the chunk's row of counts, count[chunk * buckets + b].
+template <int TABLE, bool VEC, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
@@ -62,14 +103,15 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     int buckets, int chunks, int chunk_log, int parts, int64_t slice,
                     uint32_t* __restrict__ bucket_count) {
   extern __shared__ uint32_t hist[];
+  const int table_words = TABLE == kTableShared16 ? (buckets + 1) / 2 : buckets;
   for (int unit = blockIdx.x; unit < chunks * parts; unit += gridDim.x) {
     const int chunk = unit / parts, part = unit % parts;
     uint32_t* row = bucket_count + static_cast<size_t>(chunk) * buckets;
-    if (SHARED) {
-      for (int i = threadIdx.x; i < buckets; i += THREADS) hist[i] = 0;
+    if (TABLE != kTableGlobal) {
+      for (int i = threadIdx.x; i < table_words; i += THREADS) hist[i] = 0;
       __syncthreads();
     }
-    uint32_t* target = SHARED ? hist : row;
+    uint32_t* target = TABLE != kTableGlobal ? hist : row;
     const int64_t chunk_first = static_cast<int64_t>(chunk) << chunk_log;
     const int64_t chunk_last = min(static_cast<long long>(n),
                                    static_cast<long long>(chunk_first + (int64_t{1} << chunk_log)));
@@ -118,12 +160,19 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        bin_add(target, cell_of(px[k], py[k], pz[k], g) >> shift, i0 + k < last);
+        count_add<TABLE>(target, cell_of(px[k], py[k], pz[k], g) >> shift, i0 + k < last);
     }
-    if (SHARED) {
+    if (TABLE != kTableGlobal) {
       __syncthreads();
-      for (int i = threadIdx.x; i < buckets; i += THREADS)
-        if (hist[i]) atomicAdd(&row[i], hist[i]);
+      for (int i = threadIdx.x; i < table_words; i += THREADS) {
+        const uint32_t w = hist[i];
+        if (TABLE == kTableShared16) {
+          if (w & 0xffffu) atomicAdd(&row[2 * i], w & 0xffffu);
+          if (w >> 16) atomicAdd(&row[2 * i + 1], w >> 16);
+        } else if (w) {
+          atomicAdd(&row[i], w);
+        }
+      }
       __syncthreads();
     }
   }
@@ -142,8 +191,10 @@ bucket_total_kernel(const uint32_t* __restrict__ bucket_count, int buckets, int 
 
 // Exclusive scan of the [chunk][bucket] counts in memory order: where every run
 // starts in the record array.  Two levels (1024 entries per block, then the
-// block totals), then one pass that writes the run starts as scatter cursors and,
-// transposed to [bucket][chunk], as the run table the finish kernel reads.
+// block totals), then one pass that writes the run starts twice: as the scatter's
+// cursors, which the scatter advances, and as the table run_begin[chunk * buckets + b]
+// (with the total behind its last entry) from which the finish kernel takes the run
+// of any range of buckets [b0, b1) in chunk c: run_begin[c*B + b0] .. run_begin[c*B + b1].
 constexpr int kFlatScanBlock = 1024;
 
 __global__ void __launch_bounds__(kFlatScanBlock)
@@ -176,18 +227,14 @@ run_scan_blocks_kernel(uint32_t* __restrict__ block_sum, int blocks) {
 }
 
 __global__ void __launch_bounds__(256)
-run_table_kernel(const uint32_t* __restrict__ count, const uint32_t* __restrict__ local,
-                 const uint32_t* __restrict__ block_sum, int buckets, int chunks,
-                 uint32_t* __restrict__ cursor, uint32_t* __restrict__ run_start,
-                 uint32_t* __restrict__ run_length) {
-  const int64_t entries = static_cast<int64_t>(buckets) * chunks;
+run_table_kernel(const uint32_t* __restrict__ local, const uint32_t* __restrict__ block_sum,
+                 int64_t entries, uint32_t n, uint32_t* __restrict__ cursor,
+                 uint32_t* __restrict__ run_begin) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (i >= entries) return;
-  const uint32_t start = local[i] + block_sum[i / kFlatScanBlock];
-  cursor[i] = start;
-  const int64_t chunk = i / buckets, b = i % buckets;
-  run_start[b * chunks + chunk] = start;
-  run_length[b * chunks + chunk] = count[i];
+  if (i > entries) return;
+  const uint32_t start = i < entries ? local[i] + block_sum[i / kFlatScanBlock] : n;
+  run_begin[i] = start;
+  if (i < entries) cursor[i] = start;
 }
 
 // ------------------------------------------------------------------------
@@ -367,34 +414,52 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 }
 
 // ------------------------------------------------------------------------
-// Finish: one block sorts one bucket in shared memory and writes the output.
+// Finish: a block sorts one group of buckets in shared memory and writes the output.
 // ------------------------------------------------------------------------
-constexpr int kFinishThreads = 1024;
-constexpr int kFinishCapacity = 5376;                      // records per bucket
-constexpr int kFinishItems = (kFinishCapacity + kFinishThreads - 1) / kFinishThreads;  // 6
-constexpr int kMaxLowBits = 15;                            // bits the counters resolve
-constexpr int kMaxShift = 10;                              // bucket = up to 1024 cells
-constexpr int kHistWords = (1 << kMaxLowBits) / 4;         // byte counters, 4 per word
-constexpr int kWordsPerThread = kHistWords / kFinishThreads;  // 8
-constexpr uint32_t kBulkChunkBytes = 32768;                // bytes per bulk copy
-constexpr uint32_t kBulkWaitLimit = 1u << 24;              // polls of the copy barrier
-constexpr int kMaxSegments = 32;                           // runs of cells an oversized bucket is cut into
-constexpr uint32_t kLargestBucket = kMaxSegments * kFinishCapacity;  // beyond this no cut can fit
+constexpr uint32_t kBulkChunkBytes = 32768;  // bytes per bulk copy
+constexpr uint32_t kBulkWaitLimit = 1u << 24;  // polls of the copy barrier
+constexpr int kMaxSegments = 32;  // runs of cells an oversized bucket is cut into
+constexpr int kMaxSuperBuckets = 512;  // buckets in the aligned block a group may not leave
 
+// Two shapes of the finish kernel.  The small one runs two blocks per multiprocessor, so that
+// one block's bulk copy and output stores overlap the other's ranking; it wants buckets of
+// about a thousand records, which the count kernel's table can only offer up to about a
+// hundred million particles.  Above that the large shape (one block per multiprocessor) runs.
+template <int THREADS, int CAPACITY, int LOW_BITS>
+struct FinishShape {
+  static constexpr int kThreads = THREADS;
+  static constexpr int kCapacity = CAPACITY;                // records a block holds
+  static constexpr int kItems = (CAPACITY + THREADS - 1) / THREADS;
+  static constexpr int kLowBits = LOW_BITS;                 // key bits the counters resolve
+  static constexpr int kHistWords = (1 << LOW_BITS) / 4;    // byte counters, 4 per word
+  static constexpr int kWordsPerThread = kHistWords / THREADS;
+  // A group spans at most this many cells: its low key (cell in group, shuffle bits) then has
+  // at most LOW_BITS + 2 bits, two of which the tie step may take.
+  static constexpr int kMaxCells = 1 << (LOW_BITS + 2 - kShuffleBits);
+  static constexpr uint32_t kLargestBucket = static_cast<uint32_t>(kMaxSegments) * CAPACITY;
+  static_assert(kWordsPerThread == 8, "the counter scan reads eight words per thread");
+};
+using FinishSmall = FinishShape<512, 2560, 14>;
+using FinishLarge = FinishShape<1024, 5376, 15>;
+
+template <class Shape>
 struct __align__(128) FinishSmem {
-  uint32_t raw[kFinishCapacity * kRecordWords];  // the bucket's records as they lie in HBM
-  uint32_t hist[kHistWords];     // byte counter per low-key value
-  uint16_t word_prefix[kHistWords];  // exclusive prefix of each counter word
-  uint16_t order[kFinishCapacity];  // record held by each sorted slot
+  uint32_t raw[Shape::kCapacity * kRecordWords];  // the group's records as they lie in HBM
+  uint32_t hist[Shape::kHistWords];     // byte counter per low-key value
+  uint16_t word_prefix[Shape::kHistWords];  // exclusive prefix of each counter word
+  uint16_t order[Shape::kCapacity];     // record held by each sorted slot
   uint32_t warp_sum[32];
   uint32_t total;
   uint32_t gave_up;
+  uint32_t ticket;
   unsigned long long barrier;    // mbarrier of the bulk copy
   uint32_t seg_begin[kMaxSegments + 1];  // oversized bucket: records before each run of cells
   uint16_t seg_first[kMaxSegments + 1];  // ... and the first cell of each run
   uint32_t fill;                         // ... and the records picked so far for the run at hand
 };
-static_assert(sizeof(FinishSmem) <= 227 * 1024, "finish kernel shared memory");
+static_assert(sizeof(FinishSmem<FinishLarge>) <= 227 * 1024, "finish kernel shared memory");
+static_assert(2 * (sizeof(FinishSmem<FinishSmall>) + 1024) <= 228 * 1024,
+              "two small finish blocks must share a multiprocessor");
 
 __device__ __forceinline__ uint32_t byte_sum(uint32_t w) { return __dp4a(w, 0x01010101u, 0u); }
 
@@ -445,33 +510,41 @@ struct FinishOut {
   int64_t padded_sorted;
 };
 
+// Key bits the byte counters must leave to the tie step for a set of `cells` cells.
+template <class Shape>
+__device__ __forceinline__ int drop_for(int cells) {
+  const int low_bits = (cells <= 1 ? 0 : 32 - __clz(cells - 1)) + kShuffleBits;
+  return max(0, low_bits - Shape::kLowBits);
+}
+
 // Sorts the `count` records staged in s.raw (any order) and writes them to the
 // output from slot `begin` on.  The records belong to the cells first_cell ..
-// first_cell + cells_here - 1; `low_base` is the low key (bits below the bucket
-// id) of the first of these cells.  s.hist must be zero over the counters used.
+// first_cell + cells_here - 1 (at most Shape::kMaxCells).  The low key of a record is
+// its key minus the key of the first cell's first shuffle value; the counters resolve
+// all but its `drop` lowest bits, which the tie step orders together with the index.
+// s.hist must be zero over the counters used.
 // Returns false if a byte counter wrapped (more than 255 records on one counter).
-// DROP: the number of low key bits the counters leave out, fixed at compile time
-// (0, 1, 2) or -1 to take it from `drop_at_run_time`.
-template <int DROP>
-__device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out, int count,
+template <class Shape>
+__device__ __forceinline__ bool sort_staged(FinishSmem<Shape>& s, const FinishOut& out, int count,
                                             uint32_t begin, int64_t first_cell, int cells_here,
-                                            uint32_t low_base, uint32_t low_mask,
-                                            int drop_at_run_time) {
-  const int drop = DROP >= 0 ? DROP : drop_at_run_time;
+                                            int drop) {
+  constexpr int kThreads = Shape::kThreads, kItems = Shape::kItems;
+  constexpr int kWordsPerThread = Shape::kWordsPerThread;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t key_base = static_cast<uint32_t>(first_cell) << kShuffleBits;
   const uint32_t drop_mask = (1u << drop) - 1;
   const int cell_words = 32 >> drop;  // counter words per cell
   const int hist_words = max(8, cells_here * cell_words);
 
   // Count the low key bits with byte-wide counters; the value an add returns
   // is the record's rank among the records of its counter.
-  uint32_t packed[kFinishItems];  // counter id | rank << 16
+  uint32_t packed[kItems];  // counter id | rank << 16
 #pragma unroll
-  for (int k = 0; k < kFinishItems; ++k) {
-    const int r = tid + k * kFinishThreads;
+  for (int k = 0; k < kItems; ++k) {
+    const int r = tid + k * kThreads;
     packed[k] = 0;
     if (r < count) {
-      const uint32_t low = ((s.raw[r * kRecordWords] & low_mask) - low_base) >> drop;
+      const uint32_t low = (s.raw[r * kRecordWords] - key_base) >> drop;
       const int sh = 8 * (low & 3);
       const uint32_t old = atomicAdd(&s.hist[low >> 2], 1u << sh);
       packed[k] = low | (((old >> sh) & 0xffu) << 16);
@@ -504,7 +577,7 @@ __device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out,
   if (lane == 31) s.warp_sum[warp] = incl;
   __syncthreads();
   if (warp == 0) {
-    const uint32_t w = s.warp_sum[lane];
+    const uint32_t w = lane < kThreads / 32 ? s.warp_sum[lane] : 0u;
     uint32_t wi = w;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -530,7 +603,7 @@ __device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out,
   if (wrapped) return false;
 
   // Cell tables: every cell is 128 >> drop consecutive counters.
-  for (int c = tid; c < cells_here; c += kFinishThreads) {
+  for (int c = tid; c < cells_here; c += kThreads) {
     const uint32_t lo = s.word_prefix[c * cell_words];
     const uint32_t hi = (c + 1) * cell_words < hist_words ? s.word_prefix[(c + 1) * cell_words]
                                                            : static_cast<uint32_t>(count);
@@ -540,10 +613,10 @@ __device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out,
 
   // Sorted slot of every record: start of its counter's run + arrival rank.  A
   // counter held by one record only (the usual case) is final at once.
-  uint32_t run[kFinishItems];  // run start | run length << 16, for records that share a counter
+  uint32_t run[kItems];  // run start | run length << 16, for records that share a counter
 #pragma unroll
-  for (int k = 0; k < kFinishItems; ++k) {
-    const int r = tid + k * kFinishThreads;
+  for (int k = 0; k < kItems; ++k) {
+    const int r = tid + k * kThreads;
     run[k] = 0;
     if (r < count) {
       const uint32_t low = packed[k] & 0xffffu, rank = packed[k] >> 16;
@@ -561,12 +634,12 @@ __device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out,
   // original index): a record inside such a run moves to (run start + number of
   // smaller records in the run).  Indices stay below 2^30, so the dropped bits
   // ride above them in one word.
-  uint32_t moved[kFinishItems];
+  uint32_t moved[kItems];
 #pragma unroll
-  for (int k = 0; k < kFinishItems; ++k) {
+  for (int k = 0; k < kItems; ++k) {
     moved[k] = 0xffffffffu;
     if (run[k]) {
-      const int r = tid + k * kFinishThreads;
+      const int r = tid + k * kThreads;
       const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
       const uint32_t mine = ((s.raw[r * kRecordWords] & drop_mask) << 30) | s.raw[r * kRecordWords + 1];
       uint32_t smaller = 0;
@@ -579,15 +652,13 @@ __device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out,
   }
   __syncthreads();
 #pragma unroll
-  for (int k = 0; k < kFinishItems; ++k)
-    if (moved[k] != 0xffffffffu) s.order[moved[k]] = static_cast<uint16_t>(tid + k * kFinishThreads);
+  for (int k = 0; k < kItems; ++k)
+    if (moved[k] != 0xffffffffu) s.order[moved[k]] = static_cast<uint16_t>(tid + k * kThreads);
   __syncthreads();
 
   // Coalesced output: each lane pulls one whole record out of shared memory
-  // and writes its eight words to the eight output arrays.  (128-bit stores of
-  // four consecutive slots per thread were measured: slower, 1.45 ms against
-  // 1.32 ms at 64 M particles.)
-  for (int d = tid; d < count; d += kFinishThreads) {
+  // and writes its eight words to the eight output arrays.
+  for (int d = tid; d < count; d += kThreads) {
     const int rec = s.order[d];
     const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords]);
     const uint4 c = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4]);
@@ -609,35 +680,44 @@ __device__ __forceinline__ bool sort_staged(FinishSmem& s, const FinishOut& out,
   return true;
 }
 
+// What the finish kernels need to find the records of a range of buckets.
+struct RunTable {
+  const uint32_t* records;
+  const uint32_t* bucket_start;  // [buckets + 1]: records before each bucket, all chunks
+  const uint32_t* run_begin;     // [chunks * buckets + 1]: first record of run (chunk, bucket)
+  int chunks;
+  int buckets;
+  int shift;                     // a bucket is 2^shift cells
+  int group_shift;               // a group stays inside an aligned block of 2^group_shift buckets
+};
+
 // A bucket with more records than shared memory holds (a dense region: the
 // bucket width is planned from the average load).  The block counts the
 // bucket's records per cell, cuts the cells into up to kMaxSegments runs that
 // fit, and for every run picks the run's records out of the bucket (which it
-// reads from global memory once per run) and sorts them like a small bucket.
+// reads from global memory once per run) and sorts them like a small group.
 // Returns false if it cannot (a single cell larger than shared memory, too many
 // runs, or a wrapped byte counter): the call then goes to the digit passes.
-__device__ bool finish_large_bucket(FinishSmem& s, const FinishOut& out,
-                                    const uint32_t* __restrict__ records,
-                                    const uint32_t* __restrict__ run_start,
-                                    const uint32_t* __restrict__ run_length, int chunks, int b,
-                                    uint32_t begin, int count, int64_t first_cell, int cells_here,
-                                    uint32_t low_mask, int drop) {
+template <class Shape>
+__device__ bool finish_large_bucket(FinishSmem<Shape>& s, const FinishOut& out, const RunTable& t,
+                                    int b, uint32_t begin, int count, int64_t first_cell,
+                                    int cells_here) {
+  constexpr int kThreads = Shape::kThreads, kCapacity = Shape::kCapacity;
   const int tid = threadIdx.x;
-  uint32_t* cell_count = s.hist;  // up to 1024 cells; s.hist is free until a run is sorted
-  for (int c = tid; c < cells_here; c += kFinishThreads) cell_count[c] = 0;
+  uint32_t* cell_count = s.hist;  // one word per cell; s.hist is free until a run is sorted
+  for (int c = tid; c < cells_here; c += kThreads) cell_count[c] = 0;
   __syncthreads();
   // Per-cell counts: one pass over the keys of the bucket's records.
-  for (int c = 0; c < chunks; ++c) {
-    const uint32_t start = chunks == 1 ? begin : run_start[static_cast<size_t>(b) * chunks + c];
-    const uint32_t length = chunks == 1 ? static_cast<uint32_t>(count)
-                                        : run_length[static_cast<size_t>(b) * chunks + c];
-    for (uint32_t i = tid; i < length; i += kFinishThreads) {
-      const uint32_t key = __ldg(records + static_cast<size_t>(start + i) * kRecordWords);
-      atomicAdd(&cell_count[(key & low_mask) >> kShuffleBits], 1u);
+  for (int c = 0; c < t.chunks; ++c) {
+    const size_t entry = static_cast<size_t>(c) * t.buckets + b;
+    const uint32_t start = t.run_begin[entry], length = t.run_begin[entry + 1] - start;
+    for (uint32_t i = tid; i < length; i += kThreads) {
+      const uint32_t key = __ldg(t.records + static_cast<size_t>(start + i) * kRecordWords);
+      atomicAdd(&cell_count[(key >> kShuffleBits) - static_cast<uint32_t>(first_cell)], 1u);
     }
   }
   __syncthreads();
-  // Cut into runs of cells that fit (one thread; at most 1024 cells).
+  // Cut into runs of cells that fit (one thread; at most Shape::kMaxCells cells).
   if (tid == 0) {
     int segments = 0;
     uint32_t load = 0, before = 0;
@@ -646,8 +726,8 @@ __device__ bool finish_large_bucket(FinishSmem& s, const FinishOut& out,
     s.seg_begin[0] = 0;
     for (int c = 0; c < cells_here && ok; ++c) {
       const uint32_t here = cell_count[c];
-      if (here > static_cast<uint32_t>(kFinishCapacity)) ok = false;
-      if (load + here > static_cast<uint32_t>(kFinishCapacity)) {  // close the run before cell c
+      if (here > static_cast<uint32_t>(kCapacity)) ok = false;
+      if (load + here > static_cast<uint32_t>(kCapacity)) {  // close the run before cell c
         before += load;
         load = 0;
         ++segments;
@@ -668,29 +748,28 @@ __device__ bool finish_large_bucket(FinishSmem& s, const FinishOut& out,
   const int segments = static_cast<int>(s.total);
   __syncthreads();
   if (segments == 0) return false;
-  const int cell_words = 32 >> drop;
   for (int k = 0; k < segments; ++k) {
     const int c0 = s.seg_first[k], c1 = s.seg_first[k + 1];
     const uint32_t seg_begin = s.seg_begin[k];
     const int seg_count = static_cast<int>(s.seg_begin[k + 1] - seg_begin);
+    const int drop = drop_for<Shape>(c1 - c0);
     // Zero the counters of this run and the fill cursor (cell_count is overwritten
     // from here on; the cuts above are already in seg_first / seg_begin).
-    const int words = max(8, (c1 - c0) * cell_words);
-    for (int i = tid; i < words; i += kFinishThreads) s.hist[i] = 0;
+    const int words = max(8, (c1 - c0) * (32 >> drop));
+    for (int i = tid; i < words; i += kThreads) s.hist[i] = 0;
     if (tid == 0) s.fill = 0;
     __syncthreads();
-    for (int c = 0; c < chunks; ++c) {
-      const uint32_t start = chunks == 1 ? begin : run_start[static_cast<size_t>(b) * chunks + c];
-      const uint32_t length = chunks == 1 ? static_cast<uint32_t>(count)
-                                          : run_length[static_cast<size_t>(b) * chunks + c];
-      for (uint32_t i = tid; i < length; i += kFinishThreads) {
-        const uint4* rec = reinterpret_cast<const uint4*>(records +
+    for (int c = 0; c < t.chunks; ++c) {
+      const size_t entry = static_cast<size_t>(c) * t.buckets + b;
+      const uint32_t start = t.run_begin[entry], length = t.run_begin[entry + 1] - start;
+      for (uint32_t i = tid; i < length; i += kThreads) {
+        const uint4* rec = reinterpret_cast<const uint4*>(t.records +
                                                           static_cast<size_t>(start + i) * kRecordWords);
         const uint4 lo = __ldg(rec);
-        const int cell = static_cast<int>((lo.x & low_mask) >> kShuffleBits);
+        const int cell = static_cast<int>((lo.x >> kShuffleBits) - static_cast<uint32_t>(first_cell));
         if (cell >= c0 && cell < c1) {
           const uint32_t slot = atomicAdd(&s.fill, 1u);
-          if (slot < static_cast<uint32_t>(kFinishCapacity)) {
+          if (slot < static_cast<uint32_t>(kCapacity)) {
             *reinterpret_cast<uint4*>(&s.raw[slot * kRecordWords]) = lo;
             *reinterpret_cast<uint4*>(&s.raw[slot * kRecordWords + 4]) = __ldg(rec + 1);
           }
@@ -701,30 +780,24 @@ __device__ bool finish_large_bucket(FinishSmem& s, const FinishOut& out,
     const bool consistent = s.fill == static_cast<uint32_t>(seg_count);
     __syncthreads();
     if (!consistent) return false;
-    if (!sort_staged<-1>(s, out, seg_count, begin + seg_begin, first_cell + c0, c1 - c0,
-                         static_cast<uint32_t>(c0) << kShuffleBits, low_mask, drop))
+    if (!sort_staged<Shape>(s, out, seg_count, begin + seg_begin, first_cell + c0, c1 - c0, drop))
       return false;
   }
   return true;
 }
 
-template <int DROP>
-__global__ void __launch_bounds__(kFinishThreads, 1)
-bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __restrict__ bucket_start,
-                     const uint32_t* __restrict__ run_start, const uint32_t* __restrict__ run_length,
-                     int chunks, int buckets, int shift, int64_t n, int64_t num_cells,
-                     FinishOut out, Header* __restrict__ hdr) {
+// Blocks take aligned blocks of 2^group_shift buckets by ticket and cut each into groups of
+// consecutive buckets whose records fit shared memory (greedily, from the bucket totals).  A
+// bucket that does not fit on its own is left to bucket_finish_large_kernel.
+template <class Shape>
+__global__ void __launch_bounds__(Shape::kThreads, Shape::kThreads <= 512 ? 2 : 1)
+bucket_finish_kernel(RunTable t, int64_t n, int64_t num_cells, FinishOut out,
+                     Header* __restrict__ hdr) {
   if (hdr->use_standard) return;
+  constexpr int kThreads = Shape::kThreads, kCapacity = Shape::kCapacity;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  FinishSmem& s = *reinterpret_cast<FinishSmem*>(smem_raw);
+  FinishSmem<Shape>& s = *reinterpret_cast<FinishSmem<Shape>*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // The key bits below the bucket id: shift cell bits and the 7 shuffle bits.  The
-  // counters resolve the upper 15 of them; up to two lowest bits (buckets of 512 or
-  // 1024 cells) are left to the tie step, which orders by (those bits, index).
-  const int low_bits = shift + kShuffleBits;
-  const uint32_t low_mask = (1u << low_bits) - 1;
-  constexpr int drop = DROP;  // max(0, low_bits - kMaxLowBits), chosen by the launcher
-  const int hist_words = max(8, (1 << (low_bits - drop)) / 4);
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s.barrier)) : "memory");
@@ -733,121 +806,118 @@ bucket_finish_kernel(const uint32_t* __restrict__ records, const uint32_t* __res
   }
   __syncthreads();
   uint32_t parity = 0;
+  const int blocks_of_buckets = (t.buckets + (1 << t.group_shift) - 1) >> t.group_shift;
+  // Tickets: the first one is the block's own index, the following ones come from a counter
+  // (zeroed with the header) and are asked for one block of buckets ahead.
+  uint32_t next_ticket = blockIdx.x;
 
-  // Bucket bounds and (warp 0, one chunk per lane) the bucket's run table are
-  // fetched one bucket ahead, so that their latency is not on the path of the copy.
-  const bool lane_runs = chunks > 1 && chunks <= 32;
-  uint32_t next_begin = 0, next_end = 0, next_length = 0, next_start = 0;
-  if (static_cast<int>(blockIdx.x) < buckets) {
-    next_begin = bucket_start[blockIdx.x];
-    next_end = bucket_start[blockIdx.x + 1];
-    if (warp == 0 && lane_runs && lane < chunks) {
-      next_length = run_length[static_cast<size_t>(blockIdx.x) * chunks + lane];
-      next_start = run_start[static_cast<size_t>(blockIdx.x) * chunks + lane];
-    }
-  }
-
-  for (int b = blockIdx.x; b < buckets; b += gridDim.x) {
-    const uint32_t begin = next_begin, end = next_end;
-    const uint32_t my_length = next_length, my_start = next_start;
-    const int count = static_cast<int>(end - begin);
-    {
-      const int nb = b + gridDim.x;
-      if (nb < buckets) {
-        next_begin = bucket_start[nb];
-        next_end = bucket_start[nb + 1];
-        if (warp == 0 && lane_runs && lane < chunks) {
-          next_length = run_length[static_cast<size_t>(nb) * chunks + lane];
-          next_start = run_start[static_cast<size_t>(nb) * chunks + lane];
-        }
-      }
-    }
-    const int64_t first_cell = static_cast<int64_t>(b) << shift;
-    const int cells_here = static_cast<int>(
-        min(static_cast<long long>(1) << shift, static_cast<long long>(num_cells - first_cell)));
-    if (b == buckets - 1 && tid == 0) out.cell_start[num_cells] = static_cast<int32_t>(n);
-    if (count > kFinishCapacity) continue;  // bucket_finish_large_kernel's job
-    // The bucket lies in HBM as one contiguous run of 32-byte records per chunk
-    // (a single run when there is one chunk): fetch the runs back to back into
-    // shared memory with bulk copies while the counters are cleared.  Warp 0
-    // does it: lane l looks up the runs of chunks l, l+32, ... and issues their
-    // copies after lane 0 has told the barrier how many bytes to expect.
-    if (warp == 0 && count > 0) {
-      if (lane == 0) {
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
-                         smem_addr(&s.barrier)),
-                     "r"(static_cast<uint32_t>(count) * kRecordWords * 4u)
-                     : "memory");
-      }
-      __syncwarp();
-      uint32_t offset = 0;  // records of this bucket in earlier chunks
-      for (int c0 = 0; c0 < chunks; c0 += 32) {
-        const int c = c0 + lane;
-        uint32_t length = 0, start = begin;
-        if (chunks == 1) {
-          length = lane == 0 ? static_cast<uint32_t>(count) : 0u;
-        } else if (lane_runs) {
-          length = my_length;  // zero for lanes past the last chunk
-          start = my_start;
-        } else if (c < chunks) {
-          length = run_length[static_cast<size_t>(b) * chunks + c];
-          start = run_start[static_cast<size_t>(b) * chunks + c];
-        }
-        uint32_t incl = length;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += t;
-        }
-        const uint32_t dst_record = offset + incl - length;
-        if (length > 0 && dst_record + length <= static_cast<uint32_t>(count))
-          bulk_copy(s.raw + static_cast<size_t>(dst_record) * kRecordWords,
-                    records + static_cast<size_t>(start) * kRecordWords,
-                    length * kRecordWords * 4u, &s.barrier);
-        offset += __shfl_sync(0xffffffffu, incl, 31);
-      }
-    }
-    for (int i = tid; i < hist_words; i += kFinishThreads) s.hist[i] = 0;
-    if (count > 0) {
-      if (!bulk_load_wait(&s.barrier, parity)) s.gave_up = 1;
-      parity ^= 1;
-    }
+  for (;;) {
+    if (tid == 0) s.ticket = next_ticket;
     __syncthreads();
-    if (s.gave_up) {  // the copy never landed: report and stop without touching the output
-      if (tid == 0) atomicCAS(&hdr->error, 0, kErrBulkCopyTimeout);
-      return;
+    const int block_of_buckets = static_cast<int>(s.ticket);
+    if (block_of_buckets >= blocks_of_buckets) break;
+    if (tid == 0) next_ticket = gridDim.x + atomicAdd(&hdr->aux_counter[0], 1u);
+    const int b_first = block_of_buckets << t.group_shift;
+    const int b_last = min(t.buckets, b_first + (1 << t.group_shift));
+    if (b_last == t.buckets && tid == 0) out.cell_start[num_cells] = static_cast<int32_t>(n);
+
+    int b0 = b_first;
+    uint32_t begin = t.bucket_start[b0];
+    while (b0 < b_last) {
+      // The group [b0, b1): as many buckets as fit.
+      int b1 = b0 + 1;
+      uint32_t end = t.bucket_start[b1];
+      if (end - begin <= static_cast<uint32_t>(kCapacity)) {
+        while (b1 < b_last) {
+          const uint32_t further = t.bucket_start[b1 + 1];
+          if (further - begin > static_cast<uint32_t>(kCapacity)) break;
+          end = further;
+          ++b1;
+        }
+      }
+      const int count = static_cast<int>(end - begin);
+      const int64_t first_cell = static_cast<int64_t>(b0) << t.shift;
+      const int cells_here = static_cast<int>(
+          min(static_cast<long long>(b1 - b0) << t.shift,
+              static_cast<long long>(num_cells - first_cell)));
+      if (count <= kCapacity) {
+        const int drop = drop_for<Shape>(cells_here);
+        const int hist_words = max(8, cells_here * (32 >> drop));
+        // The group lies in HBM as one contiguous run of 32-byte records per chunk: fetch
+        // the runs back to back into shared memory with bulk copies while the counters are
+        // cleared.  Warp 0 does it: lane l looks up the runs of chunks l, l+32, ... and
+        // issues their copies after lane 0 has told the barrier how many bytes to expect.
+        if (warp == 0 && count > 0) {
+          if (lane == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                             smem_addr(&s.barrier)),
+                         "r"(static_cast<uint32_t>(count) * kRecordWords * 4u)
+                         : "memory");
+          }
+          __syncwarp();
+          uint32_t offset = 0;  // records of this group in earlier chunks
+          for (int c0 = 0; c0 < t.chunks; c0 += 32) {
+            const int c = c0 + lane;
+            uint32_t length = 0, start = 0;
+            if (c < t.chunks) {
+              const size_t row = static_cast<size_t>(c) * t.buckets;
+              start = t.run_begin[row + b0];
+              length = t.run_begin[row + b1] - start;
+            }
+            uint32_t incl = length;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+              if (lane >= o) incl += up;
+            }
+            const uint32_t dst_record = offset + incl - length;
+            if (length > 0 && dst_record + length <= static_cast<uint32_t>(count))
+              bulk_copy(s.raw + static_cast<size_t>(dst_record) * kRecordWords,
+                        t.records + static_cast<size_t>(start) * kRecordWords,
+                        length * kRecordWords * 4u, &s.barrier);
+            offset += __shfl_sync(0xffffffffu, incl, 31);
+          }
+        }
+        for (int i = tid; i < hist_words; i += kThreads) s.hist[i] = 0;
+        if (count > 0) {
+          if (!bulk_load_wait(&s.barrier, parity)) s.gave_up = 1;
+          parity ^= 1;
+        }
+        __syncthreads();
+        if (s.gave_up) {  // the copy never landed: report and stop without touching the output
+          if (tid == 0) atomicCAS(&hdr->error, 0, kErrBulkCopyTimeout);
+          return;
+        }
+        if (!sort_staged<Shape>(s, out, count, begin, first_cell, cells_here, drop)) {
+          if (tid == 0) hdr->use_standard = 1;
+        }
+      }
+      b0 = b1;
+      begin = end;
     }
-    if (!sort_staged<DROP>(s, out, count, begin, first_cell, cells_here, 0u, low_mask, drop)) {
-      if (tid == 0) hdr->use_standard = 1;
-    }
+    __syncthreads();  // everyone has read the ticket before thread 0 writes the next one
   }
 }
 
 // The buckets the kernel above skipped: those with more records than its shared
 // memory holds.  Usually there are none and every block returns after a look at
-// its share of the bucket table.
-__global__ void __launch_bounds__(kFinishThreads, 1)
-bucket_finish_large_kernel(const uint32_t* __restrict__ records,
-                           const uint32_t* __restrict__ bucket_start,
-                           const uint32_t* __restrict__ run_start,
-                           const uint32_t* __restrict__ run_length, int chunks, int buckets,
-                           int shift, int64_t num_cells, FinishOut out, Header* __restrict__ hdr) {
-  if (hdr->use_standard || hdr->max_bucket <= static_cast<uint32_t>(kFinishCapacity)) return;
+// the largest bucket count.
+template <class Shape>
+__global__ void __launch_bounds__(Shape::kThreads, 1)
+bucket_finish_large_kernel(RunTable t, int64_t num_cells, FinishOut out,
+                           Header* __restrict__ hdr) {
+  if (hdr->use_standard || hdr->max_bucket <= static_cast<uint32_t>(Shape::kCapacity)) return;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  FinishSmem& s = *reinterpret_cast<FinishSmem*>(smem_raw);
-  const int low_bits = shift + kShuffleBits;
-  const uint32_t low_mask = (1u << low_bits) - 1;
-  const int drop = max(0, low_bits - kMaxLowBits);
-  for (int b = blockIdx.x; b < buckets; b += gridDim.x) {
-    const uint32_t begin = bucket_start[b], end = bucket_start[b + 1];
+  FinishSmem<Shape>& s = *reinterpret_cast<FinishSmem<Shape>*>(smem_raw);
+  for (int b = blockIdx.x; b < t.buckets; b += gridDim.x) {
+    const uint32_t begin = t.bucket_start[b], end = t.bucket_start[b + 1];
     const int count = static_cast<int>(end - begin);
-    if (count <= kFinishCapacity) continue;
-    const int64_t first_cell = static_cast<int64_t>(b) << shift;
+    if (count <= Shape::kCapacity) continue;
+    const int64_t first_cell = static_cast<int64_t>(b) << t.shift;
     const int cells_here = static_cast<int>(
-        min(static_cast<long long>(1) << shift, static_cast<long long>(num_cells - first_cell)));
-    if (!finish_large_bucket(s, out, records, run_start, run_length, chunks, b, begin, count,
-                             first_cell, cells_here, low_mask, drop)) {
+        min(static_cast<long long>(1) << t.shift, static_cast<long long>(num_cells - first_cell)));
+    if (!finish_large_bucket<Shape>(s, out, t, b, begin, count, first_cell, cells_here)) {
       if (threadIdx.x == 0) hdr->use_standard = 1;
       return;
     }
@@ -856,14 +926,11 @@ bucket_finish_large_kernel(const uint32_t* __restrict__ records,
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// The chunk-major record layout pays when the scatter is bound by scattered
-// stores and a bucket's runs stay long: up to 32 K buckets.  With more buckets
-// (few particles per bucket and chunk) one chunk holds everything.
-// Smaller inputs take smaller chunks (fewer particles contend for a slot counter, and the
-// chunk's records stay deeper inside L2): measured best 2^20 at 4 M particles, 2^21 at 16 M,
-// 2^22 from 32 M on.
-inline int chunk_log_for(int64_t buckets, int64_t n) {
-  if (buckets > 32768) return kNoChunkLog;
+// The chunk-major record layout pays when the scatter is bound by scattered stores and a
+// bucket's runs stay long enough for the bulk copies.  Smaller inputs take smaller chunks
+// (fewer particles contend for a slot counter, and the chunk's records stay deeper inside
+// L2): measured best 2^20 at 4 M particles, 2^21 at 16 M, 2^22 from 32 M on.
+inline int chunk_log_for(int64_t /*buckets*/, int64_t n) {
   if (n <= (int64_t{1} << 22)) return kChunkLog - 2;
   if (n <= (int64_t{1} << 24)) return kChunkLog - 1;
   return kChunkLog;
@@ -874,8 +941,8 @@ struct BucketLayout {
   int chunks;
   int64_t entries;  // chunks * buckets runs
   int scan_blocks;
-  size_t count_off, total_off, start_off, cursor_off, local_off, block_sum_off, run_start_off,
-      run_length_off, records_off, total;
+  size_t count_off, total_off, start_off, cursor_off, local_off, block_sum_off, run_begin_off,
+      records_off, total;
 };
 
 BucketLayout bucket_layout(int64_t n, int64_t buckets) {
@@ -885,41 +952,55 @@ BucketLayout bucket_layout(int64_t n, int64_t buckets) {
       std::max<int64_t>(1, (n + (int64_t{1} << l.chunk_log) - 1) >> l.chunk_log));
   l.entries = static_cast<int64_t>(l.chunks) * buckets;
   l.scan_blocks = static_cast<int>((l.entries + kFlatScanBlock - 1) / kFlatScanBlock);
-  const bool chunked = l.chunks > 1;
   const size_t words = sizeof(uint32_t);
   l.count_off = sizeof(Header);  // zeroed per call together with the header
   l.total_off = align_up(l.count_off + l.entries * words, 256);
-  l.start_off = align_up(l.total_off + (chunked ? buckets * words : 0), 256);
+  l.start_off = align_up(l.total_off + buckets * words, 256);
   l.cursor_off = align_up(l.start_off + (buckets + 1) * words, 256);
   l.local_off = align_up(l.cursor_off + l.entries * words, 256);
-  l.block_sum_off = align_up(l.local_off + (chunked ? l.entries * words : 0), 256);
-  l.run_start_off = align_up(l.block_sum_off + (chunked ? l.scan_blocks * words : 0), 256);
-  l.run_length_off = align_up(l.run_start_off + (chunked ? l.entries * words : 0), 256);
-  l.records_off = align_up(l.run_length_off + (chunked ? l.entries * words : 0), 256);
+  l.block_sum_off = align_up(l.local_off + l.entries * words, 256);
+  l.run_begin_off = align_up(l.block_sum_off + l.scan_blocks * words, 256);
+  l.records_off = align_up(l.run_begin_off + (l.entries + 1) * words, 256);
   l.total = align_up(l.records_off + static_cast<size_t>(n) * kRecordWords * words, 256);
+  return l;
+}
+
+// Buckets the count kernel can hold in shared memory (16-bit counters, 200 KB).
+constexpr int64_t kMaxTableBuckets = 100 * 1024;
+
+// Largest bucket width 2^s, s <= max_shift, whose average load stays at or below `target`,
+// with at least 2048 buckets (fewer make the slot counters of the scatter contend: measured
+// at 1 M and 4 M particles, 2048 beats 1024, 4096 and 8192).
+int shift_for(int64_t n, int64_t num_cells, int64_t target, int max_shift) {
+  for (int s = max_shift; s > 0; --s) {
+    const int64_t buckets = (num_cells + (int64_t{1} << s) - 1) >> s;
+    if (n <= target * buckets && buckets >= 2048) return s;
+  }
+  return 0;
+}
+
+int log2_floor(int v) {
+  int l = 0;
+  while ((2 << l) <= v) ++l;
   return l;
 }
 
 }  // namespace
 
 BucketPlan plan_buckets(int64_t n, int64_t num_cells) {
-  // Largest bucket width 2^s (s <= 10: the counters of the finish kernel resolve 15
-  // low key bits and its tie step two more) whose average load stays at or below the
-  // target.
   BucketPlan p;
-  p.shift = 0;
-  const int64_t target = 4224;
-  for (int s = kMaxShift; s >= 0; --s) {
-    const int64_t buckets = (num_cells + (int64_t{1} << s) - 1) >> s;
-    // Fewer than 2048 buckets make the slot counters of the scatter contend (measured at 1 M
-    // and 4 M particles: 2048 beats 1024, 4096 and 8192).
-    if ((n <= target * buckets && buckets >= 2048) || s == 0) {
-      p.shift = s;
-      break;
-    }
-  }
+  // The small finish shape (two blocks per multiprocessor) wants buckets well below its
+  // capacity, so that the groups cut from them fill a block whatever the density does
+  // inside a row of cells.
+  p.small_blocks = true;
+  p.shift = shift_for(n, num_cells, 1100, log2_floor(FinishSmall::kMaxCells));
   p.buckets = (num_cells + (int64_t{1} << p.shift) - 1) >> p.shift;
-  p.usable = n > 0 && n <= target * p.buckets && p.buckets <= (int64_t{1} << 24);
+  p.usable = n > 0 && n <= 1100 * p.buckets && p.buckets <= kMaxTableBuckets;
+  if (p.usable) return p;
+  p.small_blocks = false;
+  p.shift = shift_for(n, num_cells, 4224, log2_floor(FinishLarge::kMaxCells));
+  p.buckets = (num_cells + (int64_t{1} << p.shift) - 1) >> p.shift;
+  p.usable = n > 0 && n <= 4224 * p.buckets && p.buckets <= (int64_t{1} << 24);
   return p;
 }
 
@@ -927,6 +1008,28 @@ size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells) {
   const BucketPlan p = plan_buckets(n, num_cells);
   return bucket_layout(n, p.buckets).total;
 }
+
+namespace {
+
+template <class Shape>
+cudaError_t launch_finish(const RunTable& t, const SortArgs& a, const FinishOut& out, Header* hdr) {
+  const int smem = static_cast<int>(sizeof(FinishSmem<Shape>));
+  cudaError_t e = cudaFuncSetAttribute(bucket_finish_kernel<Shape>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(bucket_finish_large_kernel<Shape>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  const int per_sm = Shape::kThreads <= 512 ? 2 : 1;
+  const int blocks_of_buckets = (t.buckets + (1 << t.group_shift) - 1) >> t.group_shift;
+  bucket_finish_kernel<Shape><<<std::min(blocks_of_buckets, sm_count() * per_sm), Shape::kThreads,
+                                smem, a.stream>>>(t, a.n, a.num_cells, out, hdr);
+  bucket_finish_large_kernel<Shape><<<std::min(t.buckets, sm_count()), Shape::kThreads, smem,
+                                      a.stream>>>(t, a.num_cells, out, hdr);
+  return cudaGetLastError();
+}
+
+}  // namespace
 
 // Enqueues the bucketed path.  When a bucket turns out too large for the finish
 // kernel the device sets Header::use_standard and the remaining kernels return
@@ -937,11 +1040,13 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   auto* base = static_cast<unsigned char*>(a.workspace);
   auto words_at = [&](size_t off) { return reinterpret_cast<uint32_t*>(base + off); };
   Header* hdr = reinterpret_cast<Header*>(base);
-  const bool chunked = l.chunks > 1;
   uint32_t* count = words_at(l.count_off);
-  uint32_t* total = chunked ? words_at(l.total_off) : count;
+  uint32_t* total = words_at(l.total_off);
   uint32_t* start = words_at(l.start_off);
   uint32_t* cursor = words_at(l.cursor_off);
+  uint32_t* local = words_at(l.local_off);
+  uint32_t* block_sum = words_at(l.block_sum_off);
+  uint32_t* run_begin = words_at(l.run_begin_off);
   uint32_t* records = words_at(l.records_off);
   cudaError_t e = cudaMemsetAsync(base, 0, l.total_off, a.stream);  // header and run counts
   if (e != cudaSuccess) return e;
@@ -949,68 +1054,62 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   const uint32_t k0 = static_cast<uint32_t>(a.seed), k1 = static_cast<uint32_t>(a.seed >> 32);
   const bool vec = aligned16(a.x) && aligned16(a.y) && aligned16(a.z) &&
                    (!a.velocity || (aligned16(a.velocity) && a.padded % 4 == 0));
-  const size_t table_bytes = static_cast<size_t>(buckets) * sizeof(uint32_t);
 
   stage_begin(kStageBucketCount, a.stream);
   {
-    const bool shared = table_bytes <= 200 * 1024;
+    const size_t bytes32 = static_cast<size_t>(buckets) * sizeof(uint32_t);
+    const size_t bytes16 = (static_cast<size_t>(buckets) + 1) / 2 * sizeof(uint32_t);
+    const int table = bytes32 <= 200 * 1024 ? kTableShared32
+                      : bytes16 <= 200 * 1024 ? kTableShared16 : kTableGlobal;
+    const size_t table_bytes = table == kTableShared32 ? bytes32 : table == kTableShared16 ? bytes16 : 0;
     const bool wide = table_bytes > 96 * 1024;  // one 1024-thread block per SM holds the table
-    const int threads = shared && wide ? kCountThreadsWide : kCountThreads;
-    const int blocks_per_sm = shared ? (wide ? 1 : table_bytes <= 48 * 1024 ? 4 : 2) : 4;
+    const int threads = wide ? kCountThreadsWide : kCountThreads;
+    const int blocks_per_sm = table == kTableGlobal ? 4 : wide ? 1 : table_bytes <= 48 * 1024 ? 4 : 2;
     const int64_t chunk_size = int64_t{1} << l.chunk_log;
     const int64_t covered = std::min<int64_t>(a.n, chunk_size);
     // Slices of a chunk: enough units to fill the GPU twice over, each a multiple of one
     // block round (4 particles per thread) so that the 16-byte loads stay aligned.
     const int want = std::max(1, sm_count() * blocks_per_sm * 2 / l.chunks);
     const int64_t round = threads * 4;
-    const int64_t slice = std::max<int64_t>(round, ((covered + want - 1) / want + round - 1) / round * round);
+    int64_t slice = std::max<int64_t>(round, ((covered + want - 1) / want + round - 1) / round * round);
+    if (table == kTableShared16) slice = std::min<int64_t>(slice, kSlice16 / round * round);
     const int parts = static_cast<int>((covered + slice - 1) / slice);
-    const int grid = std::max(1, std::min(l.chunks * parts, sm_count() * blocks_per_sm));
-    if (shared) {
-      auto kernel = wide ? (vec ? bucket_count_kernel<true, true, kCountThreadsWide>
-                                : bucket_count_kernel<true, false, kCountThreadsWide>)
-                         : (vec ? bucket_count_kernel<true, true, kCountThreads>
-                                : bucket_count_kernel<true, false, kCountThreads>);
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(table_bytes));
-      if (e != cudaSuccess) return e;
-      kernel<<<grid, threads, table_bytes, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push,
-                                                       a.n, a.grid, p.shift, buckets, l.chunks,
-                                                       l.chunk_log, parts, slice, count);
-    } else {
-      auto kernel = vec ? bucket_count_kernel<false, true, kCountThreads>
-                        : bucket_count_kernel<false, false, kCountThreads>;
-      kernel<<<grid, threads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push, a.n,
-                                             a.grid, p.shift, buckets, l.chunks, l.chunk_log,
-                                             parts, slice, count);
-    }
+    const int grid = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>(static_cast<int64_t>(l.chunks) * parts, sm_count() * blocks_per_sm)));
+#define AETHER_COUNT_LAUNCH(TABLE, THREADS)                                                      \
+  do {                                                                                            \
+    auto kernel = vec ? bucket_count_kernel<TABLE, true, THREADS>                                 \
+                      : bucket_count_kernel<TABLE, false, THREADS>;                               \
+    if (table_bytes > 48 * 1024) {                                                                \
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,               \
+                               static_cast<int>(table_bytes));                                    \
+      if (e != cudaSuccess) return e;                                                             \
+    }                                                                                             \
+    kernel<<<grid, THREADS, table_bytes, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push, \
+                                                     a.n, a.grid, p.shift, buckets, l.chunks,     \
+                                                     l.chunk_log, parts, slice, count);           \
+  } while (0)
+    if (table == kTableGlobal) AETHER_COUNT_LAUNCH(kTableGlobal, kCountThreads);
+    else if (table == kTableShared16) AETHER_COUNT_LAUNCH(kTableShared16, kCountThreadsWide);
+    else if (wide) AETHER_COUNT_LAUNCH(kTableShared32, kCountThreadsWide);
+    else AETHER_COUNT_LAUNCH(kTableShared32, kCountThreads);
+#undef AETHER_COUNT_LAUNCH
   }
   stage_end(kStageBucketCount, a.stream);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
   stage_begin(kStageBucketScan, a.stream);
-  uint32_t* run_start = nullptr;
-  uint32_t* run_length = nullptr;
-  if (chunked) {
-    uint32_t* local = words_at(l.local_off);
-    uint32_t* block_sum = words_at(l.block_sum_off);
-    run_start = words_at(l.run_start_off);
-    run_length = words_at(l.run_length_off);
-    bucket_total_kernel<<<(buckets + 255) / 256, 256, 0, a.stream>>>(count, buckets, l.chunks, total);
-    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, kLargestBucket,
-                                                         start, nullptr, hdr);
-    run_scan_local_kernel<<<l.scan_blocks, kFlatScanBlock, 0, a.stream>>>(count, l.entries, local,
-                                                                          block_sum);
-    run_scan_blocks_kernel<<<1, kFlatScanBlock, 0, a.stream>>>(block_sum, l.scan_blocks);
-    run_table_kernel<<<static_cast<int>((l.entries + 255) / 256), 256, 0, a.stream>>>(
-        count, local, block_sum, buckets, l.chunks, cursor, run_start, run_length);
-    count_launches(5);
-  } else {
-    bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(count, buckets, a.n, kLargestBucket,
-                                                         start, cursor, hdr);
-    count_launches(1);
-  }
+  const uint32_t largest = p.small_blocks ? FinishSmall::kLargestBucket : FinishLarge::kLargestBucket;
+  bucket_total_kernel<<<(buckets + 255) / 256, 256, 0, a.stream>>>(count, buckets, l.chunks, total);
+  bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, largest, start,
+                                                       nullptr, hdr);
+  run_scan_local_kernel<<<l.scan_blocks, kFlatScanBlock, 0, a.stream>>>(count, l.entries, local,
+                                                                        block_sum);
+  run_scan_blocks_kernel<<<1, kFlatScanBlock, 0, a.stream>>>(block_sum, l.scan_blocks);
+  run_table_kernel<<<static_cast<int>((l.entries + 1 + 255) / 256), 256, 0, a.stream>>>(
+      local, block_sum, l.entries, static_cast<uint32_t>(a.n), cursor, run_begin);
+  count_launches(5);
   stage_end(kStageBucketScan, a.stream);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -1035,26 +1134,14 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   stage_begin(kStageBucketFinish, a.stream);
   const FinishOut out{a.keys_out, a.index_out, a.cell_counts, a.cell_start, a.xs, a.ys, a.zs,
                       a.vs, a.padded_sorted};
-  {
-    const int drop = std::max(0, p.shift + kShuffleBits - kMaxLowBits);
-    auto kernel = drop == 0 ? bucket_finish_kernel<0>
-                            : drop == 1 ? bucket_finish_kernel<1> : bucket_finish_kernel<2>;
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(sizeof(FinishSmem)));
-    if (e != cudaSuccess) return e;
-    kernel<<<std::min(buckets, sm_count()), kFinishThreads, sizeof(FinishSmem), a.stream>>>(
-        records, start, run_start, run_length, l.chunks, buckets, p.shift, a.n, a.num_cells, out,
-        hdr);
-  }
-  e = cudaFuncSetAttribute(bucket_finish_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(sizeof(FinishSmem)));
-  if (e != cudaSuccess) return e;
-  bucket_finish_large_kernel<<<std::min(buckets, sm_count()), kFinishThreads, sizeof(FinishSmem),
-                               a.stream>>>(records, start, run_start, run_length, l.chunks,
-                                           buckets, p.shift, a.num_cells, out, hdr);
+  RunTable t{records, start, run_begin, l.chunks, buckets, p.shift, 0};
+  const int max_cells = p.small_blocks ? FinishSmall::kMaxCells : FinishLarge::kMaxCells;
+  t.group_shift = std::min(log2_floor(kMaxSuperBuckets), std::max(0, log2_floor(max_cells) - p.shift));
+  e = p.small_blocks ? launch_finish<FinishSmall>(t, a, out, hdr)
+                     : launch_finish<FinishLarge>(t, a, out, hdr);
   stage_end(kStageBucketFinish, a.stream);
   count_launches(2);
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace aether
