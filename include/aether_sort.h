@@ -56,6 +56,16 @@ int AetherSortAbiVersion(void);
  * n >= 2^30, key wider than 32 bits). */
 size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload);
 
+/* How the bucketed path would lay a call out, for diagnostics and tests (no
+ * counterpart in the reference): a bucket is 2^*cells_per_bucket_log2
+ * consecutive cell ids, there are *buckets of them, and the finish kernel sorts
+ * groups of consecutive buckets of at most *group_capacity records at a time
+ * (fuller buckets are cut by cells).  Needs a current CUDA device (the group
+ * capacity depends on its multiprocessor count).  Returns cudaErrorInvalidValue
+ * when the bucketed path cannot take such a call (the digit passes then run). */
+int AetherSortBucketPlan(int64_t n, int64_t num_cells, int32_t* cells_per_bucket_log2,
+                         int64_t* buckets, int32_t* group_capacity);
+
 /* sort_particles_by_cell (fused_radix_sort.py:221-280): sorted keys,
  * permutation (original index of every sorted particle), per-cell counts (C)
  * and exclusive starts (C+1).  Inputs are not modified. */
@@ -164,6 +174,68 @@ int AetherSlabExchangeScatterMoved(const float* x, const float* y, const float* 
                                    int64_t capacity, const int64_t* count_matrix,
                                    int32_t* error_out, void* workspace, size_t workspace_bytes,
                                    void* stream);
+
+/* The sliced form of the exchange and of the local sort behind it, which lets
+ * the two overlap (no counterpart in the reference).  Every rank cuts its input
+ * into `slices` (1..32) runs of consecutive tiles; the exchange kernel tells the
+ * destinations when a slice has been stored, and the destination counts and
+ * scatters slice k of all sources into the records of its sort while later
+ * slices are still on their way; only the finish kernels wait for everything.
+ * The ordering rule, hence every result, is that of the unsliced form.
+ *
+ *   AetherSlabExchangeSliceCounts   after AetherSlabExchangeCount[Moved] on the same
+ *       workspace: slice_counts_out[k * world + d] (device) = particles of slice k for
+ *       rank d.  The ranks all-gather these into count_matrix[s][k][d].
+ *   AetherSlabExchangePrepare       from the gathered matrix: totals_out[s][d] (device,
+ *       what AetherSlabExchangeScatterSliced reads) and this rank's segment table
+ *       (segments_out, AetherSlabSegmentsBytes() bytes of device memory): where every
+ *       source's slice lies in the received arrays.
+ *   AetherSlabExchangeScatterSliced AetherSlabExchangeScatter (with the move fused in when
+ *       lo/hi are not NULL) that, when the last tile of slice k is stored, writes `epoch`
+ *       to word [rank * slices + k] of every peer_flags[d] (host array of device pointers
+ *       into the ranks' flag arrays of world * slices words); slice_done is `slices`
+ *       words of device scratch.  Epochs must grow from step to step.
+ *   AetherSlabExchangeWait          enqueues a one-warp kernel that polls this rank's flag
+ *       array until every source has signalled `slice` of `epoch`.  The wait is bounded:
+ *       after poll_limit polls (256 ns apart) it stores 6 in *error_out (device) and
+ *       returns, and the step must be discarded.
+ *
+ *   AetherSortSliced{Begin,Slice,Finish}  the bucketed sort of the received arrays with one
+ *       chunk of records per slice: Begin clears the tables, Slice k counts, scans and
+ *       scatters the particles of slice k, Finish sorts the buckets and writes all outputs.
+ *       `capacity` is the length of the input arrays; the particle count is read from the
+ *       segment table on the device; `plan_n` (host) is the particle count the bucket
+ *       widths are planned for, e.g. the previous step's.  Workspace from
+ *       AetherSortSlicedWorkspaceBytes.  Results as AetherSortAndGatherParticles. */
+int AetherSlabExchangeSliceCounts(int64_t n, int world, int slices, int64_t* slice_counts_out,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+size_t AetherSlabSegmentsBytes(void);
+int AetherSlabExchangePrepare(const int64_t* count_matrix, int world, int slices, int rank,
+                              int64_t* totals_out, void* segments_out, void* stream);
+int AetherSlabExchangeScatterSliced(const float* x, const float* y, const float* z,
+                                    const float* velocity, int64_t padded, int64_t n, float dt,
+                                    const float* lo, const float* hi, const AetherGrid* grid,
+                                    int world, int rank, float* const* peer_buffers,
+                                    int64_t capacity, const int64_t* totals, int32_t* error_out,
+                                    int slices, uint32_t epoch, uint32_t* slice_done,
+                                    uint32_t* const* peer_flags, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+int AetherSlabExchangeWait(const uint32_t* flags, int world, int slices, int slice,
+                           uint32_t epoch, uint32_t poll_limit, int32_t* error_out, void* stream);
+size_t AetherSortSlicedWorkspaceBytes(int64_t capacity, int64_t plan_n, int64_t num_cells,
+                                      int slices);
+int AetherSortSlicedBegin(int64_t capacity, int64_t plan_n, const AetherGrid* grid, int slices,
+                          void* workspace, size_t workspace_bytes, void* stream);
+int AetherSortSlicedSlice(const float* x, const float* y, const float* z, const float* velocity,
+                          int64_t padded, int64_t capacity, int64_t plan_n,
+                          const AetherGrid* grid, uint64_t seed, const void* segments, int slices,
+                          int slice, void* workspace, size_t workspace_bytes, void* stream);
+int AetherSortSlicedFinish(int64_t capacity, int64_t plan_n, const AetherGrid* grid,
+                           const void* segments, int slices, uint32_t* keys_out,
+                           int32_t* index_out, int32_t* cell_counts, int32_t* cell_start,
+                           float* x_sorted, float* y_sorted, float* z_sorted,
+                           float* velocity_sorted, int64_t padded_sorted, void* workspace,
+                           size_t workspace_bytes, void* stream);
 
 /* The move stage that precedes the sort in the DSMC step: x += v*dt, specular
  * reflection at the six walls, in place (fused_particle_push,

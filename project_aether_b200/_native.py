@@ -27,6 +27,9 @@ _I64 = ctypes.c_int64
 _SIGNATURES = {
     'AetherSortAbiVersion': (ctypes.c_int, []),
     'AetherSortWorkspaceBytes': (ctypes.c_size_t, [_I64, _I64, ctypes.c_int]),
+    'AetherSortBucketPlan': (ctypes.c_int, [_I64, _I64, ctypes.POINTER(ctypes.c_int32),
+                                            ctypes.POINTER(ctypes.c_int64),
+                                            ctypes.POINTER(ctypes.c_int32)]),
     'AetherSortParticlesByCell': (ctypes.c_int, [_P, _P, _P, _I64, ctypes.POINTER(AetherGrid),
                                                  ctypes.c_uint64, _P, _P, _P, _P, _P,
                                                  ctypes.c_size_t, _P]),
@@ -67,6 +70,31 @@ _SIGNATURES = {
                                                       ctypes.POINTER(AetherGrid), ctypes.c_int,
                                                       ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
                                                       _I64, _P, _P, _P, ctypes.c_size_t, _P]),
+    'AetherSlabExchangeSliceCounts': (ctypes.c_int, [_I64, ctypes.c_int, ctypes.c_int, _P, _P,
+                                                     ctypes.c_size_t, _P]),
+    'AetherSlabSegmentsBytes': (ctypes.c_size_t, []),
+    'AetherSlabExchangePrepare': (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P,
+                                                 _P, _P]),
+    'AetherSlabExchangeScatterSliced': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.c_float,
+                                                       ctypes.POINTER(ctypes.c_float),
+                                                       ctypes.POINTER(ctypes.c_float),
+                                                       ctypes.POINTER(AetherGrid), ctypes.c_int,
+                                                       ctypes.c_int,
+                                                       ctypes.POINTER(ctypes.c_void_p), _I64, _P,
+                                                       _P, ctypes.c_int, ctypes.c_uint32, _P,
+                                                       ctypes.POINTER(ctypes.c_void_p), _P,
+                                                       ctypes.c_size_t, _P]),
+    'AetherSlabExchangeWait': (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_uint32, ctypes.c_uint32, _P, _P]),
+    'AetherSortSlicedWorkspaceBytes': (ctypes.c_size_t, [_I64, _I64, _I64, ctypes.c_int]),
+    'AetherSortSlicedBegin': (ctypes.c_int, [_I64, _I64, ctypes.POINTER(AetherGrid), ctypes.c_int,
+                                             _P, ctypes.c_size_t, _P]),
+    'AetherSortSlicedSlice': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, _I64,
+                                             ctypes.POINTER(AetherGrid), ctypes.c_uint64, _P,
+                                             ctypes.c_int, ctypes.c_int, _P, ctypes.c_size_t, _P]),
+    'AetherSortSlicedFinish': (ctypes.c_int, [_I64, _I64, ctypes.POINTER(AetherGrid), _P,
+                                              ctypes.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _I64,
+                                              _P, ctypes.c_size_t, _P]),
     'AetherParticlePush': (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _I64, ctypes.c_float,
                                           ctypes.POINTER(ctypes.c_float),
                                           ctypes.POINTER(ctypes.c_float), _P]),

@@ -215,6 +215,16 @@ extern "C" size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int wit
   return std::max(standard, bucketed_workspace_bytes(n, num_cells));
 }
 
+extern "C" int AetherSortBucketPlan(int64_t n, int64_t num_cells, int32_t* cells_per_bucket_log2,
+                                    int64_t* buckets, int32_t* group_capacity) {
+  if (!count_ok(n) || num_cells <= 0 || key_bits_of(num_cells) > 32) return cudaErrorInvalidValue;
+  const BucketPlan plan = plan_buckets(n, num_cells);
+  if (cells_per_bucket_log2) *cells_per_bucket_log2 = plan.shift;
+  if (buckets) *buckets = plan.buckets;
+  if (group_capacity) *group_capacity = static_cast<int32_t>(bucket_group_capacity(n, plan));
+  return plan.usable ? 0 : cudaErrorInvalidValue;
+}
+
 extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const float* z,
                                          int64_t n, const AetherGrid* grid, uint64_t seed,
                                          uint32_t* keys_out, int32_t* index_out,
@@ -395,14 +405,14 @@ int exchange_scatter(const float* x, const float* y, const float* z, const float
                      int64_t padded, int64_t n, const AetherGrid* grid, int world, int rank,
                      float* const* peer_buffers, int64_t capacity, const int64_t* count_matrix,
                      int32_t* error_out, const PushSpec& push, void* workspace,
-                     size_t workspace_bytes, void* stream) {
+                     size_t workspace_bytes, void* stream, const SliceSignal* signal = nullptr) {
   if (!count_ok(n) || !grid_ok(grid) || !peer_buffers || !count_matrix || !error_out || !workspace)
     return cudaErrorInvalidValue;
   if (capacity <= 0 || capacity % 4 != 0 || world < 1 || world > 8) return cudaErrorInvalidValue;
   if (n > 0 && (!x || !y || !z || !velocity || padded < n)) return cudaErrorInvalidValue;
   return slab_exchange_scatter(x, y, z, velocity, padded, n, *grid, world, rank, peer_buffers,
                                capacity, count_matrix, error_out, push, workspace,
-                               workspace_bytes, static_cast<cudaStream_t>(stream));
+                               workspace_bytes, static_cast<cudaStream_t>(stream), signal);
 }
 }  // namespace
 }  // namespace aether
@@ -443,4 +453,110 @@ extern "C" int AetherSlabExchangeScatterMoved(
   return exchange_scatter(x, y, z, velocity, padded, n, grid, world, rank, peer_buffers, capacity,
                           count_matrix, error_out, push_spec(dt, lo, hi), workspace,
                           workspace_bytes, stream);
+}
+
+// ---- the sliced exchange and the sort of its segmented result ----
+
+extern "C" int AetherSlabExchangeSliceCounts(int64_t n, int world, int slices,
+                                             int64_t* slice_counts_out, void* workspace,
+                                             size_t workspace_bytes, void* stream) {
+  if (!count_ok(n) || !workspace) return cudaErrorInvalidValue;
+  return slab_exchange_slice_counts(n, world, slices, slice_counts_out, workspace, workspace_bytes,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t AetherSlabSegmentsBytes(void) { return sizeof(SliceSegments); }
+
+extern "C" int AetherSlabExchangePrepare(const int64_t* count_matrix, int world, int slices,
+                                         int rank, int64_t* totals_out, void* segments_out,
+                                         void* stream) {
+  return slab_exchange_prepare(count_matrix, world, slices, rank, totals_out,
+                               static_cast<SliceSegments*>(segments_out),
+                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int AetherSlabExchangeScatterSliced(
+    const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
+    int64_t n, float dt, const float* lo, const float* hi, const AetherGrid* grid, int world,
+    int rank, float* const* peer_buffers, int64_t capacity, const int64_t* totals,
+    int32_t* error_out, int slices, uint32_t epoch, uint32_t* slice_done,
+    uint32_t* const* peer_flags, void* workspace, size_t workspace_bytes, void* stream) {
+  if ((lo == nullptr) != (hi == nullptr)) return cudaErrorInvalidValue;
+  const SliceSignal signal{slices, epoch, slice_done, peer_flags};
+  return exchange_scatter(x, y, z, velocity, padded, n, grid, world, rank, peer_buffers, capacity,
+                          totals, error_out, lo ? push_spec(dt, lo, hi) : PushSpec{}, workspace,
+                          workspace_bytes, stream, &signal);
+}
+
+extern "C" int AetherSlabExchangeWait(const uint32_t* flags, int world, int slices, int slice,
+                                      uint32_t epoch, uint32_t poll_limit, int32_t* error_out,
+                                      void* stream) {
+  return slab_wait_slice(flags, world, slices, slice, epoch, poll_limit, error_out,
+                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t AetherSortSlicedWorkspaceBytes(int64_t capacity, int64_t plan_n,
+                                                 int64_t num_cells, int slices) {
+  if (!count_ok(capacity) || !count_ok(plan_n) || plan_n <= 0 || num_cells <= 0 ||
+      key_bits_of(num_cells) > 32 || slices < 1 || slices > kMaxSlices)
+    return 0;
+  return sliced_sort_workspace_bytes(capacity, plan_n, num_cells, slices);
+}
+
+namespace aether {
+namespace {
+bool sliced_args(SortArgs& a, int64_t capacity, int64_t plan_n, const AetherGrid* grid,
+                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (!count_ok(capacity) || !count_ok(plan_n) || plan_n <= 0 || !grid_ok(grid) || !workspace)
+    return false;
+  a.n = capacity;
+  a.grid = *grid;
+  a.num_cells = static_cast<int64_t>(grid->nx_local) * grid->ny * grid->nz;
+  a.key_bits = key_bits_of(a.num_cells);
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return true;
+}
+}  // namespace
+}  // namespace aether
+
+extern "C" int AetherSortSlicedBegin(int64_t capacity, int64_t plan_n, const AetherGrid* grid,
+                                     int slices, void* workspace, size_t workspace_bytes,
+                                     void* stream) {
+  SortArgs a{};
+  if (!sliced_args(a, capacity, plan_n, grid, workspace, workspace_bytes, stream))
+    return cudaErrorInvalidValue;
+  return sliced_sort_begin(a, plan_n, slices);
+}
+
+extern "C" int AetherSortSlicedSlice(const float* x, const float* y, const float* z,
+                                     const float* velocity, int64_t padded, int64_t capacity,
+                                     int64_t plan_n, const AetherGrid* grid, uint64_t seed,
+                                     const void* segments, int slices, int slice, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  SortArgs a{};
+  if (!sliced_args(a, capacity, plan_n, grid, workspace, workspace_bytes, stream))
+    return cudaErrorInvalidValue;
+  a.x = x; a.y = y; a.z = z; a.velocity = velocity; a.padded = padded; a.seed = seed;
+  return sliced_sort_slice(a, plan_n, static_cast<const SliceSegments*>(segments), slices, slice);
+}
+
+extern "C" int AetherSortSlicedFinish(int64_t capacity, int64_t plan_n, const AetherGrid* grid,
+                                      const void* segments, int slices, uint32_t* keys_out,
+                                      int32_t* index_out, int32_t* cell_counts,
+                                      int32_t* cell_start, float* x_sorted, float* y_sorted,
+                                      float* z_sorted, float* velocity_sorted,
+                                      int64_t padded_sorted, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  SortArgs a{};
+  if (!sliced_args(a, capacity, plan_n, grid, workspace, workspace_bytes, stream))
+    return cudaErrorInvalidValue;
+  if (!x_sorted || !y_sorted || !z_sorted || !velocity_sorted || padded_sorted < 4)
+    return cudaErrorInvalidValue;
+  a.keys_out = keys_out; a.index_out = index_out;
+  a.cell_counts = cell_counts; a.cell_start = cell_start;
+  a.xs = x_sorted; a.ys = y_sorted; a.zs = z_sorted; a.vs = velocity_sorted;
+  a.padded_sorted = padded_sorted;
+  return sliced_sort_finish(a, plan_n, static_cast<const SliceSegments*>(segments), slices);
 }

@@ -28,6 +28,25 @@ constexpr int kErrLookbackTimeout = 1;
 constexpr int kErrBucketOverflow = 2;
 constexpr int kErrBulkCopyTimeout = 3;
 constexpr int kErrReceiveOverflow = 5;
+constexpr int kErrExchangeTimeout = 6;
+
+constexpr int kMaxWorld = 8;    // ranks of the multi-GPU decomposition
+constexpr int kMaxSlices = 32;  // slices of one rank's input in the sliced exchange
+
+// What a rank receives in the sliced exchange, slice by slice (device memory, written by
+// slab_exchange_prepare).  The received array is the concatenation over sources s of what s
+// sent, in s's order; source s's slice k occupies [first[k][s], first[k][s] + length[k][s]).
+// The local sort lays its records out with one chunk per slice: chunk k's records start at
+// chunk_base[k] (the particles of all sources' slices before k).
+struct SliceSegments {
+  uint32_t n;        // particles received in all
+  uint32_t slices;
+  uint32_t sources;
+  uint32_t pad;
+  uint32_t chunk_base[kMaxSlices + 1];
+  uint32_t first[kMaxSlices][kMaxWorld];
+  uint32_t length[kMaxSlices][kMaxWorld];
+};
 
 // Workspace header (first 1 KiB of the workspace, zeroed by every call).
 struct alignas(16) Header {
@@ -239,8 +258,23 @@ struct BucketPlan {
   bool small_blocks;  // finish kernel shape: two small blocks per multiprocessor, or one large
 };
 BucketPlan plan_buckets(int64_t n, int64_t num_cells);
+// Most records of a group of buckets (what one block of the finish kernel sorts at a time).
+uint32_t bucket_group_capacity(int64_t n, const BucketPlan& p);
 size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells);
 cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p);
+
+// The bucketed sort of a segmented input, slice by slice (the local sort of the sliced
+// multi-GPU exchange): a.n is the CAPACITY of the input arrays, the particle count and the
+// segments are read on the device; the bucket plan is made for plan_n particles.
+// begin: clears the tables.  slice k: counts, scans and scatters the particles of slice k
+// (every source's segment) into chunk k.  finish: bucket starts, groups, and the finish
+// kernels; uses a.keys_out ... a.vs.
+size_t sliced_sort_workspace_bytes(int64_t capacity, int64_t plan_n, int64_t num_cells, int slices);
+cudaError_t sliced_sort_begin(const SortArgs& a, int64_t plan_n, int slices);
+cudaError_t sliced_sort_slice(const SortArgs& a, int64_t plan_n, const SliceSegments* segments,
+                              int slices, int slice);
+cudaError_t sliced_sort_finish(const SortArgs& a, int64_t plan_n, const SliceSegments* segments,
+                               int slices);
 
 size_t slab_partition_workspace_bytes(int64_t n, int world);
 cudaError_t slab_partition(const float* x, const float* y, const float* z, const float* v,
@@ -262,12 +296,28 @@ cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t n
 cudaError_t slab_exchange_count(const float* x, const float* vx, const PushSpec& push, int64_t n,
                                 const AetherGrid& g, int world, int64_t* totals, void* workspace,
                                 size_t workspace_bytes, cudaStream_t stream);
+// Sliced exchange: the scatter signals every destination when a slice of its tiles is stored.
+struct SliceSignal {
+  int slices;
+  uint32_t epoch;
+  uint32_t* slice_done;           // [slices] device counters (scratch)
+  uint32_t* const* peer_flags;    // [world] host array: rank d's flag array [world * slices]
+};
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
                                   int64_t padded, int64_t n, const AetherGrid& g, int world,
                                   int rank, float* const* peer_buffers, int64_t capacity,
                                   const int64_t* count_matrix, int32_t* error,
                                   const PushSpec& push, void* workspace, size_t workspace_bytes,
-                                  cudaStream_t stream);
+                                  cudaStream_t stream, const SliceSignal* signal = nullptr);
+// From the gathered counts matrix[s][k][d] (particles of source s, slice k, for destination d):
+// this rank's segment table and the totals totals2d[s][d] the exchange kernel reads.
+cudaError_t slab_exchange_prepare(const int64_t* matrix, int world, int slices, int rank,
+                                  int64_t* totals2d, SliceSegments* segments, cudaStream_t stream);
+cudaError_t slab_exchange_slice_counts(int64_t n, int world, int slices, int64_t* slice_counts,
+                                       void* workspace, size_t workspace_bytes,
+                                       cudaStream_t stream);
+cudaError_t slab_wait_slice(const uint32_t* flags, int world, int slices, int slice, uint32_t epoch,
+                            uint32_t poll_limit, int32_t* error, cudaStream_t stream);
 cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,
                           float dt, const float* lo, const float* hi, cudaStream_t stream);
 cudaError_t collide_cells(float* velocity, const int* cell_start, float* sigma_g_max,

@@ -16,7 +16,6 @@
 namespace aether {
 namespace {
 
-constexpr int kMaxWorld = 8;
 constexpr int kSlabThreads = 256;
 constexpr int kSlabItems = 8;
 constexpr int kSlabTile = kSlabThreads * kSlabItems;  // 2048 particles, blocked per thread
@@ -157,6 +156,14 @@ struct SlabTargets {
   int exchange;
   int aligned;                  // every output array starts on a 16-byte boundary
   int32_t* error;               // exchange form: set to kErrReceiveOverflow if a buffer is too small
+  // Sliced exchange: the tiles are taken in `slices` consecutive runs of tiles_per_slice;
+  // when the last tile of slice k has been stored, flag [rank * slices + k] of every
+  // destination is set to `epoch` (peer_flags[d] points into rank d's memory).
+  int slices;
+  int tiles_per_slice;
+  uint32_t epoch;
+  uint32_t* slice_done;         // [slices] tiles finished, zeroed before the launch
+  uint32_t* peer_flags[kMaxWorld];
 };
 
 // Stages the tile in shared memory grouped by destination (stable inside a
@@ -332,6 +339,69 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
       for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + (j - lb)] = stage[c][swizzle(j)];
     }
   }
+  if (tg.slices > 0) {
+    // Every thread's stores, to whichever GPU, are performed before the tile counts as
+    // finished; the block that finishes a slice's last tile tells every destination.
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      if (blockIdx.x == 0) {
+        // Slices without a tile (a short input cut into many slices) are complete as they are.
+        const int with_tiles = (static_cast<int>(gridDim.x) + tg.tiles_per_slice - 1) / tg.tiles_per_slice;
+        for (int k = with_tiles; k < tg.slices; ++k)
+          for (int d = 0; d < world; ++d)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
+                             tg.peer_flags[d] + tg.rank * tg.slices + k), "r"(tg.epoch) : "memory");
+      }
+      const int slice = blockIdx.x / tg.tiles_per_slice;
+      const uint32_t tiles_here = static_cast<uint32_t>(
+          min(tg.tiles_per_slice, static_cast<int>(gridDim.x) - slice * tg.tiles_per_slice));
+      if (atomicAdd(&tg.slice_done[slice], 1u) == tiles_here - 1) {
+        __threadfence_system();
+        for (int d = 0; d < world; ++d)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
+                           tg.peer_flags[d] + tg.rank * tg.slices + slice), "r"(tg.epoch) : "memory");
+      }
+    }
+  }
+}
+
+// Particles per (slice, destination) from the scanned tile offsets: slice k is the tiles
+// [k * tiles_per_slice, (k + 1) * tiles_per_slice) of this rank's input.
+__global__ void __launch_bounds__(256)
+slab_slice_counts_kernel(const uint32_t* __restrict__ tile_offset,
+                         const uint32_t* __restrict__ block_sum, int tiles, int world, int slices,
+                         int tiles_per_slice, int64_t n, int64_t* __restrict__ slice_counts) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= slices * world) return;
+  const int k = i / world, d = i % world;
+  auto offset = [&](int tile) -> int64_t {  // particles for destinations < d, and for d in tiles < tile
+    const int64_t entry = static_cast<int64_t>(d) * tiles + tile;  // (d, tiles) is (d + 1, 0)
+    if (entry >= static_cast<int64_t>(world) * tiles) return n;
+    return static_cast<int64_t>(tile_offset[entry]) + block_sum[entry / kScanBlock];
+  };
+  const int lo = min(tiles, k * tiles_per_slice), hi = min(tiles, (k + 1) * tiles_per_slice);
+  slice_counts[i] = offset(hi) - offset(lo);
+}
+
+// Waits (bounded) until every source rank has signalled slice `slice` of step `epoch`: one
+// lane per source polls its flag in this GPU's own memory.  A wait that runs out records
+// kErrExchangeTimeout and returns; the kernels behind it then work on incomplete data and
+// the caller must discard the step.
+__global__ void __launch_bounds__(32)
+slab_wait_kernel(const uint32_t* __restrict__ flags, int world, int slices, int slice,
+                 uint32_t epoch, uint32_t poll_limit, int32_t* __restrict__ error) {
+  const int s = threadIdx.x;
+  if (s >= world) return;
+  const uint32_t* flag = flags + s * slices + slice;
+  for (uint32_t polls = 0;; ++polls) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (static_cast<int32_t>(seen - epoch) >= 0) return;  // epochs only grow (wrap-safe compare)
+    if (polls >= poll_limit) break;
+    __nanosleep(256);
+  }
+  atomicCAS(error, 0, kErrExchangeTimeout);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -429,16 +499,110 @@ cudaError_t slab_exchange_count(const float* x, const float* vx, const PushSpec&
   return e;
 }
 
+namespace {
+// One thread: the sums are over at most kMaxWorld * kMaxSlices small numbers.
+__global__ void slab_prepare_kernel(const int64_t* __restrict__ matrix, int world, int slices,
+                                    int rank, int64_t* __restrict__ totals2d,
+                                    SliceSegments* __restrict__ seg) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  auto m = [&](int s, int k, int d) { return matrix[(static_cast<int64_t>(s) * slices + k) * world + d]; };
+  for (int s = 0; s < world; ++s)
+    for (int d = 0; d < world; ++d) {
+      int64_t sum = 0;
+      for (int k = 0; k < slices; ++k) sum += m(s, k, d);
+      totals2d[s * world + d] = sum;
+    }
+  uint32_t before = 0;  // particles of lower sources
+  for (int s = 0; s < world; ++s) {
+    uint32_t run = before;
+    for (int k = 0; k < slices; ++k) {
+      seg->first[k][s] = run;
+      seg->length[k][s] = static_cast<uint32_t>(m(s, k, rank));
+      run += static_cast<uint32_t>(m(s, k, rank));
+    }
+    before = run;
+  }
+  uint32_t base = 0;
+  for (int k = 0; k < slices; ++k) {
+    seg->chunk_base[k] = base;
+    for (int s = 0; s < world; ++s) base += static_cast<uint32_t>(m(s, k, rank));
+  }
+  seg->chunk_base[slices] = base;
+  seg->n = base;
+  seg->slices = static_cast<uint32_t>(slices);
+  seg->sources = static_cast<uint32_t>(world);
+  seg->pad = 0;
+}
+
+int slab_tiles(int64_t n) {
+  return static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
+}
+}  // namespace
+
+cudaError_t slab_exchange_prepare(const int64_t* matrix, int world, int slices, int rank,
+                                  int64_t* totals2d, SliceSegments* segments, cudaStream_t stream) {
+  if (!matrix || !totals2d || !segments || world < 1 || world > kMaxWorld || slices < 1 ||
+      slices > kMaxSlices || rank < 0 || rank >= world)
+    return cudaErrorInvalidValue;
+  slab_prepare_kernel<<<1, 32, 0, stream>>>(matrix, world, slices, rank, totals2d, segments);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+cudaError_t slab_exchange_slice_counts(int64_t n, int world, int slices, int64_t* slice_counts,
+                                       void* workspace, size_t workspace_bytes,
+                                       cudaStream_t stream) {
+  if (world < 1 || world > kMaxWorld || slices < 1 || slices > kMaxSlices || !slice_counts)
+    return cudaErrorInvalidValue;
+  if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
+  const int tiles = slab_tiles(n);
+  const int64_t entries = static_cast<int64_t>(tiles) * world;
+  const uint32_t* tile_offset = static_cast<const uint32_t*>(workspace);
+  const uint32_t* block_sum = reinterpret_cast<const uint32_t*>(
+      static_cast<const unsigned char*>(workspace) + align_up(entries * sizeof(uint32_t), 256));
+  const int tiles_per_slice = (tiles + slices - 1) / slices;
+  slab_slice_counts_kernel<<<(slices * world + 255) / 256, 256, 0, stream>>>(
+      tile_offset, block_sum, tiles, world, slices, tiles_per_slice, n, slice_counts);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+cudaError_t slab_wait_slice(const uint32_t* flags, int world, int slices, int slice, uint32_t epoch,
+                            uint32_t poll_limit, int32_t* error, cudaStream_t stream) {
+  if (!flags || !error || world < 1 || world > kMaxWorld || slices < 1 || slices > kMaxSlices ||
+      slice < 0 || slice >= slices)
+    return cudaErrorInvalidValue;
+  slab_wait_kernel<<<1, 32, 0, stream>>>(flags, world, slices, slice, epoch, poll_limit, error);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
                                   int64_t padded, int64_t n, const AetherGrid& g, int world,
                                   int rank, float* const* peer_buffers, int64_t capacity,
                                   const int64_t* count_matrix, int32_t* error,
                                   const PushSpec& push, void* workspace, size_t workspace_bytes,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, const SliceSignal* signal) {
   if (world < 1 || world > kMaxWorld || g.nx % world != 0) return cudaErrorInvalidValue;
   if (rank < 0 || rank >= world || !count_matrix || !error) return cudaErrorInvalidValue;
   if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
   SlabTargets tg{};
+  if (signal) {
+    if (signal->slices < 1 || signal->slices > kMaxSlices || !signal->slice_done ||
+        !signal->peer_flags)
+      return cudaErrorInvalidValue;
+    tg.slices = signal->slices;
+    tg.tiles_per_slice = (slab_tiles(n) + signal->slices - 1) / signal->slices;
+    tg.epoch = signal->epoch;
+    tg.slice_done = signal->slice_done;
+    for (int d = 0; d < world; ++d) {
+      if (!signal->peer_flags[d]) return cudaErrorInvalidValue;
+      tg.peer_flags[d] = signal->peer_flags[d];
+    }
+    const cudaError_t e = cudaMemsetAsync(signal->slice_done, 0,
+                                          signal->slices * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+  }
   tg.exchange = 1;
   tg.count_matrix = count_matrix;
   tg.capacity = capacity;

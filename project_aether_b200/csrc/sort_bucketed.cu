@@ -244,8 +244,9 @@ constexpr int kScanThreads = 1024;
 
 __global__ void __launch_bounds__(kScanThreads)
 bucket_scan_kernel(const uint32_t* __restrict__ bucket_count, int buckets, int64_t n,
-                   uint32_t capacity, uint32_t* __restrict__ bucket_start,
-                   uint32_t* __restrict__ cursor, Header* __restrict__ hdr) {
+                   const uint32_t* __restrict__ n_on_device, uint32_t capacity,
+                   uint32_t* __restrict__ bucket_start, uint32_t* __restrict__ cursor,
+                   Header* __restrict__ hdr) {
   __shared__ uint32_t warp_sum[32];
   __shared__ uint32_t biggest;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -285,7 +286,7 @@ bucket_scan_kernel(const uint32_t* __restrict__ bucket_count, int buckets, int64
     run += bucket_count[b];
   }
   if (tid == 0) {
-    bucket_start[buckets] = static_cast<uint32_t>(n);
+    bucket_start[buckets] = n_on_device ? *n_on_device : static_cast<uint32_t>(n);
     hdr->max_bucket = biggest;
     // A bucket above `capacity` cannot be finished at all: hand over before the scatter runs.
     if (biggest > capacity) hdr->use_standard = 1;
@@ -414,12 +415,259 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
 }
 
 // ------------------------------------------------------------------------
+// Segmented input (the local sort of the sliced multi-GPU exchange): the particles of one
+// slice are up to kMaxWorld index ranges of the input arrays, known on the device only.
+// ------------------------------------------------------------------------
+constexpr int kSegmentUnit = 16384;  // particles per work unit of the segment kernels
+
+// Work unit `unit` of slice `k`: the units of source 0's segment, then source 1's, ...  Each
+// segment is cut from its 4-aligned start in pieces of kSegmentUnit, so that the 16-byte loads
+// stay aligned.  Returns false past the last unit; else [first, last) is the piece (first a
+// multiple of 4) and `lo` the first index in it that belongs to the segment.
+__device__ __forceinline__ bool segment_unit(const SliceSegments* __restrict__ seg, int k, int unit,
+                                             int64_t* first, int64_t* last, int64_t* lo) {
+  const int sources = static_cast<int>(seg->sources);
+  for (int s = 0; s < sources; ++s) {
+    const int64_t begin = seg->first[k][s], length = seg->length[k][s];
+    if (length == 0) continue;
+    const int64_t base = begin & ~int64_t{3};
+    const int units = static_cast<int>((begin + length - base + kSegmentUnit - 1) / kSegmentUnit);
+    if (unit < units) {
+      *first = base + static_cast<int64_t>(unit) * kSegmentUnit;
+      *last = min(static_cast<long long>(begin + length), static_cast<long long>(*first + kSegmentUnit));
+      *lo = max(static_cast<long long>(begin), static_cast<long long>(*first));
+      return true;
+    }
+    unit -= units;
+  }
+  return false;
+}
+
+// Particles per bucket of one slice, added to the slice's row of counts.  `capacity` is the
+// length of the input arrays (vector loads must not pass it).
+template <int TABLE, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+bucket_count_segments_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                             const float* __restrict__ z, int64_t capacity, bool vec,
+                             const SliceSegments* __restrict__ seg, int k, AetherGrid g, int shift,
+                             int buckets, uint32_t* __restrict__ row) {
+  extern __shared__ uint32_t hist[];
+  if (TABLE != kTableGlobal) {
+    for (int i = threadIdx.x; i < buckets; i += THREADS) hist[i] = 0;
+    __syncthreads();
+  }
+  uint32_t* target = TABLE != kTableGlobal ? hist : row;
+  int64_t first, last, lo;
+  for (int unit = blockIdx.x; segment_unit(seg, k, unit, &first, &last, &lo); unit += gridDim.x) {
+    for (int64_t i0 = first + static_cast<int64_t>(threadIdx.x) * 4; i0 < last; i0 += THREADS * 4) {
+      float px[4], py[4], pz[4];
+      if (vec && i0 + 4 <= capacity) {
+        const float4 a = ldcs4(x + i0), b = ldcs4(y + i0), c = ldcs4(z + i0);
+        px[0] = a.x; px[1] = a.y; px[2] = a.z; px[3] = a.w;
+        py[0] = b.x; py[1] = b.y; py[2] = b.z; py[3] = b.w;
+        pz[0] = c.x; pz[1] = c.y; pz[2] = c.z; pz[3] = c.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const bool ok = i0 + j >= lo && i0 + j < last;
+          px[j] = ok ? x[i0 + j] : 0.f;
+          py[j] = ok ? y[i0 + j] : 0.f;
+          pz[j] = ok ? z[i0 + j] : 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        count_add<TABLE>(target, cell_of(px[j], py[j], pz[j], g) >> shift,
+                         i0 + j >= lo && i0 + j < last);
+    }
+  }
+  if (TABLE != kTableGlobal) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < buckets; i += THREADS)
+      if (hist[i]) atomicAdd(&row[i], hist[i]);
+  }
+}
+
+// Exclusive scan of one slice's row of counts, offset by the records of the slices before it:
+// the scatter's cursors and the finish kernel's run_begin row of that chunk.  One block.
+__global__ void __launch_bounds__(kFlatScanBlock)
+chunk_scan_kernel(const uint32_t* __restrict__ row, int buckets,
+                  const SliceSegments* __restrict__ seg, int k, uint32_t* __restrict__ cursor_row,
+                  uint32_t* __restrict__ run_begin_row) {
+  __shared__ uint32_t warp_sum[32];
+  __shared__ uint32_t total, carry;
+  if (threadIdx.x == 0) carry = seg->chunk_base[k];
+  __syncthreads();
+  for (int base = 0; base < buckets; base += kFlatScanBlock) {
+    const int i = base + threadIdx.x;
+    const uint32_t v = i < buckets ? row[i] : 0u;
+    const uint32_t excl = block_exclusive_scan(v, warp_sum, &total);
+    if (i < buckets) {
+      cursor_row[i] = carry + excl;
+      run_begin_row[i] = carry + excl;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) carry += total;
+    __syncthreads();
+  }
+  // Behind the last chunk's row: the end of the last run.
+  if (k + 1 == static_cast<int>(seg->slices) && threadIdx.x == 0) run_begin_row[buckets] = seg->n;
+}
+
+// Records of one slice into the runs of chunk k.
+template <int ITEMS>
+__global__ void __launch_bounds__(kScatterThreads, 8 / ITEMS)
+bucket_scatter_segments_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                               const float* __restrict__ z, const float* __restrict__ v,
+                               int64_t padded, int64_t capacity, bool vec,
+                               const SliceSegments* __restrict__ seg, int k, AetherGrid g,
+                               uint32_t k0, uint32_t k1, int shift, int buckets,
+                               uint32_t* __restrict__ cursor_row, uint32_t* __restrict__ records) {
+  int64_t first, last, lo;
+  for (int unit = blockIdx.x; segment_unit(seg, k, unit, &first, &last, &lo); unit += gridDim.x) {
+    for (int64_t i0 = first + static_cast<int64_t>(threadIdx.x) * ITEMS; i0 < last;
+         i0 += kScatterThreads * ITEMS) {
+      float f[6][ITEMS];
+      if (vec && i0 + ITEMS <= capacity) {
+        load_items<ITEMS>(x + i0, f[0]);
+        load_items<ITEMS>(y + i0, f[1]);
+        load_items<ITEMS>(z + i0, f[2]);
+        load_items<ITEMS>(v + i0, f[3]);
+        load_items<ITEMS>(v + padded + i0, f[4]);
+        load_items<ITEMS>(v + 2 * padded + i0, f[5]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j) {
+          const bool ok = i0 + j >= lo && i0 + j < last;
+          f[0][j] = ok ? x[i0 + j] : 0.f;
+          f[1][j] = ok ? y[i0 + j] : 0.f;
+          f[2][j] = ok ? z[i0 + j] : 0.f;
+          f[3][j] = ok ? v[i0 + j] : 0.f;
+          f[4][j] = ok ? v[padded + i0 + j] : 0.f;
+          f[5][j] = ok ? v[2 * padded + i0 + j] : 0.f;
+        }
+      }
+      uint32_t key[ITEMS], slot[ITEMS];
+#pragma unroll
+      for (int j = 0; j < ITEMS; ++j) {
+        const bool ok = i0 + j >= lo && i0 + j < last;
+        const uint32_t cell = cell_of(f[0][j], f[1][j], f[2][j], g);
+        slot[j] = reserve_slot(cursor_row, cell >> shift, ok);
+        key[j] = make_key(cell, static_cast<uint32_t>(i0 + j), k0, k1);
+      }
+#pragma unroll
+      for (int j = 0; j < ITEMS; ++j)
+        if (i0 + j >= lo && i0 + j < last)
+          store_record(records + static_cast<size_t>(slot[j]) * kRecordWords, key[j],
+                       static_cast<uint32_t>(i0 + j), f[0][j], f[1][j], f[2][j], f[3][j], f[4][j],
+                       f[5][j]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------
+// Groups: consecutive buckets that one block finishes together.
+// ------------------------------------------------------------------------
+// One thread per aligned block of 2^group_shift buckets cuts it, greedily from the bucket
+// totals, into groups of consecutive buckets with at most `capacity` records, and appends
+// them (first bucket, end bucket) to the group list; their order in the list is of no
+// consequence.  A bucket that exceeds the capacity on its own is not listed:
+// bucket_finish_large_kernel takes it.
+__global__ void __launch_bounds__(256)
+group_cut_kernel(const uint32_t* __restrict__ bucket_start, int buckets, int group_shift,
+                 uint32_t capacity, uint2* __restrict__ groups, uint32_t* __restrict__ group_count) {
+  const int block_of_buckets = blockIdx.x * 256 + threadIdx.x;
+  const int b_first = block_of_buckets << group_shift;
+  if (b_first >= buckets) return;
+  const int b_last = min(buckets, b_first + (1 << group_shift));
+  uint32_t base = 0;
+  for (int pass = 0; pass < 2; ++pass) {
+    uint32_t found = 0;
+    int b0 = b_first;
+    uint32_t begin = bucket_start[b0];
+    while (b0 < b_last) {
+      int b1 = b0 + 1;
+      uint32_t end = bucket_start[b1];
+      const bool fits = end - begin <= capacity;
+      if (fits) {
+        while (b1 < b_last) {
+          const uint32_t further = bucket_start[b1 + 1];
+          if (further - begin > capacity) break;
+          end = further;
+          ++b1;
+        }
+        if (pass == 1) groups[base + found] = make_uint2(static_cast<uint32_t>(b0), static_cast<uint32_t>(b1));
+        ++found;
+      }
+      b0 = b1;
+      begin = end;
+    }
+    if (pass == 0) {
+      if (found == 0) return;
+      base = atomicAdd(group_count, found);
+    }
+  }
+}
+
+// Words of one row of a group's table: one entry per chunk and three more, rounded up to
+// whole 16-byte pieces (the finish kernel fetches the tables with 16-byte copies).
+__host__ __device__ inline int table_row_words(int chunks) { return (chunks + 3 + 3) / 4 * 4; }
+
+// Where the records of every group lie: per group two rows of table_row_words(chunks) words,
+//   row 0: [c] first record of the group's run in chunk c; [chunks] first output slot of the
+//          group; [chunks + 1], [chunks + 2] its buckets b0, b1
+//   row 1: [c] records of the group in chunks before c; [chunks] records of the group.
+// One warp per group, a lane per chunk.
+__global__ void __launch_bounds__(256)
+group_table_kernel(const uint2* __restrict__ groups, const uint32_t* __restrict__ group_count,
+                   const uint32_t* __restrict__ bucket_start, const uint32_t* __restrict__ run_begin,
+                   int chunks, int buckets, uint32_t* __restrict__ tables) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t total = *group_count;
+  const int row_words = table_row_words(chunks);
+  for (uint32_t g = blockIdx.x * 8 + (threadIdx.x >> 5); g < total; g += gridDim.x * 8) {
+    const uint2 group = groups[g];
+    uint32_t* row0 = tables + static_cast<size_t>(g) * 2 * row_words;
+    uint32_t* row1 = row0 + row_words;
+    uint32_t offset = 0;
+    for (int c0 = 0; c0 < chunks; c0 += 32) {
+      const int c = c0 + lane;
+      uint32_t length = 0, start = 0;
+      if (c < chunks) {
+        const size_t row = static_cast<size_t>(c) * buckets;
+        start = run_begin[row + group.x];
+        length = run_begin[row + group.y] - start;
+      }
+      uint32_t incl = length;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (c < chunks) {
+        row0[c] = start;
+        row1[c] = offset + incl - length;
+      }
+      offset += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      row0[chunks] = bucket_start[group.x];
+      row0[chunks + 1] = group.x;
+      row0[chunks + 2] = group.y;
+      row1[chunks] = offset;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------
 // Finish: a block sorts one group of buckets in shared memory and writes the output.
 // ------------------------------------------------------------------------
 constexpr uint32_t kBulkChunkBytes = 32768;  // bytes per bulk copy
 constexpr uint32_t kBulkWaitLimit = 1u << 24;  // polls of the copy barrier
 constexpr int kMaxSegments = 32;  // runs of cells an oversized bucket is cut into
-constexpr int kMaxSuperBuckets = 512;  // buckets in the aligned block a group may not leave
+constexpr int kMaxGroupBuckets = 512;  // buckets in the aligned block a group may not leave
+constexpr int kMaxChunks = 256;        // 2^30 particles in chunks of 2^22
+constexpr int kTableRowWords = (kMaxChunks + 3 + 3) / 4 * 4;
 
 // Two shapes of the finish kernel.  The small one runs two blocks per multiprocessor, so that
 // one block's bulk copy and output stores overlap the other's ranking; it wants buckets of
@@ -440,7 +688,7 @@ struct FinishShape {
   static_assert(kWordsPerThread == 8, "the counter scan reads eight words per thread");
 };
 using FinishSmall = FinishShape<512, 2560, 14>;
-using FinishLarge = FinishShape<1024, 5376, 15>;
+using FinishLarge = FinishShape<1024, 5120, 15>;
 
 template <class Shape>
 struct __align__(128) FinishSmem {
@@ -451,15 +699,24 @@ struct __align__(128) FinishSmem {
   uint32_t warp_sum[32];
   uint32_t total;
   uint32_t gave_up;
-  uint32_t ticket;
   unsigned long long barrier;    // mbarrier of the bulk copy
   uint32_t seg_begin[kMaxSegments + 1];  // oversized bucket: records before each run of cells
   uint16_t seg_first[kMaxSegments + 1];  // ... and the first cell of each run
   uint32_t fill;                         // ... and the records picked so far for the run at hand
 };
-static_assert(sizeof(FinishSmem<FinishLarge>) <= 227 * 1024, "finish kernel shared memory");
-static_assert(2 * (sizeof(FinishSmem<FinishSmall>) + 1024) <= 228 * 1024,
+// Behind the structure, in the same dynamic allocation: the tables of three consecutive
+// groups, 2 * row_words words each (at most kTableRowWords per row).
+constexpr size_t kSmallShapeTableBytes = 3 * 2 * 16 * sizeof(uint32_t);  // up to 13 chunks
+static_assert(sizeof(FinishSmem<FinishLarge>) + 3 * 2 * kTableRowWords * sizeof(uint32_t) <=
+                  227 * 1024, "finish kernel shared memory");
+static_assert(2 * (sizeof(FinishSmem<FinishSmall>) + kSmallShapeTableBytes + 1024) <= 228 * 1024,
               "two small finish blocks must share a multiprocessor");
+
+template <class Shape>
+__device__ __forceinline__ uint32_t* group_table(FinishSmem<Shape>& s, int q, int row_words) {
+  return reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(&s) + sizeof(FinishSmem<Shape>)) +
+         q * 2 * row_words;
+}
 
 __device__ __forceinline__ uint32_t byte_sum(uint32_t w) { return __dp4a(w, 0x01010101u, 0u); }
 
@@ -685,10 +942,12 @@ struct RunTable {
   const uint32_t* records;
   const uint32_t* bucket_start;  // [buckets + 1]: records before each bucket, all chunks
   const uint32_t* run_begin;     // [chunks * buckets + 1]: first record of run (chunk, bucket)
+  const uint32_t* tables;        // two rows of row_words words per group (group_table_kernel)
+  const uint32_t* group_count;
+  int row_words;
   int chunks;
   int buckets;
   int shift;                     // a bucket is 2^shift cells
-  int group_shift;               // a group stays inside an aligned block of 2^group_shift buckets
 };
 
 // A bucket with more records than shared memory holds (a dense region: the
@@ -786,117 +1045,124 @@ __device__ bool finish_large_bucket(FinishSmem<Shape>& s, const FinishOut& out, 
   return true;
 }
 
-// Blocks take aligned blocks of 2^group_shift buckets by ticket and cut each into groups of
-// consecutive buckets whose records fit shared memory (greedily, from the bucket totals).  A
-// bucket that does not fit on its own is left to bucket_finish_large_kernel.
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Starts the asynchronous copy of the table of group `g` (if there is one) into set `q`.
+template <class Shape>
+__device__ __forceinline__ void fetch_table(FinishSmem<Shape>& s, int q, const RunTable& t,
+                                            uint32_t g, uint32_t groups) {
+  const int pieces = 2 * t.row_words / 4;  // 16-byte pieces of the two rows
+  if (g >= groups || static_cast<int>(threadIdx.x) >= pieces) return;
+  const uint32_t* src = t.tables + static_cast<size_t>(g) * 2 * t.row_words + threadIdx.x * 4;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   smem_addr(group_table(s, q, t.row_words) + threadIdx.x * 4)), "l"(src) : "memory");
+}
+
+// Warp 0: the runs of the group whose table is in set `q`, one per chunk.  FETCH: bulk copies
+// back to back into s.raw, counted on the barrier (lane 0 tells it first how many bytes to
+// expect); otherwise only a request to bring the runs into L2, for the group after.
+template <class Shape, bool FETCH>
+__device__ __forceinline__ void touch_runs(FinishSmem<Shape>& s, int q, const RunTable& t) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t* run_first = group_table(s, q, t.row_words);
+  const uint32_t* run_offset = run_first + t.row_words;
+  const uint32_t count = run_offset[t.chunks];
+  if (count == 0) return;
+  if (FETCH) {
+    if (lane == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                       smem_addr(&s.barrier)), "r"(count * kRecordWords * 4u) : "memory");
+    }
+    __syncwarp();
+  }
+  for (int c = lane; c < t.chunks; c += 32) {
+    const uint32_t length = run_offset[c + 1] - run_offset[c];
+    if (length == 0) continue;
+    const uint32_t* src = t.records + static_cast<size_t>(run_first[c]) * kRecordWords;
+    if (FETCH) {
+      if (run_offset[c + 1] <= static_cast<uint32_t>(Shape::kCapacity))
+        bulk_copy(s.raw + static_cast<size_t>(run_offset[c]) * kRecordWords, src,
+                  length * kRecordWords * 4u, &s.barrier);
+    } else {
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src),
+                   "r"(length * kRecordWords * 4u) : "memory");
+    }
+  }
+}
+
+// A block works through groups blockIdx.x, blockIdx.x + gridDim.x, ... of the group list.
+// What it needs to know about a group (where its runs lie) arrives two groups ahead by
+// asynchronous copies; a group's records are asked into L2 while the group before it is
+// sorted, and copied into shared memory as soon as that one's output is written.
 template <class Shape>
 __global__ void __launch_bounds__(Shape::kThreads, Shape::kThreads <= 512 ? 2 : 1)
-bucket_finish_kernel(RunTable t, int64_t n, int64_t num_cells, FinishOut out,
-                     Header* __restrict__ hdr) {
+bucket_finish_kernel(RunTable t, int64_t n, const uint32_t* __restrict__ n_on_device,
+                     int64_t num_cells, FinishOut out, Header* __restrict__ hdr) {
   if (hdr->use_standard) return;
-  constexpr int kThreads = Shape::kThreads, kCapacity = Shape::kCapacity;
+  constexpr int kThreads = Shape::kThreads;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FinishSmem<Shape>& s = *reinterpret_cast<FinishSmem<Shape>*>(smem_raw);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t groups = *t.group_count;
+  if (blockIdx.x == 0 && tid == 0)
+    out.cell_start[num_cells] = n_on_device ? static_cast<int32_t>(*n_on_device) : static_cast<int32_t>(n);
+  const uint32_t stride = gridDim.x;
+  uint32_t g = blockIdx.x;
+  if (g >= groups) return;
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s.barrier)) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s.gave_up = 0;
   }
+  fetch_table<Shape>(s, 0, t, g, groups);
+  fetch_table<Shape>(s, 1, t, g + stride, groups);
+  copy_commit();
+  copy_wait_all();
   __syncthreads();
+  if (warp == 0) {
+    touch_runs<Shape, true>(s, 0, t);
+    if (g + stride < groups) touch_runs<Shape, false>(s, 1, t);
+  }
   uint32_t parity = 0;
-  const int blocks_of_buckets = (t.buckets + (1 << t.group_shift) - 1) >> t.group_shift;
-  // Tickets: the first one is the block's own index, the following ones come from a counter
-  // (zeroed with the header) and are asked for one block of buckets ahead.
-  uint32_t next_ticket = blockIdx.x;
 
-  for (;;) {
-    if (tid == 0) s.ticket = next_ticket;
-    __syncthreads();
-    const int block_of_buckets = static_cast<int>(s.ticket);
-    if (block_of_buckets >= blocks_of_buckets) break;
-    if (tid == 0) next_ticket = gridDim.x + atomicAdd(&hdr->aux_counter[0], 1u);
-    const int b_first = block_of_buckets << t.group_shift;
-    const int b_last = min(t.buckets, b_first + (1 << t.group_shift));
-    if (b_last == t.buckets && tid == 0) out.cell_start[num_cells] = static_cast<int32_t>(n);
-
-    int b0 = b_first;
-    uint32_t begin = t.bucket_start[b0];
-    while (b0 < b_last) {
-      // The group [b0, b1): as many buckets as fit.
-      int b1 = b0 + 1;
-      uint32_t end = t.bucket_start[b1];
-      if (end - begin <= static_cast<uint32_t>(kCapacity)) {
-        while (b1 < b_last) {
-          const uint32_t further = t.bucket_start[b1 + 1];
-          if (further - begin > static_cast<uint32_t>(kCapacity)) break;
-          end = further;
-          ++b1;
-        }
-      }
-      const int count = static_cast<int>(end - begin);
-      const int64_t first_cell = static_cast<int64_t>(b0) << t.shift;
-      const int cells_here = static_cast<int>(
-          min(static_cast<long long>(b1 - b0) << t.shift,
-              static_cast<long long>(num_cells - first_cell)));
-      if (count <= kCapacity) {
-        const int drop = drop_for<Shape>(cells_here);
-        const int hist_words = max(8, cells_here * (32 >> drop));
-        // The group lies in HBM as one contiguous run of 32-byte records per chunk: fetch
-        // the runs back to back into shared memory with bulk copies while the counters are
-        // cleared.  Warp 0 does it: lane l looks up the runs of chunks l, l+32, ... and
-        // issues their copies after lane 0 has told the barrier how many bytes to expect.
-        if (warp == 0 && count > 0) {
-          if (lane == 0) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
-                             smem_addr(&s.barrier)),
-                         "r"(static_cast<uint32_t>(count) * kRecordWords * 4u)
-                         : "memory");
-          }
-          __syncwarp();
-          uint32_t offset = 0;  // records of this group in earlier chunks
-          for (int c0 = 0; c0 < t.chunks; c0 += 32) {
-            const int c = c0 + lane;
-            uint32_t length = 0, start = 0;
-            if (c < t.chunks) {
-              const size_t row = static_cast<size_t>(c) * t.buckets;
-              start = t.run_begin[row + b0];
-              length = t.run_begin[row + b1] - start;
-            }
-            uint32_t incl = length;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-              const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-              if (lane >= o) incl += up;
-            }
-            const uint32_t dst_record = offset + incl - length;
-            if (length > 0 && dst_record + length <= static_cast<uint32_t>(count))
-              bulk_copy(s.raw + static_cast<size_t>(dst_record) * kRecordWords,
-                        t.records + static_cast<size_t>(start) * kRecordWords,
-                        length * kRecordWords * 4u, &s.barrier);
-            offset += __shfl_sync(0xffffffffu, incl, 31);
-          }
-        }
-        for (int i = tid; i < hist_words; i += kThreads) s.hist[i] = 0;
-        if (count > 0) {
-          if (!bulk_load_wait(&s.barrier, parity)) s.gave_up = 1;
-          parity ^= 1;
-        }
-        __syncthreads();
-        if (s.gave_up) {  // the copy never landed: report and stop without touching the output
-          if (tid == 0) atomicCAS(&hdr->error, 0, kErrBulkCopyTimeout);
-          return;
-        }
-        if (!sort_staged<Shape>(s, out, count, begin, first_cell, cells_here, drop)) {
-          if (tid == 0) hdr->use_standard = 1;
-        }
-      }
-      b0 = b1;
-      begin = end;
+  for (int q = 0; g < groups; g += stride, q = q == 2 ? 0 : q + 1) {
+    const int q1 = q == 2 ? 0 : q + 1, q2 = q1 == 2 ? 0 : q1 + 1;
+    fetch_table<Shape>(s, q2, t, g + 2 * stride, groups);
+    copy_commit();
+    const uint32_t* row0 = group_table(s, q, t.row_words);
+    const int count = static_cast<int>(row0[t.row_words + t.chunks]);
+    const uint32_t begin = row0[t.chunks];
+    const int b0 = static_cast<int>(row0[t.chunks + 1]), b1 = static_cast<int>(row0[t.chunks + 2]);
+    const int64_t first_cell = static_cast<int64_t>(b0) << t.shift;
+    const int cells_here = static_cast<int>(
+        min(static_cast<long long>(b1 - b0) << t.shift, static_cast<long long>(num_cells - first_cell)));
+    const int drop = drop_for<Shape>(cells_here);
+    const int hist_words = max(8, cells_here * (32 >> drop));
+    for (int i = tid; i < hist_words; i += kThreads) s.hist[i] = 0;
+    if (count > 0) {
+      if (!bulk_load_wait(&s.barrier, parity)) s.gave_up = 1;
+      parity ^= 1;
     }
-    __syncthreads();  // everyone has read the ticket before thread 0 writes the next one
+    __syncthreads();
+    if (s.gave_up) {  // the copy never landed: report and stop without touching the output
+      if (tid == 0) atomicCAS(&hdr->error, 0, kErrBulkCopyTimeout);
+      copy_wait_all();
+      return;
+    }
+    if (!sort_staged<Shape>(s, out, count, begin, first_cell, cells_here, drop)) {
+      if (tid == 0) hdr->use_standard = 1;
+    }
+    // s.raw is free (sort_staged ended with a barrier): the next group's records, which L2
+    // holds by now, can come in, and the group after it is asked into L2.
+    copy_wait_all();
+    __syncthreads();  // the table of group g + 2 * stride is visible
+    if (warp == 0) {
+      if (g + stride < groups) touch_runs<Shape, true>(s, q1, t);
+      if (g + 2 * stride < groups) touch_runs<Shape, false>(s, q2, t);
+    }
   }
 }
 
@@ -906,14 +1172,14 @@ bucket_finish_kernel(RunTable t, int64_t n, int64_t num_cells, FinishOut out,
 template <class Shape>
 __global__ void __launch_bounds__(Shape::kThreads, 1)
 bucket_finish_large_kernel(RunTable t, int64_t num_cells, FinishOut out,
-                           Header* __restrict__ hdr) {
-  if (hdr->use_standard || hdr->max_bucket <= static_cast<uint32_t>(Shape::kCapacity)) return;
+                           Header* __restrict__ hdr, uint32_t capacity) {
+  if (hdr->use_standard || hdr->max_bucket <= capacity) return;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FinishSmem<Shape>& s = *reinterpret_cast<FinishSmem<Shape>*>(smem_raw);
   for (int b = blockIdx.x; b < t.buckets; b += gridDim.x) {
     const uint32_t begin = t.bucket_start[b], end = t.bucket_start[b + 1];
     const int count = static_cast<int>(end - begin);
-    if (count <= Shape::kCapacity) continue;
+    if (static_cast<uint32_t>(count) <= capacity) continue;
     const int64_t first_cell = static_cast<int64_t>(b) << t.shift;
     const int cells_here = static_cast<int>(
         min(static_cast<long long>(1) << t.shift, static_cast<long long>(num_cells - first_cell)));
@@ -942,14 +1208,14 @@ struct BucketLayout {
   int64_t entries;  // chunks * buckets runs
   int scan_blocks;
   size_t count_off, total_off, start_off, cursor_off, local_off, block_sum_off, run_begin_off,
-      records_off, total;
+      groups_off, tables_off, records_off, total;
 };
 
-BucketLayout bucket_layout(int64_t n, int64_t buckets) {
+// Tables and records for `n` particles (or room for that many) in `chunks` chunks.
+BucketLayout bucket_layout_of(int64_t n, int64_t buckets, int chunk_log, int chunks) {
   BucketLayout l;
-  l.chunk_log = chunk_log_for(buckets, n);
-  l.chunks = static_cast<int>(
-      std::max<int64_t>(1, (n + (int64_t{1} << l.chunk_log) - 1) >> l.chunk_log));
+  l.chunk_log = chunk_log;
+  l.chunks = chunks;
   l.entries = static_cast<int64_t>(l.chunks) * buckets;
   l.scan_blocks = static_cast<int>((l.entries + kFlatScanBlock - 1) / kFlatScanBlock);
   const size_t words = sizeof(uint32_t);
@@ -960,13 +1226,24 @@ BucketLayout bucket_layout(int64_t n, int64_t buckets) {
   l.local_off = align_up(l.cursor_off + l.entries * words, 256);
   l.block_sum_off = align_up(l.local_off + l.entries * words, 256);
   l.run_begin_off = align_up(l.block_sum_off + l.scan_blocks * words, 256);
-  l.records_off = align_up(l.run_begin_off + (l.entries + 1) * words, 256);
+  l.groups_off = align_up(l.run_begin_off + (l.entries + 1) * words, 256);
+  l.tables_off = align_up(l.groups_off + buckets * 2 * words, 256);
+  l.records_off = align_up(l.tables_off + buckets * 2 * table_row_words(l.chunks) * words, 256);
   l.total = align_up(l.records_off + static_cast<size_t>(n) * kRecordWords * words, 256);
   return l;
 }
 
-// Buckets the count kernel can hold in shared memory (16-bit counters, 200 KB).
-constexpr int64_t kMaxTableBuckets = 100 * 1024;
+BucketLayout bucket_layout(int64_t n, int64_t buckets) {
+  const int chunk_log = chunk_log_for(buckets, n);
+  const int chunks = static_cast<int>(
+      std::max<int64_t>(1, (n + (int64_t{1} << chunk_log) - 1) >> chunk_log));
+  return bucket_layout_of(n, buckets, chunk_log, chunks);
+}
+
+// Most buckets the small finish shape is planned for: beyond, the count kernel's table, the
+// scans and the scatter pay more for the many small buckets than the finish kernel gains
+// (measured at 64 M particles: 65,536 buckets of 1,024 against 16,384 of 4,096).
+constexpr int64_t kMaxSmallShapeBuckets = 32 * 1024;
 
 // Largest bucket width 2^s, s <= max_shift, whose average load stays at or below `target`,
 // with at least 2048 buckets (fewer make the slot counters of the scatter contend: measured
@@ -987,7 +1264,8 @@ int log2_floor(int v) {
 
 }  // namespace
 
-BucketPlan plan_buckets(int64_t n, int64_t num_cells) {
+namespace {
+BucketPlan plan_buckets_shape(int64_t n, int64_t num_cells, bool allow_small) {
   BucketPlan p;
   // The small finish shape (two blocks per multiprocessor) wants buckets well below its
   // capacity, so that the groups cut from them fill a block whatever the density does
@@ -995,13 +1273,25 @@ BucketPlan plan_buckets(int64_t n, int64_t num_cells) {
   p.small_blocks = true;
   p.shift = shift_for(n, num_cells, 1100, log2_floor(FinishSmall::kMaxCells));
   p.buckets = (num_cells + (int64_t{1} << p.shift) - 1) >> p.shift;
-  p.usable = n > 0 && n <= 1100 * p.buckets && p.buckets <= kMaxTableBuckets;
+  p.usable = allow_small && n > 0 && n <= 1100 * p.buckets && p.buckets <= kMaxSmallShapeBuckets;
   if (p.usable) return p;
   p.small_blocks = false;
-  p.shift = shift_for(n, num_cells, 4224, log2_floor(FinishLarge::kMaxCells));
+  p.shift = shift_for(n, num_cells, 4160, log2_floor(FinishLarge::kMaxCells));
   p.buckets = (num_cells + (int64_t{1} << p.shift) - 1) >> p.shift;
-  p.usable = n > 0 && n <= 4224 * p.buckets && p.buckets <= (int64_t{1} << 24);
+  p.usable = n > 0 && n <= 4160 * p.buckets && p.buckets <= (int64_t{1} << 24);
   return p;
+}
+}  // namespace
+
+BucketPlan plan_buckets(int64_t n, int64_t num_cells) {
+  return plan_buckets_shape(n, num_cells, true);
+}
+
+uint32_t bucket_group_capacity(int64_t n, const BucketPlan& p) {
+  // A block's capacity, or less on small inputs so that every multiprocessor gets several groups.
+  const int capacity = p.small_blocks ? FinishSmall::kCapacity : FinishLarge::kCapacity;
+  return static_cast<uint32_t>(std::min<int64_t>(
+      capacity, std::max<int64_t>(1024, n / (4 * static_cast<int64_t>(sm_count())))));
 }
 
 size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells) {
@@ -1012,20 +1302,26 @@ size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells) {
 namespace {
 
 template <class Shape>
-cudaError_t launch_finish(const RunTable& t, const SortArgs& a, const FinishOut& out, Header* hdr) {
-  const int smem = static_cast<int>(sizeof(FinishSmem<Shape>));
+cudaError_t launch_finish(const RunTable& t, const SortArgs& a, const FinishOut& out, Header* hdr,
+                          uint32_t group_capacity, const uint32_t* n_on_device = nullptr) {
+  const size_t table_bytes = 3 * 2 * static_cast<size_t>(t.row_words) * sizeof(uint32_t);
+  if (Shape::kThreads <= 512 && table_bytes > kSmallShapeTableBytes) return cudaErrorInvalidValue;
+  const int smem = static_cast<int>(sizeof(FinishSmem<Shape>) + table_bytes);
   cudaError_t e = cudaFuncSetAttribute(bucket_finish_kernel<Shape>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(bucket_finish_large_kernel<Shape>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  // Buckets in no group (more records than a group may hold) go to the large shape whatever
+  // the shape of the groups: a single cell may then hold up to its 5120 records.
+  const int smem_large = static_cast<int>(sizeof(FinishSmem<FinishLarge>));
+  e = cudaFuncSetAttribute(bucket_finish_large_kernel<FinishLarge>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem_large);
   if (e != cudaSuccess) return e;
   const int per_sm = Shape::kThreads <= 512 ? 2 : 1;
-  const int blocks_of_buckets = (t.buckets + (1 << t.group_shift) - 1) >> t.group_shift;
-  bucket_finish_kernel<Shape><<<std::min(blocks_of_buckets, sm_count() * per_sm), Shape::kThreads,
-                                smem, a.stream>>>(t, a.n, a.num_cells, out, hdr);
-  bucket_finish_large_kernel<Shape><<<std::min(t.buckets, sm_count()), Shape::kThreads, smem,
-                                      a.stream>>>(t, a.num_cells, out, hdr);
+  bucket_finish_kernel<Shape><<<std::min(t.buckets, sm_count() * per_sm), Shape::kThreads, smem,
+                                a.stream>>>(t, a.n, n_on_device, a.num_cells, out, hdr);
+  bucket_finish_large_kernel<FinishLarge><<<std::min(t.buckets, sm_count()), FinishLarge::kThreads,
+                                            smem_large, a.stream>>>(t, a.num_cells, out, hdr,
+                                                                    group_capacity);
   return cudaGetLastError();
 }
 
@@ -1036,7 +1332,7 @@ cudaError_t launch_finish(const RunTable& t, const SortArgs& a, const FinishOut&
 // at once; the caller then enqueues the digit-pass path predicated on that flag.
 cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   const BucketLayout l = bucket_layout(a.n, p.buckets);
-  if (a.workspace_bytes < l.total) return cudaErrorInvalidValue;
+  if (a.workspace_bytes < l.total || l.chunks > kMaxChunks) return cudaErrorInvalidValue;
   auto* base = static_cast<unsigned char*>(a.workspace);
   auto words_at = [&](size_t off) { return reinterpret_cast<uint32_t*>(base + off); };
   Header* hdr = reinterpret_cast<Header*>(base);
@@ -1047,6 +1343,8 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   uint32_t* local = words_at(l.local_off);
   uint32_t* block_sum = words_at(l.block_sum_off);
   uint32_t* run_begin = words_at(l.run_begin_off);
+  uint2* groups = reinterpret_cast<uint2*>(base + l.groups_off);
+  uint32_t* tables = words_at(l.tables_off);
   uint32_t* records = words_at(l.records_off);
   cudaError_t e = cudaMemsetAsync(base, 0, l.total_off, a.stream);  // header and run counts
   if (e != cudaSuccess) return e;
@@ -1100,16 +1398,25 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   if (e != cudaSuccess) return e;
 
   stage_begin(kStageBucketScan, a.stream);
-  const uint32_t largest = p.small_blocks ? FinishSmall::kLargestBucket : FinishLarge::kLargestBucket;
+  const uint32_t largest = FinishLarge::kLargestBucket;
+  const int max_cells = p.small_blocks ? FinishSmall::kMaxCells : FinishLarge::kMaxCells;
+  const uint32_t group_capacity = bucket_group_capacity(a.n, p);
+  const int group_shift = std::min(log2_floor(kMaxGroupBuckets),
+                                   std::max(0, log2_floor(max_cells) - p.shift));
+  const int blocks_of_buckets = (buckets + (1 << group_shift) - 1) >> group_shift;
   bucket_total_kernel<<<(buckets + 255) / 256, 256, 0, a.stream>>>(count, buckets, l.chunks, total);
-  bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, largest, start,
+  bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, nullptr, largest, start,
                                                        nullptr, hdr);
+  group_cut_kernel<<<(blocks_of_buckets + 255) / 256, 256, 0, a.stream>>>(
+      start, buckets, group_shift, group_capacity, groups, &hdr->aux_counter[1]);
   run_scan_local_kernel<<<l.scan_blocks, kFlatScanBlock, 0, a.stream>>>(count, l.entries, local,
                                                                         block_sum);
   run_scan_blocks_kernel<<<1, kFlatScanBlock, 0, a.stream>>>(block_sum, l.scan_blocks);
   run_table_kernel<<<static_cast<int>((l.entries + 1 + 255) / 256), 256, 0, a.stream>>>(
       local, block_sum, l.entries, static_cast<uint32_t>(a.n), cursor, run_begin);
-  count_launches(5);
+  group_table_kernel<<<std::max(1, std::min((buckets + 7) / 8, sm_count() * 8)), 256, 0, a.stream>>>(
+      groups, &hdr->aux_counter[1], start, run_begin, l.chunks, buckets, tables);
+  count_launches(7);
   stage_end(kStageBucketScan, a.stream);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -1134,13 +1441,165 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   stage_begin(kStageBucketFinish, a.stream);
   const FinishOut out{a.keys_out, a.index_out, a.cell_counts, a.cell_start, a.xs, a.ys, a.zs,
                       a.vs, a.padded_sorted};
-  RunTable t{records, start, run_begin, l.chunks, buckets, p.shift, 0};
-  const int max_cells = p.small_blocks ? FinishSmall::kMaxCells : FinishLarge::kMaxCells;
-  t.group_shift = std::min(log2_floor(kMaxSuperBuckets), std::max(0, log2_floor(max_cells) - p.shift));
-  e = p.small_blocks ? launch_finish<FinishSmall>(t, a, out, hdr)
-                     : launch_finish<FinishLarge>(t, a, out, hdr);
+  const RunTable t{records, start, run_begin, tables, &hdr->aux_counter[1],
+                   table_row_words(l.chunks), l.chunks, buckets, p.shift};
+  e = p.small_blocks ? launch_finish<FinishSmall>(t, a, out, hdr, group_capacity)
+                     : launch_finish<FinishLarge>(t, a, out, hdr, group_capacity);
   stage_end(kStageBucketFinish, a.stream);
   count_launches(2);
+  return e;
+}
+
+// ---- the segmented form: one chunk per slice of the sliced exchange ----
+
+namespace {
+// The small shape's shared memory has room for the tables of a dozen chunks only.
+BucketPlan sliced_plan(int64_t plan_n, int64_t num_cells, int slices) {
+  const bool tables_fit =
+      3 * 2 * static_cast<size_t>(table_row_words(slices)) * sizeof(uint32_t) <= kSmallShapeTableBytes;
+  return plan_buckets_shape(plan_n, num_cells, tables_fit);
+}
+}  // namespace
+
+size_t sliced_sort_workspace_bytes(int64_t capacity, int64_t plan_n, int64_t num_cells, int slices) {
+  const BucketPlan p = sliced_plan(plan_n, num_cells, slices);
+  return bucket_layout_of(capacity, p.buckets, 0, slices).total;
+}
+
+namespace {
+struct SlicedState {
+  BucketPlan plan;
+  BucketLayout layout;
+  unsigned char* base;
+  bool ok;
+};
+SlicedState sliced_state(const SortArgs& a, int64_t plan_n, int slices) {
+  SlicedState st{};
+  st.plan = sliced_plan(plan_n, a.num_cells, slices);
+  st.layout = bucket_layout_of(a.n, st.plan.buckets, 0, slices);
+  st.base = static_cast<unsigned char*>(a.workspace);
+  st.ok = st.plan.usable && slices >= 1 && slices <= kMaxSlices && a.workspace &&
+          a.workspace_bytes >= st.layout.total &&
+          (reinterpret_cast<uintptr_t>(a.workspace) & 255) == 0;
+  return st;
+}
+}  // namespace
+
+cudaError_t sliced_sort_begin(const SortArgs& a, int64_t plan_n, int slices) {
+  const SlicedState st = sliced_state(a, plan_n, slices);
+  if (!st.ok) return cudaErrorInvalidValue;
+  stage_reset();
+  return cudaMemsetAsync(st.base, 0, st.layout.total_off, a.stream);  // header and run counts
+}
+
+cudaError_t sliced_sort_slice(const SortArgs& a, int64_t plan_n, const SliceSegments* segments,
+                              int slices, int slice) {
+  const SlicedState st = sliced_state(a, plan_n, slices);
+  if (!st.ok || !segments || slice < 0 || slice >= slices) return cudaErrorInvalidValue;
+  if (!a.x || !a.y || !a.z || !a.velocity || a.padded < a.n) return cudaErrorInvalidValue;
+  const BucketLayout& l = st.layout;
+  auto words_at = [&](size_t off) { return reinterpret_cast<uint32_t*>(st.base + off); };
+  const int buckets = static_cast<int>(st.plan.buckets);
+  uint32_t* row = words_at(l.count_off) + static_cast<size_t>(slice) * buckets;
+  uint32_t* cursor_row = words_at(l.cursor_off) + static_cast<size_t>(slice) * buckets;
+  uint32_t* run_begin_row = words_at(l.run_begin_off) + static_cast<size_t>(slice) * buckets;
+  uint32_t* records = words_at(l.records_off);
+  const bool vec = aligned16(a.x) && aligned16(a.y) && aligned16(a.z) && aligned16(a.velocity) &&
+                   a.padded % 4 == 0;
+  // Work units of a slice: its share of the planned particles, and one partial unit per source.
+  const int64_t units = plan_n / slices / kSegmentUnit + kMaxWorld + 1;
+  cudaError_t e = cudaSuccess;
+
+  stage_begin(kStageBucketCount, a.stream);
+  {
+    const size_t table_bytes = static_cast<size_t>(buckets) * sizeof(uint32_t);
+    const bool shared = table_bytes <= 200 * 1024;
+    const bool wide = shared && table_bytes > 96 * 1024;
+    const int per_sm = !shared ? 4 : wide ? 1 : table_bytes <= 48 * 1024 ? 4 : 2;
+    const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(units, sm_count() * per_sm)));
+    if (!shared) {
+      bucket_count_segments_kernel<kTableGlobal, kCountThreads><<<grid, kCountThreads, 0, a.stream>>>(
+          a.x, a.y, a.z, a.n, vec, segments, slice, a.grid, st.plan.shift, buckets, row);
+    } else if (wide) {
+      auto kernel = bucket_count_segments_kernel<kTableShared32, kCountThreadsWide>;
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(table_bytes));
+      if (e != cudaSuccess) return e;
+      kernel<<<grid, kCountThreadsWide, table_bytes, a.stream>>>(
+          a.x, a.y, a.z, a.n, vec, segments, slice, a.grid, st.plan.shift, buckets, row);
+    } else {
+      auto kernel = bucket_count_segments_kernel<kTableShared32, kCountThreads>;
+      if (table_bytes > 48 * 1024) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(table_bytes));
+        if (e != cudaSuccess) return e;
+      }
+      kernel<<<grid, kCountThreads, table_bytes, a.stream>>>(
+          a.x, a.y, a.z, a.n, vec, segments, slice, a.grid, st.plan.shift, buckets, row);
+    }
+  }
+  stage_end(kStageBucketCount, a.stream);
+  stage_begin(kStageBucketScan, a.stream);
+  chunk_scan_kernel<<<1, kFlatScanBlock, 0, a.stream>>>(row, buckets, segments, slice, cursor_row,
+                                                        run_begin_row);
+  stage_end(kStageBucketScan, a.stream);
+  stage_begin(kStageBucketScatter, a.stream);
+  {
+    constexpr int kItems = 2;
+    const int grid = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>(units, sm_count() * (8 / kItems))));
+    const uint32_t k0 = static_cast<uint32_t>(a.seed), k1 = static_cast<uint32_t>(a.seed >> 32);
+    bucket_scatter_segments_kernel<kItems><<<grid, kScatterThreads, 0, a.stream>>>(
+        a.x, a.y, a.z, a.velocity, a.padded, a.n, vec, segments, slice, a.grid, k0, k1,
+        st.plan.shift, buckets, cursor_row, records);
+  }
+  stage_end(kStageBucketScatter, a.stream);
+  count_launches(3);
+  return cudaGetLastError();
+}
+
+cudaError_t sliced_sort_finish(const SortArgs& a, int64_t plan_n, const SliceSegments* segments,
+                               int slices) {
+  const SlicedState st = sliced_state(a, plan_n, slices);
+  if (!st.ok || !segments) return cudaErrorInvalidValue;
+  if (!a.keys_out || !a.index_out || !a.cell_counts || !a.cell_start) return cudaErrorInvalidValue;
+  const BucketLayout& l = st.layout;
+  const BucketPlan& p = st.plan;
+  auto words_at = [&](size_t off) { return reinterpret_cast<uint32_t*>(st.base + off); };
+  Header* hdr = reinterpret_cast<Header*>(st.base);
+  const int buckets = static_cast<int>(p.buckets);
+  uint32_t* count = words_at(l.count_off);
+  uint32_t* total = words_at(l.total_off);
+  uint32_t* start = words_at(l.start_off);
+  uint32_t* run_begin = words_at(l.run_begin_off);
+  uint2* groups = reinterpret_cast<uint2*>(st.base + l.groups_off);
+  uint32_t* tables = words_at(l.tables_off);
+  uint32_t* records = words_at(l.records_off);
+  const uint32_t* n_on_device = &segments->n;
+
+  stage_begin(kStageBucketFinish, a.stream);
+  const int max_cells = p.small_blocks ? FinishSmall::kMaxCells : FinishLarge::kMaxCells;
+  const uint32_t group_capacity = bucket_group_capacity(plan_n, p);
+  const int group_shift = std::min(log2_floor(kMaxGroupBuckets),
+                                   std::max(0, log2_floor(max_cells) - p.shift));
+  const int blocks_of_buckets = (buckets + (1 << group_shift) - 1) >> group_shift;
+  bucket_total_kernel<<<(buckets + 255) / 256, 256, 0, a.stream>>>(count, buckets, l.chunks, total);
+  bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, n_on_device,
+                                                       FinishLarge::kLargestBucket, start, nullptr,
+                                                       hdr);
+  group_cut_kernel<<<(blocks_of_buckets + 255) / 256, 256, 0, a.stream>>>(
+      start, buckets, group_shift, group_capacity, groups, &hdr->aux_counter[1]);
+  group_table_kernel<<<std::max(1, std::min((buckets + 7) / 8, sm_count() * 8)), 256, 0, a.stream>>>(
+      groups, &hdr->aux_counter[1], start, run_begin, l.chunks, buckets, tables);
+  count_launches(6);
+  const FinishOut out{a.keys_out, a.index_out, a.cell_counts, a.cell_start, a.xs, a.ys, a.zs,
+                      a.vs, a.padded_sorted};
+  const RunTable t{records, start, run_begin, tables, &hdr->aux_counter[1],
+                   table_row_words(l.chunks), l.chunks, buckets, p.shift};
+  const cudaError_t e = p.small_blocks
+                            ? launch_finish<FinishSmall>(t, a, out, hdr, group_capacity, n_on_device)
+                            : launch_finish<FinishLarge>(t, a, out, hdr, group_capacity, n_on_device);
+  stage_end(kStageBucketFinish, a.stream);
   return e;
 }
 

@@ -97,50 +97,82 @@ def exchange_particles(arrays: Sequence[torch.Tensor], matrix: torch.Tensor, gro
     return received
 
 
+FLAG_WORDS = 1024          # words reserved in front of a receive buffer for the arrival flags
+MAX_SLICES = 32            # kMaxSlices of the library
+SLICE_PARTICLES = 1 << 22  # particles of one slice (one chunk of the local sort's records)
+WAIT_POLLS = 1 << 22       # polls (256 ns apart: about a second) before a slice wait gives up
+
+
 class PeerBuffers:
     """Receive buffers of all ranks, mapped into every rank's address space
-    (`torch.distributed._symmetric_memory`): 6 arrays of `capacity` floats per rank,
-    [x | y | z | vx | vy | vz].  The fused partition + exchange kernel stores into
-    them over NVLink."""
+    (`torch.distributed._symmetric_memory`).  Per rank: FLAG_WORDS words of arrival flags
+    (word [s * slices + k] = last step in which source s stored its slice k), then 6 arrays
+    of `capacity` floats [x | y | z | vx | vy | vz].  The fused partition + exchange kernel
+    stores into them over NVLink."""
 
     def __init__(self, capacity: int, device: torch.device, group=None):
         import torch.distributed._symmetric_memory as symm_mem
         self.capacity = -(-int(capacity) // 4) * 4
-        self.buffer = symm_mem.empty(6 * self.capacity, dtype=torch.float32, device=device)
+        self.buffer = symm_mem.empty(FLAG_WORDS + 6 * self.capacity, dtype=torch.float32,
+                                     device=device)
         self.handle = symm_mem.rendezvous(self.buffer, group if group is not None
                                           else dist.group.WORLD)
-        self.pointers = [int(p) for p in self.handle.buffer_ptrs]
-        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        base = [int(p) for p in self.handle.buffer_ptrs]
+        self.flag_pointers = base
+        self.pointers = [p + 4 * FLAG_WORDS for p in base]
+        self.buffer[:FLAG_WORDS].zero_()
+        self.data = self.buffer[FLAG_WORDS:]
 
     def views(self, n: int):
         """(x, y, z, velocity(3, capacity)) of the first n received particles."""
         c = self.capacity
-        b = self.buffer
+        b = self.data
         return b[0:n], b[c:c + n], b[2 * c:2 * c + n], b[3 * c:6 * c].view(3, c)
 
 
-_peer_buffers = {}
+class _ExchangeState:
+    """What a rank keeps from step to step for one (device, process group)."""
+
+    def __init__(self, device: torch.device):
+        self.buffers: Optional[PeerBuffers] = None
+        self.epoch = 0
+        self.slices = 0            # slices agreed for the next step (0: not yet known)
+        self.plan_n = 0            # particle count the next local sort is planned for
+        self.exchange_stream = torch.cuda.Stream(device=device, priority=-1)
+        self.side_stream = torch.cuda.Stream(device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self.slice_done = torch.zeros(MAX_SLICES, dtype=torch.int32, device=device)
 
 
-def _buffers_for(capacity: int, device: torch.device, group) -> PeerBuffers:
+_states = {}
+
+
+def _state_for(device: torch.device, group) -> _ExchangeState:
     key = (device.index, id(group))
-    have = _peer_buffers.get(key)
-    if have is None or have.capacity < capacity:
-        # Collective: every rank takes this branch together, because the capacity asked for
-        # is computed from the count matrix that all ranks hold.
-        have = PeerBuffers(int(capacity * 1.25) + 1024, device, group)
-        _peer_buffers[key] = have
-    return have
+    state = _states.get(key)
+    if state is None:
+        state = _ExchangeState(device)
+        _states[key] = state
+    return state
+
+
+def slices_for(largest_share: int) -> int:
+    """Slices every rank cuts its input into: about SLICE_PARTICLES particles each."""
+    return max(1, min(MAX_SLICES, -(-int(largest_share) // SLICE_PARTICLES)))
 
 
 def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
                        path: int = PATH_AUTO, mark=lambda name: None,
                        push: Optional[tuple] = None) -> SortedParticles:
-    """distributed_sort with the partition and the exchange fused: one kernel reads the
-    rank's particles once and stores each into its destination GPU's receive buffer over
-    NVLink.  The count all-gather before it and a one-word all-reduce after it are the only
-    collectives.  The kernel reads the gathered counts on the device, so the host waits for
-    them (it needs its own receive count to launch the local sort) while the exchange runs.
+    """distributed_sort with the partition and the exchange fused, and the exchange
+    overlapped with the local sort.  One kernel reads the rank's particles once and stores
+    each into its destination GPU's receive buffer over NVLink, on a stream of its own; it
+    works through the input in slices and tells the destinations when a slice is complete.
+    Meanwhile the local sort counts and scatters, slice by slice, what has arrived; only its
+    finish kernels wait for the last slice.  The count all-gather before the exchange is the
+    only collective of a step.  From the second step on the host waits for nothing until
+    everything is enqueued: buffer capacity, slice count and bucket widths come from the
+    previous step's counts (a step whose counts outgrow the buffers is repeated).
     With `push` = (dt, lo, hi) the count and exchange kernels take every particle as it is
     after the move stage, so the particles arrive moved and the inputs stay untouched."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -148,107 +180,185 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
     n, device = x.numel(), x.device
     lib = _native.load_library()
     g = native_grid(grid)
+    local_grid = native_grid(grid, ix_offset, nx_local)
+    cells = nx_local * grid.cells[1] * grid.cells[2]
     if velocity.stride(1) != 1:
         velocity = velocity.contiguous()
-    key = (device.index, id(group))
+    state = _state_for(device, group)
+    move = None
+    if push is not None:
+        move = (float(push[0]), (ctypes.c_float * 3)(*[float(c) for c in push[1]]),
+                (ctypes.c_float * 3)(*[float(c) for c in push[2]]))
     with torch.cuda.device(device):
         current = torch.cuda.current_stream(device)
         stream = ctypes.c_void_p(current.cuda_stream)
-        counts = torch.zeros(world, dtype=torch.int64, device=device)
+        if state.slices == 0:
+            # First step: agree on the slice count from the largest share.
+            largest = torch.tensor([n], dtype=torch.int64, device=device)
+            dist.all_reduce(largest, op=dist.ReduceOp.MAX, group=group)
+            state.slices = slices_for(int(largest))
         part_bytes = lib.AetherSlabPartitionWorkspaceBytes(n, world)
         part_ws = torch.empty(-(-part_bytes // (1 << 20)) * (1 << 20), dtype=torch.uint8,
                               device=device)
-        if push is None:
-            _native.check(lib.AetherSlabExchangeCount(
-                x.data_ptr(), n, ctypes.byref(g), world, counts.data_ptr(), part_ws.data_ptr(),
-                part_ws.numel(), stream), 'AetherSlabExchangeCount')
-        else:
-            dt = float(push[0])
-            lo = (ctypes.c_float * 3)(*[float(c) for c in push[1]])
-            hi = (ctypes.c_float * 3)(*[float(c) for c in push[2]])
-            _native.check(lib.AetherSlabExchangeCountMoved(
-                x.data_ptr(), velocity.data_ptr(), n, dt, lo, hi, ctypes.byref(g), world,
-                counts.data_ptr(), part_ws.data_ptr(), part_ws.numel(), stream),
-                'AetherSlabExchangeCountMoved')
-        mark('partition')
-        # The all-gather also orders this step after the peers' previous sort.
-        matrix_dev = torch.empty((world, world), dtype=torch.int64, device=device)
-        dist.all_gather_into_tensor(matrix_dev, counts, group=group)
-        gathered = torch.cuda.Event()
-        gathered.record(current)
-        mark('counts')
-        buffers = _peer_buffers.get(key)
+        segments = torch.empty(lib.AetherSlabSegmentsBytes(), dtype=torch.uint8, device=device)
         while True:
-            if buffers is not None:
-                pointers = (ctypes.c_void_p * world)(*buffers.pointers)
-                error = torch.zeros(1, dtype=torch.int32, device=device)
-                if push is None:
-                    _native.check(lib.AetherSlabExchangeScatter(
-                        x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
-                        velocity.stride(0), n, ctypes.byref(g), world, rank, pointers,
-                        buffers.capacity, matrix_dev.data_ptr(), error.data_ptr(),
-                        part_ws.data_ptr(), part_ws.numel(), stream), 'AetherSlabExchangeScatter')
-                else:
-                    _native.check(lib.AetherSlabExchangeScatterMoved(
-                        x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
-                        velocity.stride(0), n, dt, lo, hi, ctypes.byref(g), world, rank, pointers,
-                        buffers.capacity, matrix_dev.data_ptr(), error.data_ptr(),
-                        part_ws.data_ptr(), part_ws.numel(), stream),
-                        'AetherSlabExchangeScatterMoved')
-                # Every rank's stores must have landed before anyone reads its buffer.
-                dist.all_reduce(buffers.flag, group=group)
-            # Fetch the counts on a side stream so that the copy does not queue behind the
-            # exchange kernel.
-            side = _side_stream(device)
-            side.wait_event(gathered)
-            with torch.cuda.stream(side):
+            slices = state.slices
+            counts = torch.zeros(world, dtype=torch.int64, device=device)
+            slice_counts = torch.zeros(slices * world, dtype=torch.int64, device=device)
+            if move is None:
+                _native.check(lib.AetherSlabExchangeCount(
+                    x.data_ptr(), n, ctypes.byref(g), world, counts.data_ptr(), part_ws.data_ptr(),
+                    part_ws.numel(), stream), 'AetherSlabExchangeCount')
+            else:
+                _native.check(lib.AetherSlabExchangeCountMoved(
+                    x.data_ptr(), velocity.data_ptr(), n, move[0], move[1], move[2],
+                    ctypes.byref(g), world, counts.data_ptr(), part_ws.data_ptr(), part_ws.numel(),
+                    stream), 'AetherSlabExchangeCountMoved')
+            _native.check(lib.AetherSlabExchangeSliceCounts(
+                n, world, slices, slice_counts.data_ptr(), part_ws.data_ptr(), part_ws.numel(),
+                stream), 'AetherSlabExchangeSliceCounts')
+            mark('partition')
+            # The all-gather also orders this step after the peers' previous sort: nobody
+            # still reads a receive buffer when the first store of this step arrives.
+            matrix_dev = torch.empty((world, slices, world), dtype=torch.int64, device=device)
+            dist.all_gather_into_tensor(matrix_dev, slice_counts, group=group)
+            totals = torch.empty((world, world), dtype=torch.int64, device=device)
+            _native.check(lib.AetherSlabExchangePrepare(
+                matrix_dev.data_ptr(), world, slices, rank, totals.data_ptr(), segments.data_ptr(),
+                stream), 'AetherSlabExchangePrepare')
+            gathered = torch.cuda.Event()
+            gathered.record(current)
+            mark('counts')
+            # The counts travel to the host on a side stream; the host looks at them only
+            # after everything is enqueued (or at once, when there are no buffers yet).
+            state.side_stream.wait_event(gathered)
+            with torch.cuda.stream(state.side_stream):
                 matrix = matrix_dev.to('cpu', non_blocking=True)
-            side.synchronize()
-            received = matrix.sum(dim=0)
-            if buffers is not None and int(received.max()) <= buffers.capacity:
-                break
-            # First call, or a rank would receive more than the buffers hold: (re)allocate,
-            # collectively, and run the exchange again.  Nobody may still be storing into
-            # the buffers that are about to be dropped.
-            torch.cuda.synchronize(device)
-            dist.barrier(group=group)
-            buffers = _buffers_for(int(received.max()), device, group)
-        mark('exchange')
+            buffers = state.buffers
+            if buffers is None:
+                state.side_stream.synchronize()
+                received = matrix.sum(dim=(0, 1))
+                torch.cuda.synchronize(device)
+                dist.barrier(group=group)
+                buffers = state.buffers = PeerBuffers(int(int(received.max()) * 1.25) + 1024,
+                                                      device, group)
+                state.plan_n = max(1, int(received[rank]))
+                torch.cuda.synchronize(device)
+                dist.barrier(group=group)  # every rank's flags are cleared before any store
+                continue  # the step starts over with buffers in place (same counts)
+            capacity = buffers.capacity
+            state.epoch += 1
+            epoch = state.epoch
+            pointers = (ctypes.c_void_p * world)(*buffers.pointers)
+            flag_pointers = (ctypes.c_void_p * world)(*buffers.flag_pointers)
+            state.exchange_stream.wait_event(gathered)
+            with torch.cuda.stream(state.exchange_stream):
+                _native.check(lib.AetherSlabExchangeScatterSliced(
+                    x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
+                    velocity.stride(0), n, move[0] if move else 0.0, move[1] if move else None,
+                    move[2] if move else None, ctypes.byref(g), world, rank, pointers, capacity,
+                    totals.data_ptr(), state.error.data_ptr(), slices, epoch,
+                    state.slice_done.data_ptr(), flag_pointers, part_ws.data_ptr(),
+                    part_ws.numel(), ctypes.c_void_p(state.exchange_stream.cuda_stream)),
+                    'AetherSlabExchangeScatterSliced')
+                sent = torch.cuda.Event()
+                sent.record(state.exchange_stream)
+            rx, ry, rz, rv = buffers.views(capacity)
+            plan_n = max(1, state.plan_n)
+            flags = buffers.flag_pointers[rank]
+            if lib.AetherSortBucketPlan(plan_n, cells, None, None, None) != 0:
+                # The bucketed sort cannot take this many particles per cell: wait for the
+                # whole exchange and hand the received arrays to the general entry point.
+                for k in range(slices):
+                    _native.check(lib.AetherSlabExchangeWait(
+                        flags, world, slices, k, epoch, WAIT_POLLS, state.error.data_ptr(), stream),
+                        'AetherSlabExchangeWait')
+                current.wait_event(sent)
+                state.side_stream.synchronize()
+                received = matrix.sum(dim=(0, 1))
+                if int(received.max()) > capacity:
+                    torch.cuda.synchronize(device)
+                    state.error.zero_()
+                    dist.barrier(group=group)
+                    state.buffers = None
+                    continue
+                m = int(received[rank])
+                state.plan_n = max(1, m)
+                state.slices = slices_for(int(received.max()))
+                mark('exchange')
+                out = sort_and_gather_particles(rx[:m], ry[:m], rz[:m], rv, grid, seed,
+                                                ix_offset=ix_offset, nx_local=nx_local, path=path,
+                                                padded_out=-(-m // 4) * 4)
+                mark('sort')
+                return out
+            # The local sort, slice by slice as the slices arrive.
+            ws_bytes = lib.AetherSortSlicedWorkspaceBytes(capacity, plan_n, cells, slices)
+            ws = _workspace(device, ws_bytes)
+            _native.check(lib.AetherSortSlicedBegin(
+                capacity, plan_n, ctypes.byref(local_grid), slices, ws.data_ptr(), ws.numel(),
+                stream), 'AetherSortSlicedBegin')
+            for k in range(slices):
+                _native.check(lib.AetherSlabExchangeWait(
+                    flags, world, slices, k, epoch, WAIT_POLLS, state.error.data_ptr(), stream),
+                    'AetherSlabExchangeWait')
+                _native.check(lib.AetherSortSlicedSlice(
+                    rx.data_ptr(), ry.data_ptr(), rz.data_ptr(), rv.data_ptr(), capacity, capacity,
+                    plan_n, ctypes.byref(local_grid), int(seed) & 0xFFFFFFFFFFFFFFFF,
+                    segments.data_ptr(), slices, k, ws.data_ptr(), ws.numel(), stream),
+                    'AetherSortSlicedSlice')
+            mark('exchange')
+            # Results are cut out of allocations of the buffers' capacity: the number of
+            # particles a rank holds changes a little from step to step, and allocations whose
+            # size changes every step defeat torch's caching allocator.
+            keys = torch.empty(capacity, dtype=torch.int32, device=device)
+            index = torch.empty(capacity, dtype=torch.int32, device=device)
+            cell_counts = torch.empty(cells, dtype=torch.int32, device=device)
+            cell_start = torch.empty(cells + 1, dtype=torch.int32, device=device)
+            xs, ys, zs = (torch.empty(capacity, dtype=torch.float32, device=device)
+                          for _ in range(3))
+            vs = torch.empty((3, capacity), dtype=torch.float32, device=device)
+            _native.check(lib.AetherSortSlicedFinish(
+                capacity, plan_n, ctypes.byref(local_grid), segments.data_ptr(), slices,
+                keys.data_ptr(), index.data_ptr(), cell_counts.data_ptr(), cell_start.data_ptr(),
+                xs.data_ptr(), ys.data_ptr(), zs.data_ptr(), vs.data_ptr(), capacity,
+                ws.data_ptr(), ws.numel(), stream), 'AetherSortSlicedFinish')
+            current.wait_event(sent)  # the inputs may be reused once this step's work is done
+            mark('sort')
+            # Only now does the host look at the counts.
+            state.side_stream.synchronize()
+            received = matrix.sum(dim=(0, 1))
+            largest = int(received.max())
+            state.slices = slices_for(largest)
+            if largest > capacity:
+                # A rank would have received more than the buffers hold: nothing was stored
+                # for it.  Grow the buffers (collectively) and repeat the step.
+                torch.cuda.synchronize(device)
+                state.error.zero_()
+                dist.barrier(group=group)
+                state.buffers = None
+                state.slices = slices
+                continue
+            break
         m = int(received[rank])
-        rx, ry, rz, rv = buffers.views(m)
-        # The results are cut out of allocations of the buffers' capacity: the number of
-        # particles a rank holds changes a little from step to step, and allocations whose
-        # size changes every step defeat torch's caching allocator (a stall of tens of
-        # milliseconds whenever it has to return its cache to the driver).
-        cap, padded_out = buffers.capacity, -(-m // 4) * 4
-        cells = nx_local * grid.cells[1] * grid.cells[2]
-
-        def cut(dtype):
-            return torch.empty(cap, dtype=dtype, device=device)[:m]
-
-        order = SortResult(cut(torch.int32), cut(torch.int32),
-                           torch.empty(cells, dtype=torch.int32, device=device),
-                           torch.empty(cells + 1, dtype=torch.int32, device=device))
-        vs = torch.empty(3 * cap, dtype=torch.float32, device=device)[:3 * padded_out].view(
-            3, padded_out)
-        results = SortedParticles(order, (cut(torch.float32), cut(torch.float32),
-                                          cut(torch.float32)), vs)
-        out = sort_and_gather_particles(rx, ry, rz, rv, grid, seed, ix_offset=ix_offset,
-                                        nx_local=nx_local, path=path, padded_out=padded_out,
-                                        out=results)
-        mark('sort')
+        state.plan_n = max(1, m)
+        padded_out = -(-m // 4) * 4
+        velocity_out = vs[:, :padded_out]
+        if padded_out > m:
+            velocity_out[:, m:].zero_()
+        out = SortedParticles(SortResult(keys[:m], index[:m], cell_counts, cell_start),
+                              (xs[:m], ys[:m], zs[:m]), velocity_out)
     return out
 
 
-_side_streams = {}
-
-
-def _side_stream(device: torch.device) -> torch.cuda.Stream:
-    s = _side_streams.get(device.index)
-    if s is None:
-        s = torch.cuda.Stream(device=device)
-        _side_streams[device.index] = s
-    return s
+def exchange_status(device: torch.device, group=None) -> int:
+    """Synchronises and returns the device status of the last sliced exchange on `device`:
+    0 when clean, 5 when a receive buffer was too small, 6 when a slice wait ran out (the
+    results of that step are then invalid)."""
+    state = _states.get((device.index, id(group)))
+    if state is None:
+        return 0
+    torch.cuda.synchronize(device)
+    return int(state.error.item())
 
 
 def distributed_sort(x: torch.Tensor, y: torch.Tensor, z: torch.Tensor, velocity: torch.Tensor,

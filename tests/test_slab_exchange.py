@@ -200,3 +200,132 @@ def test_distributed_sort_over_nccl(tmp_path):
         pytest.skip('needs at least two GPUs')
     mp.spawn(_nccl_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == [f'ok{r}' for r in range(world)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('world,slices,n', [(2, 1, 30_000), (4, 3, 50_000), (8, 8, 200_000),
+                                            (3, 32, 70_001)])
+def test_sliced_exchange_and_sliced_sort_emulated_on_one_gpu(cuda, world, slices, n):
+    """The sliced pipeline through the C ABI with all ranks on one GPU, one after another:
+    counts per (slice, destination), the gathered matrix, every rank's exchange kernel storing
+    into the ranks' receive buffers and setting their arrival flags, then per rank the slice
+    waits (the flags are set by then, so no wait polls twice) and the sort slice by slice.
+    Every rank's result equals the oracle's replay of exchange + slab-local sort."""
+    import ctypes
+    from project_aether_b200 import _native
+    from project_aether_b200.particle_sort import native_grid
+    lib = _native.load_library()
+    nx = 24 if world == 3 else 32
+    grid = pa.CellGrid((0., 0., 0.), (1., 1., 1.), (nx, 16, 8))
+    ogrid = so.Grid(grid.lo, grid.hi, grid.cells)
+    g = native_grid(grid)
+    seed, dt = 0x1234500000077, 0.05
+    move = (dt, (ctypes.c_float * 3)(*grid.lo), (ctypes.c_float * 3)(*grid.hi))
+    shares = [_device_share(grid, n + 5 * r, 300 + r, cuda) for r in range(world)]
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
+    with torch.cuda.device(cuda):
+        # Counts of every rank, then the "all-gather".
+        spaces, rows = [], []
+        for x, y, z, v in shares:
+            m = x.numel()
+            ws = torch.empty(lib.AetherSlabPartitionWorkspaceBytes(m, world), dtype=torch.uint8,
+                             device=cuda)
+            totals = torch.zeros(world, dtype=torch.int64, device=cuda)
+            per_slice = torch.zeros(slices * world, dtype=torch.int64, device=cuda)
+            _native.check(lib.AetherSlabExchangeCountMoved(
+                x.data_ptr(), v.data_ptr(), m, move[0], move[1], move[2], ctypes.byref(g), world,
+                totals.data_ptr(), ws.data_ptr(), ws.numel(), stream), 'count')
+            _native.check(lib.AetherSlabExchangeSliceCounts(
+                m, world, slices, per_slice.data_ptr(), ws.data_ptr(), ws.numel(), stream), 'slices')
+            assert torch.equal(per_slice.view(slices, world).sum(0), totals)
+            spaces.append(ws)
+            rows.append(per_slice)
+        matrix = torch.stack(rows).view(world, slices, world).contiguous()
+        received = matrix.sum(dim=(0, 1)).cpu()
+        capacity = -(-int(received.max()) // 4) * 4 + 8
+        flag_words = -(-world * slices // 4) * 4  # keeps the arrays behind the flags 16-byte aligned
+        buffers = [torch.zeros(flag_words + 6 * capacity, dtype=torch.float32, device=cuda)
+                   for _ in range(world)]
+        flag_pointers = (ctypes.c_void_p * world)(*[b.data_ptr() for b in buffers])
+        data_pointers = (ctypes.c_void_p * world)(*[b.data_ptr() + 4 * flag_words for b in buffers])
+        error = torch.zeros(1, dtype=torch.int32, device=cuda)
+        done = torch.zeros(32, dtype=torch.int32, device=cuda)
+        segments, epoch = [], 3
+        for r, (x, y, z, v) in enumerate(shares):
+            totals2d = torch.empty((world, world), dtype=torch.int64, device=cuda)
+            seg = torch.empty(lib.AetherSlabSegmentsBytes(), dtype=torch.uint8, device=cuda)
+            _native.check(lib.AetherSlabExchangePrepare(
+                matrix.data_ptr(), world, slices, r, totals2d.data_ptr(), seg.data_ptr(), stream),
+                'prepare')
+            assert torch.equal(totals2d, matrix.sum(dim=1))
+            segments.append(seg)
+            _native.check(lib.AetherSlabExchangeScatterSliced(
+                x.data_ptr(), y.data_ptr(), z.data_ptr(), v.data_ptr(), v.stride(0), x.numel(),
+                move[0], move[1], move[2], ctypes.byref(g), world, r, data_pointers, capacity,
+                totals2d.data_ptr(), error.data_ptr(), slices, epoch, done.data_ptr(),
+                flag_pointers, spaces[r].data_ptr(), spaces[r].numel(), stream), 'exchange')
+        torch.cuda.synchronize()
+        assert int(error) == 0
+        for b in buffers:  # every (source, slice) flag carries the epoch
+            assert torch.equal(b[:world * slices].view(torch.int32),
+                               torch.full((world * slices,), epoch, dtype=torch.int32, device=cuda))
+        # The oracle's replay: move every share, exchange, sort every slab.
+        host = []
+        for x, y, z, v in shares:
+            m = x.numel()
+            p, q = so.push_particles([t.cpu().numpy() for t in (x, y, z)],
+                                     [v[k, :m].cpu().numpy() for k in range(3)], dt, grid.lo, grid.hi)
+            host.append(tuple(p) + tuple(q))
+        replay = so.exchange_replay(host, ogrid, world)
+        for r in range(world):
+            m = int(received[r])
+            off, width = slab_sort.slab_range(grid, world, r)
+            local = native_grid(grid, off, width)
+            cells = width * grid.cells[1] * grid.cells[2]
+            plan_n = max(1, m + (r % 2) * 1000)  # the plan may come from another step's count
+            data = buffers[r][flag_words:]
+            rx, ry, rz = data[0:capacity], data[capacity:2 * capacity], data[2 * capacity:3 * capacity]
+            rv = data[3 * capacity:6 * capacity]
+            ws = torch.empty(lib.AetherSortSlicedWorkspaceBytes(capacity, plan_n, cells, slices),
+                             dtype=torch.uint8, device=cuda)
+            _native.check(lib.AetherSortSlicedBegin(capacity, plan_n, ctypes.byref(local), slices,
+                                                    ws.data_ptr(), ws.numel(), stream), 'begin')
+            for k in range(slices):
+                _native.check(lib.AetherSlabExchangeWait(buffers[r].data_ptr(), world, slices, k, epoch,
+                                                         4, error.data_ptr(), stream), 'wait')
+                _native.check(lib.AetherSortSlicedSlice(
+                    rx.data_ptr(), ry.data_ptr(), rz.data_ptr(), rv.data_ptr(), capacity, capacity,
+                    plan_n, ctypes.byref(local), seed, segments[r].data_ptr(), slices, k,
+                    ws.data_ptr(), ws.numel(), stream), 'slice')
+            keys = torch.empty(capacity, dtype=torch.int32, device=cuda)
+            index = torch.empty(capacity, dtype=torch.int32, device=cuda)
+            counts = torch.empty(cells, dtype=torch.int32, device=cuda)
+            start = torch.empty(cells + 1, dtype=torch.int32, device=cuda)
+            outs = [torch.empty(capacity, dtype=torch.float32, device=cuda) for _ in range(3)]
+            vs = torch.empty((3, capacity), dtype=torch.float32, device=cuda)
+            _native.check(lib.AetherSortSlicedFinish(
+                capacity, plan_n, ctypes.byref(local), segments[r].data_ptr(), slices,
+                keys.data_ptr(), index.data_ptr(), counts.data_ptr(), start.data_ptr(),
+                outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), vs.data_ptr(), capacity,
+                ws.data_ptr(), ws.numel(), stream), 'finish')
+            status = ctypes.c_int32(-1)
+            _native.check(lib.AetherSortReadStatus(ws.data_ptr(), stream, ctypes.byref(status)),
+                          'status')
+            assert status.value == 0 and int(error) == 0
+            mine = replay[r]
+            assert mine[0].size == m
+            want = so.sort_particles(*mine[:3], ogrid, seed, ix_offset=off, nx_local=width)
+            np.testing.assert_array_equal(keys[:m].cpu().numpy().view(np.uint32), want.keys)
+            np.testing.assert_array_equal(index[:m].cpu().numpy(), want.particle_index)
+            np.testing.assert_array_equal(counts.cpu().numpy(), want.cell_counts)
+            np.testing.assert_array_equal(start.cpu().numpy(), want.cell_start)
+            for k in range(3):
+                np.testing.assert_array_equal(outs[k][:m].cpu().numpy(),
+                                              mine[k][want.particle_index])
+                np.testing.assert_array_equal(vs[k, :m].cpu().numpy(),
+                                              mine[3 + k][want.particle_index])
+        # A flag that nothing sets: the wait runs out after its few polls and reports.
+        _native.check(lib.AetherSlabExchangeWait(buffers[0].data_ptr(), world, slices, 0, epoch + 1,
+                                                 4, error.data_ptr(), stream), 'wait')
+        torch.cuda.synchronize()
+        assert int(error) == 6

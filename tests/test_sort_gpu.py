@@ -166,14 +166,17 @@ def test_dense_layer_overfills_buckets_without_leaving_the_bucketed_path(cuda, n
     y[layer] = 0.5 + dense * (y[layer] - 0.5)
     got = _check_all(x, y, z, vel, grid, 77, pa.PATH_AUTO, big=True)
     assert not pa.last_sort_used_digit_passes(cuda)
-    # The layer really overfills buckets: with the library's bucket width (the largest
-    # 2^s <= 1024 cells with an average of at most 4224 particles and at least 2048 buckets)
-    # some bucket holds more than the 5376 records of the finish kernel's shared memory.
+    # The layer really overfills buckets: with the library's own bucket width some bucket holds
+    # more records than a block of the finish kernel sorts at a time.
+    import ctypes
+    from project_aether_b200 import _native
+    shift, buckets, capacity = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int32()
+    assert _native.load_library().AetherSortBucketPlan(
+        n, grid.num_cells, ctypes.byref(shift), ctypes.byref(buckets), ctypes.byref(capacity)) == 0
     counts = got.order.cell_counts.cpu().numpy().astype(np.int64)
-    shift = next(s for s in range(10, -1, -1)
-                 if s == 0 or (n <= 4224 * -(-counts.size >> s) and -(-counts.size >> s) >= 2048))
-    per_bucket = np.add.reduceat(counts, np.arange(0, counts.size, 1 << shift))
-    assert per_bucket.max() > 5376
+    per_bucket = np.add.reduceat(counts, np.arange(0, counts.size, 1 << shift.value))
+    assert per_bucket.size == buckets.value
+    assert per_bucket.max() > capacity.value
 
 
 def test_uniform_input_does_not_use_the_digit_passes(cuda):
