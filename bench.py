@@ -573,6 +573,9 @@ def run_multi(args):
     x, y, z, v = workloads.make_particles(w, device, seed=rank, n=n_local)
 
     exchange = os.environ.get('AETHER_EXCHANGE', 'peer')  # 'peer' (NVLink stores) or 'nccl'
+    if os.environ.get('AETHER_EXCHANGE_BLOCKS'):  # resident exchange blocks per multiprocessor
+        _native.check(lib.AetherSlabExchangeSetResidentBlocks(
+            int(os.environ['AETHER_EXCHANGE_BLOCKS'])), 'AetherSlabExchangeSetResidentBlocks')
     steady = w.name.startswith('c5')
     state = {'x': x, 'y': y, 'z': z, 'v': v}
 
@@ -604,9 +607,14 @@ def run_multi(args):
     for s in range(warmup):
         out = step(s)
     torch.cuda.synchronize()
-    status = torch.tensor([pa.last_sort_status(device)], device=device)
-    dist.all_reduce(status, op=dist.ReduceOp.MAX)
-    assert int(status) == 0
+
+    def device_status():
+        worst = max(pa.last_sort_status(device), slab_sort.exchange_status(device))
+        status = torch.tensor([worst], device=device)
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+        return int(status)
+
+    assert device_status() == 0
 
     lib.AetherSortSetStageTiming(1)
     launches0 = lib.AetherSortKernelLaunches()
@@ -643,6 +651,7 @@ def run_multi(args):
     received = torch.tensor([out.order.keys.numel()], device=device, dtype=torch.int64)
     dist.all_reduce(received)
     assert int(received) == n_local * world, 'particles were lost in the exchange'
+    assert device_status() == 0, 'a bounded device wait gave up during the timed steps'
 
     # Parity where the numbers are made: one step's results on every rank against the CPU
     # oracle's replay of move + exchange + slab-local sort.  At the full size on up to two

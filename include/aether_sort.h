@@ -206,7 +206,12 @@ int AetherSlabExchangeScatterMoved(const float* x, const float* y, const float* 
  *       `capacity` is the length of the input arrays; the particle count is read from the
  *       segment table on the device; `plan_n` (host) is the particle count the bucket
  *       widths are planned for, e.g. the previous step's.  Workspace from
- *       AetherSortSlicedWorkspaceBytes.  Results as AetherSortAndGatherParticles. */
+ *       AetherSortSlicedWorkspaceBytes.  Results as AetherSortAndGatherParticles.
+ *   AetherSlabExchangeSetResidentBlocks  tuning knob: thread blocks of the sliced exchange
+ *       kernel per multiprocessor (1..4, default 2).  Fewer leave more of the GPU to the
+ *       local sort's kernels that run beside it; more keep more NVLink stores in flight.
+ */
+int AetherSlabExchangeSetResidentBlocks(int blocks_per_multiprocessor);
 int AetherSlabExchangeSliceCounts(int64_t n, int world, int slices, int64_t* slice_counts_out,
                                   void* workspace, size_t workspace_bytes, void* stream);
 size_t AetherSlabSegmentsBytes(void);

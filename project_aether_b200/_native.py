@@ -73,6 +73,7 @@ _SIGNATURES = {
     'AetherSlabExchangeSliceCounts': (ctypes.c_int, [_I64, ctypes.c_int, ctypes.c_int, _P, _P,
                                                      ctypes.c_size_t, _P]),
     'AetherSlabSegmentsBytes': (ctypes.c_size_t, []),
+    'AetherSlabExchangeSetResidentBlocks': (ctypes.c_int, [ctypes.c_int]),
     'AetherSlabExchangePrepare': (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P,
                                                  _P, _P]),
     'AetherSlabExchangeScatterSliced': (ctypes.c_int, [_P, _P, _P, _P, _I64, _I64, ctypes.c_float,

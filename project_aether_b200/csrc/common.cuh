@@ -313,6 +313,7 @@ cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z
 // this rank's segment table and the totals totals2d[s][d] the exchange kernel reads.
 cudaError_t slab_exchange_prepare(const int64_t* matrix, int world, int slices, int rank,
                                   int64_t* totals2d, SliceSegments* segments, cudaStream_t stream);
+void slab_exchange_set_blocks_per_sm(int blocks);
 cudaError_t slab_exchange_slice_counts(int64_t n, int world, int slices, int64_t* slice_counts,
                                        void* workspace, size_t workspace_bytes,
                                        cudaStream_t stream);

@@ -172,7 +172,7 @@ struct SlabTargets {
 __global__ void __launch_bounds__(kSlabThreads, 4)
 slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
-                    int64_t n, AetherGrid g, int slab_width, int world, bool vec,
+                    int64_t n, AetherGrid g, int slab_width, int world, bool vec, int tiles,
                     const uint32_t* __restrict__ tile_offset,
                     const uint32_t* __restrict__ block_sum, SlabTargets tg, PushSpec push) {
   extern __shared__ float stage_raw[];  // [6][kSlabTile]
@@ -182,11 +182,15 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   __shared__ uint32_t out_base[kMaxWorld];        // start of that run in the output arrays
   __shared__ int run_head[kMaxWorld], run_quads[kMaxWorld];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t tile_first = static_cast<int64_t>(blockIdx.x) * kSlabTile;
+  // A block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...: with fewer blocks than tiles
+  // the kernel leaves room on every multiprocessor for the kernels of the local sort that
+  // run beside it, and the tiles, hence the slices, complete roughly in order.
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+  const int64_t tile_first = static_cast<int64_t>(tile) * kSlabTile;
   const int64_t i0 = tile_first + static_cast<int64_t>(tid) * kSlabItems;
   // Where this tile's runs go (global reads: started before anything waits on them).
   if (tid < world) {
-    const size_t entry = static_cast<size_t>(tid) * gridDim.x + blockIdx.x;
+    const size_t entry = static_cast<size_t>(tid) * tiles + tile;
     uint32_t base = tile_offset[entry] + block_sum[entry / kScanBlock];
     if (tg.exchange) {
       // Receive position: what lower ranks send to destination tid, then this rank's block.
@@ -196,12 +200,12 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
         if (s < tg.rank) lower += c;
         all += c;
       }
-      const size_t first = static_cast<size_t>(tid) * gridDim.x;  // this rank's first tile for tid
+      const size_t first = static_cast<size_t>(tid) * tiles;  // this rank's first tile for tid
       base = base - (tile_offset[first] + block_sum[first / kScanBlock]) +
              static_cast<uint32_t>(lower);
       if (all > tg.capacity) {  // never store past a peer's buffer
         base = 0xffffffffu;
-        if (blockIdx.x == 0) atomicCAS(tg.error, 0, kErrReceiveOverflow);
+        if (tile == 0) atomicCAS(tg.error, 0, kErrReceiveOverflow);
       }
     }
     out_base[tid] = base;
@@ -345,17 +349,17 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     __threadfence_system();
     __syncthreads();
     if (tid == 0) {
-      if (blockIdx.x == 0) {
+      if (tile == 0) {
         // Slices without a tile (a short input cut into many slices) are complete as they are.
-        const int with_tiles = (static_cast<int>(gridDim.x) + tg.tiles_per_slice - 1) / tg.tiles_per_slice;
+        const int with_tiles = (tiles + tg.tiles_per_slice - 1) / tg.tiles_per_slice;
         for (int k = with_tiles; k < tg.slices; ++k)
           for (int d = 0; d < world; ++d)
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
                              tg.peer_flags[d] + tg.rank * tg.slices + k), "r"(tg.epoch) : "memory");
       }
-      const int slice = blockIdx.x / tg.tiles_per_slice;
+      const int slice = tile / tg.tiles_per_slice;
       const uint32_t tiles_here = static_cast<uint32_t>(
-          min(tg.tiles_per_slice, static_cast<int>(gridDim.x) - slice * tg.tiles_per_slice));
+          min(tg.tiles_per_slice, tiles - slice * tg.tiles_per_slice));
       if (atomicAdd(&tg.slice_done[slice], 1u) == tiles_here - 1) {
         __threadfence_system();
         for (int d = 0; d < world; ++d)
@@ -363,6 +367,8 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                            tg.peer_flags[d] + tg.rank * tg.slices + slice), "r"(tg.epoch) : "memory");
       }
     }
+  }
+  __syncthreads();  // the staged tile and the run tables are reused by the block's next tile
   }
 }
 
@@ -440,6 +446,10 @@ cudaError_t slab_count(const float* x, const float* vx, const PushSpec& push, in
   return cudaGetLastError();
 }
 
+// Resident blocks of the exchange kernel per multiprocessor in the sliced exchange (1..4).
+int g_exchange_blocks_per_sm = 2;
+int exchange_blocks_per_sm() { return g_exchange_blocks_per_sm; }
+
 cudaError_t slab_scatter(const float* x, const float* y, const float* z, const float* v,
                          int64_t padded, int64_t n, const AetherGrid& g, int world, bool vec,
                          const SlabTargets& tg, const PushSpec& push, void* workspace,
@@ -453,8 +463,12 @@ cudaError_t slab_scatter(const float* x, const float* y, const float* z, const f
   cudaError_t e = cudaFuncSetAttribute(slab_scatter_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
   if (e != cudaSuccess) return e;
-  slab_scatter_kernel<<<tiles, kSlabThreads, kStageBytes, stream>>>(
-      x, y, z, v, padded, n, g, g.nx / world, world, vec, tile_count, block_sum, tg, push);
+  // Blocks per multiprocessor: all four that fit when the kernel runs alone; two in the sliced
+  // exchange, where the local sort's kernels work beside it on what has arrived.
+  const int per_sm = tg.slices > 0 ? exchange_blocks_per_sm() : 4;
+  const int grid = std::min(tiles, sm_count() * per_sm);
+  slab_scatter_kernel<<<grid, kSlabThreads, kStageBytes, stream>>>(
+      x, y, z, v, padded, n, g, g.nx / world, world, vec, tiles, tile_count, block_sum, tg, push);
   count_launches(1);
   return cudaGetLastError();
 }
@@ -538,6 +552,10 @@ int slab_tiles(int64_t n) {
   return static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
 }
 }  // namespace
+
+void slab_exchange_set_blocks_per_sm(int blocks) {
+  g_exchange_blocks_per_sm = std::max(1, std::min(4, blocks));
+}
 
 cudaError_t slab_exchange_prepare(const int64_t* matrix, int world, int slices, int rank,
                                   int64_t* totals2d, SliceSegments* segments, cudaStream_t stream) {

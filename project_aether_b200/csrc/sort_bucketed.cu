@@ -459,7 +459,10 @@ bucket_count_segments_kernel(const float* __restrict__ x, const float* __restric
   uint32_t* target = TABLE != kTableGlobal ? hist : row;
   int64_t first, last, lo;
   for (int unit = blockIdx.x; segment_unit(seg, k, unit, &first, &last, &lo); unit += gridDim.x) {
-    for (int64_t i0 = first + static_cast<int64_t>(threadIdx.x) * 4; i0 < last; i0 += THREADS * 4) {
+    // Every thread of the block makes the same number of rounds: the adds below use
+    // warp-wide votes, which all 32 lanes must reach.
+    for (int64_t round = first; round < last; round += THREADS * 4) {
+      const int64_t i0 = round + static_cast<int64_t>(threadIdx.x) * 4;
       float px[4], py[4], pz[4];
       if (vec && i0 + 4 <= capacity) {
         const float4 a = ldcs4(x + i0), b = ldcs4(y + i0), c = ldcs4(z + i0);
@@ -525,8 +528,10 @@ bucket_scatter_segments_kernel(const float* __restrict__ x, const float* __restr
                                uint32_t* __restrict__ cursor_row, uint32_t* __restrict__ records) {
   int64_t first, last, lo;
   for (int unit = blockIdx.x; segment_unit(seg, k, unit, &first, &last, &lo); unit += gridDim.x) {
-    for (int64_t i0 = first + static_cast<int64_t>(threadIdx.x) * ITEMS; i0 < last;
-         i0 += kScatterThreads * ITEMS) {
+    // Every thread of the block makes the same number of rounds: the slot reservation uses
+    // warp-wide votes, which all 32 lanes must reach.
+    for (int64_t round = first; round < last; round += kScatterThreads * ITEMS) {
+      const int64_t i0 = round + static_cast<int64_t>(threadIdx.x) * ITEMS;
       float f[6][ITEMS];
       if (vec && i0 + ITEMS <= capacity) {
         load_items<ITEMS>(x + i0, f[0]);

@@ -56,6 +56,79 @@ def _gloo_worker(rank, world, port, result_dir):
         dist.destroy_process_group()
 
 
+def _steady_start(world, rank):
+    """A rank's particles at the start of the stepping loop: all inside its own slab."""
+    width = (GRID.hi[0] - GRID.lo[0]) / world
+    share = list(_shares(world, 400, seed=5)[rank])
+    share[0] = (GRID.lo[0] + (rank + share[0] * 0.999) * width).astype(np.float32)
+    share[3:] = [(a - 0.5).astype(np.float32) for a in share[3:]]
+    return tuple(share)
+
+
+def _steady_states(world, steps, dt):
+    """The steady-state loop replayed in one process: a step moves every rank's particles,
+    exchanges those that left the slab and sorts every slab again.  Returns the ranks' states
+    after every step."""
+    ogrid = so.Grid(GRID.lo, GRID.hi, GRID.cells)
+    states = [_steady_start(world, r) for r in range(world)]
+    history = []
+    for step in range(steps):
+        moved = []
+        for st in states:
+            p, q = so.push_particles(list(st[:3]), list(st[3:]), dt, GRID.lo, GRID.hi)
+            moved.append(tuple(p) + tuple(q))
+        received = so.exchange_replay(moved, ogrid, world)
+        states = []
+        for r, rec in enumerate(received):
+            off, wid = slab_sort.slab_range(GRID, world, r)
+            order = so.sort_particles(*rec[:3], ogrid, 1234 ^ (step << 20), ix_offset=off,
+                                      nx_local=wid).particle_index
+            states.append(tuple(a[order] for a in rec))
+        history.append(states)
+    return history
+
+
+def _gloo_loop_worker(rank, world, port, result_dir):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        ogrid = so.Grid(GRID.lo, GRID.hi, GRID.cells)
+        steps, dt = 4, 0.08
+        want = _steady_states(world, steps, dt)
+        state = _steady_start(world, rank)
+        crossed = 0
+        for step in range(steps):
+            p, q = so.push_particles(list(state[:3]), list(state[3:]), dt, GRID.lo, GRID.hi)
+            arrays = tuple(p) + tuple(q)
+            dest = so.slab_of(arrays[0], ogrid, world)
+            crossed += int((dest != rank).sum())
+            order = np.argsort(dest, kind='stable')      # host stand-in for the CUDA partition
+            parts = [torch.from_numpy(a[order].copy()) for a in arrays]
+            counts = torch.from_numpy(np.bincount(dest, minlength=world).astype(np.int64))
+            matrix = slab_sort.exchange_counts(counts)
+            got = [t.numpy() for t in slab_sort.exchange_particles(parts, matrix)]
+            off, wid = slab_sort.slab_range(GRID, world, rank)
+            perm = so.sort_particles(*got[:3], ogrid, 1234 ^ (step << 20), ix_offset=off,
+                                     nx_local=wid).particle_index
+            state = tuple(a[perm] for a in got)
+            for g, w in zip(state, want[step][rank]):
+                np.testing.assert_array_equal(g, w)
+        assert crossed > 0  # particles really changed slab during the loop
+        open(os.path.join(result_dir, f'ok{rank}'), 'w').close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_steady_state_loop_on_cpu_ranks(tmp_path):
+    """Host logic of the stepping loop on two gloo ranks: per step move, partition, count
+    exchange, all-to-all, slab-local sort; every rank's state after every step equals the
+    one-process replay (the per-rank particle counts drift from step to step)."""
+    world = 2
+    mp.spawn(_gloo_loop_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == [f'ok{r}' for r in range(world)]
+
+
 @pytest.mark.parametrize('world', [2, 3])
 def test_exchange_on_cpu_ranks_follows_the_ordering_rule(tmp_path, world):
     mp.spawn(_gloo_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
@@ -188,6 +261,30 @@ def _nccl_worker(rank, world, port, result_dir):
                                               mine[3 + k][want.particle_index])
             for t, b in zip((x, y, z, v), before):
                 assert torch.equal(t, b)
+        assert slab_sort.exchange_status(device) == 0
+        # A stepping loop over the sliced exchange: the output of a step is the next input,
+        # the per-rank particle counts drift, buffers and plans come from the step before.
+        state = (x, y, z, v)
+        shares_now = host
+        for step in range(4):
+            moved = []
+            for h in shares_now:
+                p, w = so.push_particles(list(h[:3]), list(h[3:]), dt, grid.lo, grid.hi)
+                moved.append(tuple(p) + tuple(w))
+            received = so.exchange_replay(moved, ogrid, world)
+            shares_now = []
+            for r, rec in enumerate(received):
+                o, wd = slab_sort.slab_range(grid, world, r)
+                perm = so.sort_particles(*rec[:3], ogrid, 500 + step, ix_offset=o,
+                                         nx_local=wd).particle_index
+                shares_now.append(tuple(a[perm] for a in rec))
+            got = slab_sort.distributed_sort(*state, grid, 500 + step, push=(dt, grid.lo, grid.hi))
+            for k in range(3):
+                np.testing.assert_array_equal(got.positions[k].cpu().numpy(), shares_now[rank][k])
+                np.testing.assert_array_equal(
+                    got.velocity.cpu().numpy()[k, :shares_now[rank][0].size], shares_now[rank][3 + k])
+            state = (*got.positions, got.velocity)
+        assert slab_sort.exchange_status(device) == 0
         open(os.path.join(result_dir, f'ok{rank}'), 'w').close()
     finally:
         dist.destroy_process_group()
