@@ -52,8 +52,11 @@ constexpr int kRecordWords = 8;  // 32-byte record
 constexpr int kCountThreads = 512;       // blocks that share an SM (table up to 96 KB)
 constexpr int kCountThreadsWide = 1024;  // one block per SM (table up to 200 KB)
 
-constexpr int kChunkLog = 22;      // particles per chunk of the record layout (2^22; 2^21, 2^23
-                                   // and 2^24 measured slower end to end)
+#ifndef AETHER_TUNE_CHUNK_LOG
+#define AETHER_TUNE_CHUNK_LOG 22
+#endif
+constexpr int kChunkLog = AETHER_TUNE_CHUNK_LOG;  // particles per chunk of the record layout at 64 M
+                                                  // particles; see chunk_log_for
 
 // Where a block keeps its counts while it works through a slice.
 enum CountTable {
@@ -745,9 +748,12 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t b
   }
 }
 
-// Waits (bounded) for the phase `parity` of the copy barrier; false if it gave up.
+// Waits (bounded) for the phase `parity` of the copy barrier; false if it gave up: after
+// kBulkWaitLimit polls, or after about two seconds on the global timer (a single poll may
+// itself wait a while inside the hardware), whichever comes first.
 __device__ __forceinline__ bool bulk_load_wait(unsigned long long* barrier, uint32_t parity) {
   const uint32_t bar = smem_addr(barrier);
+  unsigned long long started = 0;
   for (uint32_t polls = 0; polls < kBulkWaitLimit; ++polls) {
     uint32_t ready;
     asm volatile(
@@ -755,6 +761,12 @@ __device__ __forceinline__ bool bulk_load_wait(unsigned long long* barrier, uint
         " selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ready) : "r"(bar), "r"(parity) : "memory");
     if (ready) return true;
+    if ((polls & 1023u) == 1023u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (started == 0) started = now;
+      else if (now - started > 2000000000ull) return false;
+    }
   }
   return false;
 }
@@ -1197,14 +1209,21 @@ bucket_finish_large_kernel(RunTable t, int64_t num_cells, FinishOut out,
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// The chunk-major record layout pays when the scatter is bound by scattered stores and a
-// bucket's runs stay long enough for the bulk copies.  Smaller inputs take smaller chunks
-// (fewer particles contend for a slot counter, and the chunk's records stay deeper inside
-// L2): measured best 2^20 at 4 M particles, 2^21 at 16 M, 2^22 from 32 M on.
-inline int chunk_log_for(int64_t /*buckets*/, int64_t n) {
+// The chunk-major record layout: while a chunk is scattered its stores stay inside the
+// chunk's region, which L2 serves faster than the whole record array; but every bucket gets
+// one run per chunk, and short runs cost the scatter (partial lines) and the finish kernel
+// (many small copies) more than the window saves.  Measured optimum on random input: runs of
+// about 256 records, i.e. 2^22 particles per chunk with 16 K buckets (64 M particles: 2.50 ms
+// against 2.63 at 2^23), 2^23 with 32 K buckets (128 M: 5.15 against 5.66 at 2^22 and 5.50 at
+// 2^24), 2^24 with 64 K buckets (256 M: 11.8 against 14.7 at 2^22, 12.8 at 2^23, 12.0 at
+// 2^25).  Smaller inputs take smaller chunks (fewer particles contend for a slot counter):
+// best 2^20 at 4 M particles, 2^21 at 16 M.
+inline int chunk_log_for(int64_t buckets, int64_t n) {
   if (n <= (int64_t{1} << 22)) return kChunkLog - 2;
   if (n <= (int64_t{1} << 24)) return kChunkLog - 1;
-  return kChunkLog;
+  int bucket_log = 0;
+  while ((int64_t{1} << bucket_log) < buckets) ++bucket_log;
+  return std::min(kChunkLog + 2, std::max(kChunkLog, bucket_log + 8));
 }
 
 struct BucketLayout {

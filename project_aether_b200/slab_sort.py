@@ -99,7 +99,6 @@ def exchange_particles(arrays: Sequence[torch.Tensor], matrix: torch.Tensor, gro
 
 FLAG_WORDS = 1024          # words reserved in front of a receive buffer for the arrival flags
 MAX_SLICES = 32            # kMaxSlices of the library
-SLICE_PARTICLES = 1 << 22  # particles of one slice (one chunk of the local sort's records)
 WAIT_POLLS = 1 << 22       # polls (256 ns apart: about a second) before a slice wait gives up
 
 
@@ -157,8 +156,12 @@ def _state_for(device: torch.device, group) -> _ExchangeState:
 
 
 def slices_for(largest_share: int) -> int:
-    """Slices every rank cuts its input into: about SLICE_PARTICLES particles each."""
-    return max(1, min(MAX_SLICES, -(-int(largest_share) // SLICE_PARTICLES)))
+    """Slices every rank cuts its input into.  A slice is one chunk of the local sort's record
+    layout, whose measured optimum grows with the particle count: 2^22 particles up to 64 M
+    particles per rank, 2^23 up to 128 M, 2^24 beyond."""
+    share = int(largest_share)
+    slice_particles = 1 << (22 if share <= (1 << 26) else 23 if share <= (1 << 27) else 24)
+    return max(1, min(MAX_SLICES, -(-share // slice_particles)))
 
 
 def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
