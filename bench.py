@@ -641,13 +641,29 @@ def run_multi(args):
     launches = int(lib.AetherSortKernelLaunches() - launches0)
     stages = stage_times(lib, _native)
     lib.AetherSortSetStageTiming(0)
-    # Phase times of one more step (events on the stream).
+    # Phase times of one more step (events on the stream), and of its exchange kernels, which
+    # run on a stream of their own beside the local sort's count and scatter kernels.
     marks = []
+    if exchange == 'peer':
+        slab_sort.time_exchange(device, True)
     slab_sort.distributed_sort(state['x'], state['y'], state['z'], state['v'], w.grid,
                                workloads.step_seed(1234, 999), marks=marks, exchange=exchange,
                                push=move)
     torch.cuda.synchronize()
     phases = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) for i in range(1, len(marks))}
+    exchange_ms = slab_sort.last_exchange_ms(device) if exchange == 'peer' else None
+    slab_sort.time_exchange(device, False)
+    if args.kernels_only:  # a short run for sweeps: no parity, end-to-end or one-GPU leg
+        if rank == 0:
+            print(json.dumps({'metric': 'sorted particles/s', 'value': n_total / (ms * 1e-3),
+                              'n_gpus': world, 'ms_per_step': ms,
+                              'config': workload_config(workload, w, world),
+                              'stage_ms_rank0': stages, 'phase_ms_rank0': phases,
+                              'exchange_ms_rank0': exchange_ms, 'step_ms_rank0': step_ms,
+                              'kernels_only': True}))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     received = torch.tensor([out.order.keys.numel()], device=device, dtype=torch.int64)
     dist.all_reduce(received)
     assert int(received) == n_local * world, 'particles were lost in the exchange'
@@ -764,14 +780,15 @@ def run_multi(args):
                                     if top in NCU_DRAM_BYTES_PER_PARTICLE else None),
                         'bytes_per_launch': nbytes, 'ms_per_launch': stages[top]}
         nvlink = None
-        if exchange == 'peer' and 'slab_exchange' in stages and not steady:
-            # The exchange kernel reads 24 B per particle and stores 24 B, (G-1)/G of them into
-            # the peers' memory: NVLink bounds it.
+        if exchange_ms and not steady:
+            # The exchange kernels read 24 B per particle and store 24 B, (G-1)/G of them into
+            # the peers' memory: NVLink bounds them.  Timed over all slices of one step, while
+            # the local sort's kernels run beside them.
             crossing = 24 * n_rank * (world - 1) / world
-            link = crossing / (stages['slab_exchange'] * 1e-3) / 1e9
-            nvlink = {'kernel': 'slab_exchange', 'bytes_out_per_gpu': crossing, 'achieved': link,
-                      'peak': PEER_COPY_GBS, 'unit': 'GB/s', 'frac': link / PEER_COPY_GBS,
-                      'ms_per_launch': stages['slab_exchange'],
+            link = crossing / (exchange_ms * 1e-3) / 1e9
+            nvlink = {'kernel': 'slab_scatter_kernel (all slices)', 'bytes_out_per_gpu': crossing,
+                      'achieved': link, 'peak': PEER_COPY_GBS, 'unit': 'GB/s',
+                      'frac': link / PEER_COPY_GBS, 'ms': exchange_ms,
                       'peak_kind': 'peer copy measured on this pool'}
         line = {
             'metric': 'sorted particles/s', 'value': n_total / (ms * 1e-3), 'unit': 'particles/s',
@@ -818,8 +835,8 @@ def main():
                     help='scale the workload to 2^LOG2N particles at the same particles per cell '
                          '(the grid\'s z extent follows); for profiler captures and quick runs')
     ap.add_argument('--kernels-only', action='store_true',
-                    help='single GPU: stop after the device-resident timing (no end-to-end leg, '
-                         'no CPU baseline); for profiler captures')
+                    help='stop after the device-resident timing (no end-to-end leg, no CPU '
+                         'baseline, no parity check); for profiler captures and sweeps')
     ap.add_argument('--no-stage-events', action='store_true',
                     help='single GPU: do not record per-stage events inside the timed steps')
     ap.add_argument('--separate-push', action='store_true',

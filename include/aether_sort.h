@@ -177,7 +177,7 @@ int AetherSlabExchangeScatterMoved(const float* x, const float* y, const float* 
 
 /* The sliced form of the exchange and of the local sort behind it, which lets
  * the two overlap (no counterpart in the reference).  Every rank cuts its input
- * into `slices` (1..32) runs of consecutive tiles; the exchange kernel tells the
+ * into `slices` (1..32) runs of consecutive tiles; the exchange tells the
  * destinations when a slice has been stored, and the destination counts and
  * scatters slice k of all sources into the records of its sort while later
  * slices are still on their way; only the finish kernels wait for everything.
@@ -191,10 +191,12 @@ int AetherSlabExchangeScatterMoved(const float* x, const float* y, const float* 
  *       (segments_out, AetherSlabSegmentsBytes() bytes of device memory): where every
  *       source's slice lies in the received arrays.
  *   AetherSlabExchangeScatterSliced AetherSlabExchangeScatter (with the move fused in when
- *       lo/hi are not NULL) that, when the last tile of slice k is stored, writes `epoch`
- *       to word [rank * slices + k] of every peer_flags[d] (host array of device pointers
- *       into the ranks' flag arrays of world * slices words); slice_done is `slices`
- *       words of device scratch.  Epochs must grow from step to step.
+ *       lo/hi are not NULL) for the tiles of slice `slice` only, followed in the stream by a
+ *       one-warp kernel that writes `epoch` to word [rank * slices + slice] of every
+ *       peer_flags[d] (host array of device pointers into the ranks' flag arrays of
+ *       world * slices words).  A kernel is complete only when its stores are performed, so
+ *       the flag cannot overtake the data.  Called once per slice, in order; epochs must
+ *       grow from step to step.
  *   AetherSlabExchangeWait          enqueues a one-warp kernel that polls this rank's flag
  *       array until every source has signalled `slice` of `epoch`.  The wait is bounded:
  *       after poll_limit polls (256 ns apart) it stores 6 in *error_out (device) and
@@ -222,7 +224,7 @@ int AetherSlabExchangeScatterSliced(const float* x, const float* y, const float*
                                     const float* lo, const float* hi, const AetherGrid* grid,
                                     int world, int rank, float* const* peer_buffers,
                                     int64_t capacity, const int64_t* totals, int32_t* error_out,
-                                    int slices, uint32_t epoch, uint32_t* slice_done,
+                                    int slices, int slice, uint32_t epoch,
                                     uint32_t* const* peer_flags, void* workspace,
                                     size_t workspace_bytes, void* stream);
 int AetherSlabExchangeWait(const uint32_t* flags, int world, int slices, int slice,

@@ -82,7 +82,8 @@ _SIGNATURES = {
                                                        ctypes.POINTER(AetherGrid), ctypes.c_int,
                                                        ctypes.c_int,
                                                        ctypes.POINTER(ctypes.c_void_p), _I64, _P,
-                                                       _P, ctypes.c_int, ctypes.c_uint32, _P,
+                                                       _P, ctypes.c_int, ctypes.c_int,
+                                                       ctypes.c_uint32,
                                                        ctypes.POINTER(ctypes.c_void_p), _P,
                                                        ctypes.c_size_t, _P]),
     'AetherSlabExchangeWait': (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int,

@@ -485,10 +485,10 @@ extern "C" int AetherSlabExchangeScatterSliced(
     const float* x, const float* y, const float* z, const float* velocity, int64_t padded,
     int64_t n, float dt, const float* lo, const float* hi, const AetherGrid* grid, int world,
     int rank, float* const* peer_buffers, int64_t capacity, const int64_t* totals,
-    int32_t* error_out, int slices, uint32_t epoch, uint32_t* slice_done,
-    uint32_t* const* peer_flags, void* workspace, size_t workspace_bytes, void* stream) {
+    int32_t* error_out, int slices, int slice, uint32_t epoch, uint32_t* const* peer_flags,
+    void* workspace, size_t workspace_bytes, void* stream) {
   if ((lo == nullptr) != (hi == nullptr)) return cudaErrorInvalidValue;
-  const SliceSignal signal{slices, epoch, slice_done, peer_flags};
+  const SliceSignal signal{slices, slice, epoch, peer_flags};
   return exchange_scatter(x, y, z, velocity, padded, n, grid, world, rank, peer_buffers, capacity,
                           totals, error_out, lo ? push_spec(dt, lo, hi) : PushSpec{}, workspace,
                           workspace_bytes, stream, &signal);

@@ -296,11 +296,11 @@ cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t n
 cudaError_t slab_exchange_count(const float* x, const float* vx, const PushSpec& push, int64_t n,
                                 const AetherGrid& g, int world, int64_t* totals, void* workspace,
                                 size_t workspace_bytes, cudaStream_t stream);
-// Sliced exchange: the scatter signals every destination when a slice of its tiles is stored.
+// Sliced exchange: one call stores the tiles of one slice and then tells every destination.
 struct SliceSignal {
   int slices;
+  int slice;
   uint32_t epoch;
-  uint32_t* slice_done;           // [slices] device counters (scratch)
   uint32_t* const* peer_flags;    // [world] host array: rank d's flag array [world * slices]
 };
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,

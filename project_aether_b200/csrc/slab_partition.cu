@@ -148,6 +148,10 @@ slab_scan_blocks_kernel(const uint32_t* __restrict__ tile_count, uint32_t* __res
 // the receive buffers of the destination GPUs, written over NVLink, and the
 // position is recv_base[d] (what lower ranks send to d) plus the offset inside
 // this rank's block for d.
+struct SliceFlags {
+  uint32_t* peer[kMaxWorld];  // rank d's flag array [world * slices], in rank d's memory
+};
+
 struct SlabTargets {
   float* array[kMaxWorld][6];
   const int64_t* count_matrix;  // exchange form: [world][world] on the device, [s][d] = s sends d
@@ -156,14 +160,6 @@ struct SlabTargets {
   int exchange;
   int aligned;                  // every output array starts on a 16-byte boundary
   int32_t* error;               // exchange form: set to kErrReceiveOverflow if a buffer is too small
-  // Sliced exchange: the tiles are taken in `slices` consecutive runs of tiles_per_slice;
-  // when the last tile of slice k has been stored, flag [rank * slices + k] of every
-  // destination is set to `epoch` (peer_flags[d] points into rank d's memory).
-  int slices;
-  int tiles_per_slice;
-  uint32_t epoch;
-  uint32_t* slice_done;         // [slices] tiles finished, zeroed before the launch
-  uint32_t* peer_flags[kMaxWorld];
 };
 
 // Stages the tile in shared memory grouped by destination (stable inside a
@@ -173,7 +169,7 @@ __global__ void __launch_bounds__(kSlabThreads, 4)
 slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                     int64_t n, AetherGrid g, int slab_width, int world, bool vec, int tiles,
-                    const uint32_t* __restrict__ tile_offset,
+                    int tile_begin, int tile_end, const uint32_t* __restrict__ tile_offset,
                     const uint32_t* __restrict__ block_sum, SlabTargets tg, PushSpec push) {
   extern __shared__ float stage_raw[];  // [6][kSlabTile]
   float (*stage)[kSlabTile] = reinterpret_cast<float (*)[kSlabTile]>(stage_raw);
@@ -182,10 +178,10 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
   __shared__ uint32_t out_base[kMaxWorld];        // start of that run in the output arrays
   __shared__ int run_head[kMaxWorld], run_quads[kMaxWorld];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // A block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...: with fewer blocks than tiles
-  // the kernel leaves room on every multiprocessor for the kernels of the local sort that
-  // run beside it, and the tiles, hence the slices, complete roughly in order.
-  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+  // A block takes tiles tile_begin + blockIdx.x, + gridDim.x, ... of the launch's range of
+  // tiles: with fewer blocks than tiles the kernel leaves room on every multiprocessor for the
+  // kernels of the local sort that run beside it in the sliced exchange.
+  for (int tile = tile_begin + blockIdx.x; tile < tile_end; tile += gridDim.x) {
   const int64_t tile_first = static_cast<int64_t>(tile) * kSlabTile;
   const int64_t i0 = tile_first + static_cast<int64_t>(tid) * kSlabItems;
   // Where this tile's runs go (global reads: started before anything waits on them).
@@ -343,33 +339,21 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
       for (int c = 0; c < 6; ++c) tg.array[d][c][g0 + (j - lb)] = stage[c][swizzle(j)];
     }
   }
-  if (tg.slices > 0) {
-    // Every thread's stores, to whichever GPU, are performed before the tile counts as
-    // finished; the block that finishes a slice's last tile tells every destination.
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-      if (tile == 0) {
-        // Slices without a tile (a short input cut into many slices) are complete as they are.
-        const int with_tiles = (tiles + tg.tiles_per_slice - 1) / tg.tiles_per_slice;
-        for (int k = with_tiles; k < tg.slices; ++k)
-          for (int d = 0; d < world; ++d)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
-                             tg.peer_flags[d] + tg.rank * tg.slices + k), "r"(tg.epoch) : "memory");
-      }
-      const int slice = tile / tg.tiles_per_slice;
-      const uint32_t tiles_here = static_cast<uint32_t>(
-          min(tg.tiles_per_slice, tiles - slice * tg.tiles_per_slice));
-      if (atomicAdd(&tg.slice_done[slice], 1u) == tiles_here - 1) {
-        __threadfence_system();
-        for (int d = 0; d < world; ++d)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
-                           tg.peer_flags[d] + tg.rank * tg.slices + slice), "r"(tg.epoch) : "memory");
-      }
-    }
-  }
   __syncthreads();  // the staged tile and the run tables are reused by the block's next tile
   }
+}
+
+// Tells every destination that this rank's slice `slice` of step `epoch` is stored: word
+// [rank * slices + slice] of rank d's flag array.  Launched behind the exchange kernel of the
+// slice in the same stream: a kernel is complete only when its stores, to whichever GPU, are
+// performed, so the flag can never overtake the data.
+__global__ void __launch_bounds__(32)
+slab_signal_kernel(SliceFlags flags, int world, int rank, int slices, int slice, uint32_t epoch) {
+  const int d = threadIdx.x;
+  if (d >= world) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.peer[d] + rank * slices + slice),
+               "r"(epoch) : "memory");
 }
 
 // Particles per (slice, destination) from the scanned tile offsets: slice k is the tiles
@@ -453,7 +437,7 @@ int exchange_blocks_per_sm() { return g_exchange_blocks_per_sm; }
 cudaError_t slab_scatter(const float* x, const float* y, const float* z, const float* v,
                          int64_t padded, int64_t n, const AetherGrid& g, int world, bool vec,
                          const SlabTargets& tg, const PushSpec& push, void* workspace,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, int slices = 0, int slice = 0) {
   const int tiles = static_cast<int>(std::max<int64_t>(1, (n + kSlabTile - 1) / kSlabTile));
   uint32_t* tile_count = static_cast<uint32_t*>(workspace);
   const int64_t entries = static_cast<int64_t>(tiles) * world;
@@ -463,12 +447,21 @@ cudaError_t slab_scatter(const float* x, const float* y, const float* z, const f
   cudaError_t e = cudaFuncSetAttribute(slab_scatter_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
   if (e != cudaSuccess) return e;
-  // Blocks per multiprocessor: all four that fit when the kernel runs alone; two in the sliced
-  // exchange, where the local sort's kernels work beside it on what has arrived.
-  const int per_sm = tg.slices > 0 ? exchange_blocks_per_sm() : 4;
-  const int grid = std::min(tiles, sm_count() * per_sm);
+  // The whole input, or the tiles of one slice.  Blocks per multiprocessor: all four that fit
+  // when the kernel runs alone; fewer in the sliced exchange, where the local sort's kernels
+  // work beside it on what has arrived.
+  int tile_begin = 0, tile_end = tiles;
+  if (slices > 0) {
+    const int tiles_per_slice = (tiles + slices - 1) / slices;
+    tile_begin = std::min(tiles, slice * tiles_per_slice);
+    tile_end = std::min(tiles, tile_begin + tiles_per_slice);
+  }
+  if (tile_end == tile_begin) return cudaSuccess;  // a slice without tiles
+  const int per_sm = slices > 0 ? exchange_blocks_per_sm() : 4;
+  const int grid = std::min(tile_end - tile_begin, sm_count() * per_sm);
   slab_scatter_kernel<<<grid, kSlabThreads, kStageBytes, stream>>>(
-      x, y, z, v, padded, n, g, g.nx / world, world, vec, tiles, tile_count, block_sum, tg, push);
+      x, y, z, v, padded, n, g, g.nx / world, world, vec, tiles, tile_begin, tile_end, tile_count,
+      block_sum, tg, push);
   count_launches(1);
   return cudaGetLastError();
 }
@@ -605,22 +598,9 @@ cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z
   if (rank < 0 || rank >= world || !count_matrix || !error) return cudaErrorInvalidValue;
   if (workspace_bytes < slab_partition_workspace_bytes(n, world)) return cudaErrorInvalidValue;
   SlabTargets tg{};
-  if (signal) {
-    if (signal->slices < 1 || signal->slices > kMaxSlices || !signal->slice_done ||
-        !signal->peer_flags)
-      return cudaErrorInvalidValue;
-    tg.slices = signal->slices;
-    tg.tiles_per_slice = (slab_tiles(n) + signal->slices - 1) / signal->slices;
-    tg.epoch = signal->epoch;
-    tg.slice_done = signal->slice_done;
-    for (int d = 0; d < world; ++d) {
-      if (!signal->peer_flags[d]) return cudaErrorInvalidValue;
-      tg.peer_flags[d] = signal->peer_flags[d];
-    }
-    const cudaError_t e = cudaMemsetAsync(signal->slice_done, 0,
-                                          signal->slices * sizeof(uint32_t), stream);
-    if (e != cudaSuccess) return e;
-  }
+  if (signal && (signal->slices < 1 || signal->slices > kMaxSlices || signal->slice < 0 ||
+                 signal->slice >= signal->slices || !signal->peer_flags))
+    return cudaErrorInvalidValue;
   tg.exchange = 1;
   tg.count_matrix = count_matrix;
   tg.capacity = capacity;
@@ -633,7 +613,19 @@ cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z
   }
   const bool vec = aligned16(x) && aligned16(y) && aligned16(z) && aligned16(v);
   stage_begin(kStageSlabExchange, stream);
-  cudaError_t e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, push, workspace, stream);
+  cudaError_t e = slab_scatter(x, y, z, v, padded, n, g, world, vec, tg, push, workspace, stream,
+                               signal ? signal->slices : 0, signal ? signal->slice : 0);
+  if (e == cudaSuccess && signal) {
+    SliceFlags flags{};
+    for (int d = 0; d < world; ++d) {
+      if (!signal->peer_flags[d]) return cudaErrorInvalidValue;
+      flags.peer[d] = signal->peer_flags[d];
+    }
+    slab_signal_kernel<<<1, 32, 0, stream>>>(flags, world, rank, signal->slices, signal->slice,
+                                             signal->epoch);
+    count_launches(1);
+    e = cudaGetLastError();
+  }
   stage_end(kStageSlabExchange, stream);
   return e;
 }

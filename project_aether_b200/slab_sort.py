@@ -140,7 +140,8 @@ class _ExchangeState:
         self.exchange_stream = torch.cuda.Stream(device=device, priority=-1)
         self.side_stream = torch.cuda.Stream(device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
-        self.slice_done = torch.zeros(MAX_SLICES, dtype=torch.int32, device=device)
+        self.exchange_events = None  # (begin, end) of the last exchange, when timing is on
+        self.time_exchange = False
 
 
 _states = {}
@@ -256,14 +257,21 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             flag_pointers = (ctypes.c_void_p * world)(*buffers.flag_pointers)
             state.exchange_stream.wait_event(gathered)
             with torch.cuda.stream(state.exchange_stream):
-                _native.check(lib.AetherSlabExchangeScatterSliced(
-                    x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
-                    velocity.stride(0), n, move[0] if move else 0.0, move[1] if move else None,
-                    move[2] if move else None, ctypes.byref(g), world, rank, pointers, capacity,
-                    totals.data_ptr(), state.error.data_ptr(), slices, epoch,
-                    state.slice_done.data_ptr(), flag_pointers, part_ws.data_ptr(),
-                    part_ws.numel(), ctypes.c_void_p(state.exchange_stream.cuda_stream)),
-                    'AetherSlabExchangeScatterSliced')
+                if state.time_exchange:
+                    state.exchange_events = (torch.cuda.Event(enable_timing=True),
+                                             torch.cuda.Event(enable_timing=True))
+                    state.exchange_events[0].record(state.exchange_stream)
+                for k in range(slices):
+                    _native.check(lib.AetherSlabExchangeScatterSliced(
+                        x.data_ptr(), y.data_ptr(), z.data_ptr(), velocity.data_ptr(),
+                        velocity.stride(0), n, move[0] if move else 0.0, move[1] if move else None,
+                        move[2] if move else None, ctypes.byref(g), world, rank, pointers,
+                        capacity, totals.data_ptr(), state.error.data_ptr(), slices, k, epoch,
+                        flag_pointers, part_ws.data_ptr(), part_ws.numel(),
+                        ctypes.c_void_p(state.exchange_stream.cuda_stream)),
+                        'AetherSlabExchangeScatterSliced')
+                if state.time_exchange:
+                    state.exchange_events[1].record(state.exchange_stream)
                 sent = torch.cuda.Event()
                 sent.record(state.exchange_stream)
             rx, ry, rz, rv = buffers.views(capacity)
@@ -351,6 +359,21 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
         out = SortedParticles(SortResult(keys[:m], index[:m], cell_counts, cell_start),
                               (xs[:m], ys[:m], zs[:m]), velocity_out)
     return out
+
+
+def time_exchange(device: torch.device, enabled: bool, group=None) -> None:
+    """Turns CUDA-event timing of the exchange kernels (all slices, on their own stream) on or
+    off for the following steps on `device`."""
+    _state_for(device, group).time_exchange = bool(enabled)
+
+
+def last_exchange_ms(device: torch.device, group=None) -> Optional[float]:
+    """Synchronises and returns the duration of the last timed exchange, or None."""
+    state = _states.get((device.index, id(group)))
+    if state is None or state.exchange_events is None:
+        return None
+    state.exchange_events[1].synchronize()
+    return state.exchange_events[0].elapsed_time(state.exchange_events[1])
 
 
 def exchange_status(device: torch.device, group=None) -> int:

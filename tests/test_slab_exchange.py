@@ -346,7 +346,6 @@ def test_sliced_exchange_and_sliced_sort_emulated_on_one_gpu(cuda, world, slices
         flag_pointers = (ctypes.c_void_p * world)(*[b.data_ptr() for b in buffers])
         data_pointers = (ctypes.c_void_p * world)(*[b.data_ptr() + 4 * flag_words for b in buffers])
         error = torch.zeros(1, dtype=torch.int32, device=cuda)
-        done = torch.zeros(32, dtype=torch.int32, device=cuda)
         segments, epoch = [], 3
         for r, (x, y, z, v) in enumerate(shares):
             totals2d = torch.empty((world, world), dtype=torch.int64, device=cuda)
@@ -356,11 +355,12 @@ def test_sliced_exchange_and_sliced_sort_emulated_on_one_gpu(cuda, world, slices
                 'prepare')
             assert torch.equal(totals2d, matrix.sum(dim=1))
             segments.append(seg)
-            _native.check(lib.AetherSlabExchangeScatterSliced(
-                x.data_ptr(), y.data_ptr(), z.data_ptr(), v.data_ptr(), v.stride(0), x.numel(),
-                move[0], move[1], move[2], ctypes.byref(g), world, r, data_pointers, capacity,
-                totals2d.data_ptr(), error.data_ptr(), slices, epoch, done.data_ptr(),
-                flag_pointers, spaces[r].data_ptr(), spaces[r].numel(), stream), 'exchange')
+            for k in range(slices):
+                _native.check(lib.AetherSlabExchangeScatterSliced(
+                    x.data_ptr(), y.data_ptr(), z.data_ptr(), v.data_ptr(), v.stride(0), x.numel(),
+                    move[0], move[1], move[2], ctypes.byref(g), world, r, data_pointers, capacity,
+                    totals2d.data_ptr(), error.data_ptr(), slices, k, epoch, flag_pointers,
+                    spaces[r].data_ptr(), spaces[r].numel(), stream), 'exchange')
         torch.cuda.synchronize()
         assert int(error) == 0
         for b in buffers:  # every (source, slice) flag carries the epoch
