@@ -574,8 +574,7 @@ def run_multi(args):
 
     exchange = os.environ.get('AETHER_EXCHANGE', 'peer')  # 'peer' (NVLink stores) or 'nccl'
     if os.environ.get('AETHER_EXCHANGE_BLOCKS'):  # resident exchange blocks per multiprocessor
-        _native.check(lib.AetherSlabExchangeSetResidentBlocks(
-            int(os.environ['AETHER_EXCHANGE_BLOCKS'])), 'AetherSlabExchangeSetResidentBlocks')
+        slab_sort._state_for(device, None).resident_blocks = int(os.environ['AETHER_EXCHANGE_BLOCKS'])
     steady = w.name.startswith('c5')
     state = {'x': x, 'y': y, 'z': z, 'v': v}
 

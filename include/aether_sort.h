@@ -210,8 +210,9 @@ int AetherSlabExchangeScatterMoved(const float* x, const float* y, const float* 
  *       widths are planned for, e.g. the previous step's.  Workspace from
  *       AetherSortSlicedWorkspaceBytes.  Results as AetherSortAndGatherParticles.
  *   AetherSlabExchangeSetResidentBlocks  tuning knob: thread blocks of the sliced exchange
- *       kernel per multiprocessor (1..4, default 2).  Fewer leave more of the GPU to the
- *       local sort's kernels that run beside it; more keep more NVLink stores in flight.
+ *       kernel per multiprocessor (1..4, default 2; 0 = one block per tile).  Fewer leave
+ *       more of the GPU to the local sort's kernels that run beside it; more keep more
+ *       NVLink stores in flight.
  */
 int AetherSlabExchangeSetResidentBlocks(int blocks_per_multiprocessor);
 int AetherSlabExchangeSliceCounts(int64_t n, int world, int slices, int64_t* slice_counts_out,

@@ -468,7 +468,7 @@ extern "C" int AetherSlabExchangeSliceCounts(int64_t n, int world, int slices,
 extern "C" size_t AetherSlabSegmentsBytes(void) { return sizeof(SliceSegments); }
 
 extern "C" int AetherSlabExchangeSetResidentBlocks(int blocks_per_multiprocessor) {
-  if (blocks_per_multiprocessor < 1 || blocks_per_multiprocessor > 4) return cudaErrorInvalidValue;
+  if (blocks_per_multiprocessor < 0 || blocks_per_multiprocessor > 4) return cudaErrorInvalidValue;
   slab_exchange_set_blocks_per_sm(blocks_per_multiprocessor);
   return 0;
 }

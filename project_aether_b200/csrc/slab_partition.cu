@@ -317,10 +317,15 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     const int j = lb + run_head[d] + 4 * (q - quad_first[d]);
     const size_t o = static_cast<size_t>(out_base[d]) + (j - lb);
 #pragma unroll
-    for (int c = 0; c < 6; ++c)
-      *reinterpret_cast<float4*>(tg.array[d][c] + o) =
-          make_float4(stage[c][swizzle(j)], stage[c][swizzle(j + 1)], stage[c][swizzle(j + 2)],
-                      stage[c][swizzle(j + 3)]);
+    for (int c = 0; c < 6; ++c) {
+      const float4 quad = make_float4(stage[c][swizzle(j)], stage[c][swizzle(j + 1)],
+                                      stage[c][swizzle(j + 2)], stage[c][swizzle(j + 3)]);
+#ifdef AETHER_TUNE_EXCHANGE_STREAMING_STORES
+      __stcs(reinterpret_cast<float4*>(tg.array[d][c] + o), quad);
+#else
+      *reinterpret_cast<float4*>(tg.array[d][c] + o) = quad;
+#endif
+    }
   }
   // Heads and tails: at most three elements each per destination when aligned;
   // the whole run when the buffers are not 16-byte aligned.
@@ -430,7 +435,8 @@ cudaError_t slab_count(const float* x, const float* vx, const PushSpec& push, in
   return cudaGetLastError();
 }
 
-// Resident blocks of the exchange kernel per multiprocessor in the sliced exchange (1..4).
+// Resident blocks of the exchange kernel per multiprocessor in the sliced exchange (1..4), or
+// 0 for one block per tile.
 int g_exchange_blocks_per_sm = 2;
 int exchange_blocks_per_sm() { return g_exchange_blocks_per_sm; }
 
@@ -458,7 +464,10 @@ cudaError_t slab_scatter(const float* x, const float* y, const float* z, const f
   }
   if (tile_end == tile_begin) return cudaSuccess;  // a slice without tiles
   const int per_sm = slices > 0 ? exchange_blocks_per_sm() : 4;
-  const int grid = std::min(tile_end - tile_begin, sm_count() * per_sm);
+  // per_sm 0: one block per tile (blocks come and go, so that a kernel of higher priority
+  // takes the multiprocessors over as they retire).
+  const int grid = per_sm > 0 ? std::min(tile_end - tile_begin, sm_count() * per_sm)
+                              : tile_end - tile_begin;
   slab_scatter_kernel<<<grid, kSlabThreads, kStageBytes, stream>>>(
       x, y, z, v, padded, n, g, g.nx / world, world, vec, tiles, tile_begin, tile_end, tile_count,
       block_sum, tg, push);
@@ -547,7 +556,7 @@ int slab_tiles(int64_t n) {
 }  // namespace
 
 void slab_exchange_set_blocks_per_sm(int blocks) {
-  g_exchange_blocks_per_sm = std::max(1, std::min(4, blocks));
+  g_exchange_blocks_per_sm = std::max(0, std::min(4, blocks));
 }
 
 cudaError_t slab_exchange_prepare(const int64_t* matrix, int world, int slices, int rank,

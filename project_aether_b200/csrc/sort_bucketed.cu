@@ -496,25 +496,56 @@ bucket_count_segments_kernel(const float* __restrict__ x, const float* __restric
 
 // Exclusive scan of one slice's row of counts, offset by the records of the slices before it:
 // the scatter's cursors and the finish kernel's run_begin row of that chunk.  One block.
+// STAGED: the row fits shared memory (padded against bank conflicts); it is read and written
+// once, coalesced, and every thread scans a contiguous piece of it.  Otherwise 1024 entries
+// at a time.
+constexpr int kStagedScanMax = 48 * 1024;  // buckets whose row (plus padding) fits 200 KB
+
+template <bool STAGED>
 __global__ void __launch_bounds__(kFlatScanBlock)
 chunk_scan_kernel(const uint32_t* __restrict__ row, int buckets,
                   const SliceSegments* __restrict__ seg, int k, uint32_t* __restrict__ cursor_row,
                   uint32_t* __restrict__ run_begin_row) {
+  extern __shared__ uint32_t staged[];
   __shared__ uint32_t warp_sum[32];
   __shared__ uint32_t total, carry;
-  if (threadIdx.x == 0) carry = seg->chunk_base[k];
-  __syncthreads();
-  for (int base = 0; base < buckets; base += kFlatScanBlock) {
-    const int i = base + threadIdx.x;
-    const uint32_t v = i < buckets ? row[i] : 0u;
-    const uint32_t excl = block_exclusive_scan(v, warp_sum, &total);
-    if (i < buckets) {
-      cursor_row[i] = carry + excl;
-      run_begin_row[i] = carry + excl;
+  if (STAGED) {
+    const int per = (buckets + kFlatScanBlock - 1) / kFlatScanBlock;
+    const int pad = 1 + (per & 1);  // pieces an odd number of words apart: no bank conflicts
+    auto at = [per, pad](int i) { return i + i / per * pad; };
+    for (int i = threadIdx.x; i < buckets; i += kFlatScanBlock) staged[at(i)] = row[i];
+    __syncthreads();
+    const int first = min(buckets, static_cast<int>(threadIdx.x) * per);
+    const int last = min(buckets, first + per);
+    uint32_t sum = 0;
+    for (int b = first; b < last; ++b) sum += staged[at(b)];
+    uint32_t run = seg->chunk_base[k] + block_exclusive_scan(sum, warp_sum, &total);
+    for (int b = first; b < last; ++b) {
+      const uint32_t here = staged[at(b)];
+      staged[at(b)] = run;
+      run += here;
     }
     __syncthreads();
-    if (threadIdx.x == 0) carry += total;
+    for (int i = threadIdx.x; i < buckets; i += kFlatScanBlock) {
+      const uint32_t start = staged[at(i)];
+      cursor_row[i] = start;
+      run_begin_row[i] = start;
+    }
+  } else {
+    if (threadIdx.x == 0) carry = seg->chunk_base[k];
     __syncthreads();
+    for (int base = 0; base < buckets; base += kFlatScanBlock) {
+      const int i = base + threadIdx.x;
+      const uint32_t v = i < buckets ? row[i] : 0u;
+      const uint32_t excl = block_exclusive_scan(v, warp_sum, &total);
+      if (i < buckets) {
+        cursor_row[i] = carry + excl;
+        run_begin_row[i] = carry + excl;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) carry += total;
+      __syncthreads();
+    }
   }
   // Behind the last chunk's row: the end of the last run.
   if (k + 1 == static_cast<int>(seg->slices) && threadIdx.x == 0) run_begin_row[buckets] = seg->n;
@@ -1564,8 +1595,20 @@ cudaError_t sliced_sort_slice(const SortArgs& a, int64_t plan_n, const SliceSegm
   }
   stage_end(kStageBucketCount, a.stream);
   stage_begin(kStageBucketScan, a.stream);
-  chunk_scan_kernel<<<1, kFlatScanBlock, 0, a.stream>>>(row, buckets, segments, slice, cursor_row,
-                                                        run_begin_row);
+  if (buckets <= kStagedScanMax) {
+    const int per = (buckets + kFlatScanBlock - 1) / kFlatScanBlock;
+    const size_t bytes = (static_cast<size_t>(buckets) + 2 * (buckets / per + 1)) * sizeof(uint32_t);
+    if (bytes > 48 * 1024) {
+      e = cudaFuncSetAttribute(chunk_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(bytes));
+      if (e != cudaSuccess) return e;
+    }
+    chunk_scan_kernel<true><<<1, kFlatScanBlock, bytes, a.stream>>>(row, buckets, segments, slice,
+                                                                    cursor_row, run_begin_row);
+  } else {
+    chunk_scan_kernel<false><<<1, kFlatScanBlock, 0, a.stream>>>(row, buckets, segments, slice,
+                                                                 cursor_row, run_begin_row);
+  }
   stage_end(kStageBucketScan, a.stream);
   stage_begin(kStageBucketScatter, a.stream);
   {

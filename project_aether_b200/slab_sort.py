@@ -102,6 +102,20 @@ MAX_SLICES = 32            # kMaxSlices of the library
 WAIT_POLLS = 1 << 22       # polls (256 ns apart: about a second) before a slice wait gives up
 
 
+def overlap_default(world: int) -> bool:
+    """Whether the local sort's count and scatter kernels run beside the exchange kernels.
+    Both stream through L2; with two ranks the exchange moves half of every rank's particles
+    through local memory as well and the two slow each other down by more than the overlap
+    gains, so the step runs them one after the other.  From four ranks on the exchange is
+    bound by NVLink, touches little local memory, and hides the local work.
+    AETHER_EXCHANGE_OVERLAP=0/1 overrides."""
+    import os
+    forced = os.environ.get('AETHER_EXCHANGE_OVERLAP')
+    if forced in ('0', '1'):
+        return forced == '1'
+    return world >= 4
+
+
 class PeerBuffers:
     """Receive buffers of all ranks, mapped into every rank's address space
     (`torch.distributed._symmetric_memory`).  Per rank: FLAG_WORDS words of arrival flags
@@ -137,9 +151,13 @@ class _ExchangeState:
         self.epoch = 0
         self.slices = 0            # slices agreed for the next step (0: not yet known)
         self.plan_n = 0            # particle count the next local sort is planned for
-        self.exchange_stream = torch.cuda.Stream(device=device, priority=-1)
+        import os
+        low = os.environ.get('AETHER_EXCHANGE_PRIORITY') == 'low'
+        self.exchange_stream = torch.cuda.Stream(device=device, priority=0 if low else -1)
+        self.sort_stream = torch.cuda.Stream(device=device, priority=-1) if low else None
         self.side_stream = torch.cuda.Stream(device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        self.resident_blocks = None  # exchange blocks per multiprocessor; None: 2 beside the sort, else 4
         self.exchange_events = None  # (begin, end) of the last exchange, when timing is on
         self.time_exchange = False
 
@@ -205,8 +223,10 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
         part_ws = torch.empty(-(-part_bytes // (1 << 20)) * (1 << 20), dtype=torch.uint8,
                               device=device)
         segments = torch.empty(lib.AetherSlabSegmentsBytes(), dtype=torch.uint8, device=device)
+        overlap = overlap_default(world)
         while True:
-            slices = state.slices
+            # Without overlap the exchange is one piece and the local sort is the ordinary one.
+            slices = state.slices if overlap else 1
             counts = torch.zeros(world, dtype=torch.int64, device=device)
             slice_counts = torch.zeros(slices * world, dtype=torch.int64, device=device)
             if move is None:
@@ -255,6 +275,9 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             epoch = state.epoch
             pointers = (ctypes.c_void_p * world)(*buffers.pointers)
             flag_pointers = (ctypes.c_void_p * world)(*buffers.flag_pointers)
+            _native.check(lib.AetherSlabExchangeSetResidentBlocks(
+                state.resident_blocks if state.resident_blocks is not None
+                else (2 if overlap else 4)), 'AetherSlabExchangeSetResidentBlocks')
             state.exchange_stream.wait_event(gathered)
             with torch.cuda.stream(state.exchange_stream):
                 if state.time_exchange:
@@ -277,9 +300,11 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             rx, ry, rz, rv = buffers.views(capacity)
             plan_n = max(1, state.plan_n)
             flags = buffers.flag_pointers[rank]
-            if lib.AetherSortBucketPlan(plan_n, cells, None, None, None) != 0:
-                # The bucketed sort cannot take this many particles per cell: wait for the
-                # whole exchange and hand the received arrays to the general entry point.
+            if not overlap or lib.AetherSortBucketPlan(plan_n, cells, None, None, None) != 0:
+                # No overlap wanted, or the bucketed sort cannot take this many particles per
+                # cell: wait for the whole exchange and hand the received arrays to the general
+                # entry point.  The host needs the particle count for that; the counts reached
+                # it while the exchange was running, so the GPU does not wait for the host.
                 for k in range(slices):
                     _native.check(lib.AetherSlabExchangeWait(
                         flags, world, slices, k, epoch, WAIT_POLLS, state.error.data_ptr(), stream),
@@ -302,37 +327,54 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
                                                 padded_out=-(-m // 4) * 4)
                 mark('sort')
                 return out
-            # The local sort, slice by slice as the slices arrive.
-            ws_bytes = lib.AetherSortSlicedWorkspaceBytes(capacity, plan_n, cells, slices)
-            ws = _workspace(device, ws_bytes)
-            _native.check(lib.AetherSortSlicedBegin(
-                capacity, plan_n, ctypes.byref(local_grid), slices, ws.data_ptr(), ws.numel(),
-                stream), 'AetherSortSlicedBegin')
-            for k in range(slices):
-                _native.check(lib.AetherSlabExchangeWait(
-                    flags, world, slices, k, epoch, WAIT_POLLS, state.error.data_ptr(), stream),
-                    'AetherSlabExchangeWait')
-                _native.check(lib.AetherSortSlicedSlice(
-                    rx.data_ptr(), ry.data_ptr(), rz.data_ptr(), rv.data_ptr(), capacity, capacity,
-                    plan_n, ctypes.byref(local_grid), int(seed) & 0xFFFFFFFFFFFFFFFF,
-                    segments.data_ptr(), slices, k, ws.data_ptr(), ws.numel(), stream),
-                    'AetherSortSlicedSlice')
-            mark('exchange')
-            # Results are cut out of allocations of the buffers' capacity: the number of
-            # particles a rank holds changes a little from step to step, and allocations whose
-            # size changes every step defeat torch's caching allocator.
-            keys = torch.empty(capacity, dtype=torch.int32, device=device)
-            index = torch.empty(capacity, dtype=torch.int32, device=device)
-            cell_counts = torch.empty(cells, dtype=torch.int32, device=device)
-            cell_start = torch.empty(cells + 1, dtype=torch.int32, device=device)
-            xs, ys, zs = (torch.empty(capacity, dtype=torch.float32, device=device)
-                          for _ in range(3))
-            vs = torch.empty((3, capacity), dtype=torch.float32, device=device)
-            _native.check(lib.AetherSortSlicedFinish(
-                capacity, plan_n, ctypes.byref(local_grid), segments.data_ptr(), slices,
-                keys.data_ptr(), index.data_ptr(), cell_counts.data_ptr(), cell_start.data_ptr(),
-                xs.data_ptr(), ys.data_ptr(), zs.data_ptr(), vs.data_ptr(), capacity,
-                ws.data_ptr(), ws.numel(), stream), 'AetherSortSlicedFinish')
+            # The local sort, slice by slice as the slices arrive (or, without overlap, once
+            # this rank's own exchange kernels are through).  It runs on the caller's stream,
+            # or (AETHER_EXCHANGE_PRIORITY=low) on a high-priority stream of its own, so that
+            # its short kernels take the multiprocessors over from the exchange kernel's blocks.
+            sort_on = state.sort_stream if state.sort_stream is not None else current
+            handle = ctypes.c_void_p(sort_on.cuda_stream)
+            if sort_on is not current:
+                sort_on.wait_event(gathered)
+            with torch.cuda.stream(sort_on):
+                ws_bytes = lib.AetherSortSlicedWorkspaceBytes(capacity, plan_n, cells, slices)
+                ws = _workspace(device, ws_bytes)
+                if not overlap:
+                    sort_on.wait_event(sent)
+                _native.check(lib.AetherSortSlicedBegin(
+                    capacity, plan_n, ctypes.byref(local_grid), slices, ws.data_ptr(), ws.numel(),
+                    handle), 'AetherSortSlicedBegin')
+                for k in range(slices):
+                    _native.check(lib.AetherSlabExchangeWait(
+                        flags, world, slices, k, epoch, WAIT_POLLS, state.error.data_ptr(), handle),
+                        'AetherSlabExchangeWait')
+                    _native.check(lib.AetherSortSlicedSlice(
+                        rx.data_ptr(), ry.data_ptr(), rz.data_ptr(), rv.data_ptr(), capacity,
+                        capacity, plan_n, ctypes.byref(local_grid), int(seed) & 0xFFFFFFFFFFFFFFFF,
+                        segments.data_ptr(), slices, k, ws.data_ptr(), ws.numel(), handle),
+                        'AetherSortSlicedSlice')
+                if sort_on is current:
+                    mark('exchange')
+                # Results are cut out of allocations of the buffers' capacity: the number of
+                # particles a rank holds changes a little from step to step, and allocations
+                # whose size changes every step defeat torch's caching allocator.
+                keys = torch.empty(capacity, dtype=torch.int32, device=device)
+                index = torch.empty(capacity, dtype=torch.int32, device=device)
+                cell_counts = torch.empty(cells, dtype=torch.int32, device=device)
+                cell_start = torch.empty(cells + 1, dtype=torch.int32, device=device)
+                xs, ys, zs = (torch.empty(capacity, dtype=torch.float32, device=device)
+                              for _ in range(3))
+                vs = torch.empty((3, capacity), dtype=torch.float32, device=device)
+                _native.check(lib.AetherSortSlicedFinish(
+                    capacity, plan_n, ctypes.byref(local_grid), segments.data_ptr(), slices,
+                    keys.data_ptr(), index.data_ptr(), cell_counts.data_ptr(),
+                    cell_start.data_ptr(), xs.data_ptr(), ys.data_ptr(), zs.data_ptr(),
+                    vs.data_ptr(), capacity, ws.data_ptr(), ws.numel(), handle),
+                    'AetherSortSlicedFinish')
+            if sort_on is not current:
+                current.wait_stream(sort_on)
+                for t in (keys, index, cell_counts, cell_start, xs, ys, zs, vs):
+                    t.record_stream(current)
+                mark('exchange')
             current.wait_event(sent)  # the inputs may be reused once this step's work is done
             mark('sort')
             # Only now does the host look at the counts.

@@ -140,3 +140,37 @@ def test_cpu_binning_pipeline_counts_equal_the_oracle():
     assert bool((keys[1:] >= keys[:-1]).all())
     np.testing.assert_array_equal(np.sort(order.numpy()), np.arange(20_000))
     np.testing.assert_array_equal((keys >> 7).numpy(), want.keys >> 7)
+
+
+def test_bucket_plan_query_is_host_arithmetic(lib):
+    """AetherSortBucketPlan: bucket widths and finish-group capacities of the benchmark
+    configurations (a bucket never spans more cells than a group may; the small finish shape
+    up to 32,768 buckets, the large one beyond)."""
+    def plan(n, cells):
+        shift, buckets, capacity = ctypes.c_int32(-1), ctypes.c_int64(-1), ctypes.c_int32(-1)
+        rc = lib.AetherSortBucketPlan(n, cells, ctypes.byref(shift), ctypes.byref(buckets),
+                                      ctypes.byref(capacity))
+        return rc, shift.value, buckets.value, capacity.value
+
+    rc, shift, buckets, capacity = plan(1 << 26, 256 * 128 * 128)   # 64 M hypersonic
+    assert (rc, shift, buckets, capacity) == (0, 8, 16384, 5120)
+    rc, shift, buckets, capacity = plan(1 << 24, 128 ** 3)           # 16 M
+    assert (rc, shift, buckets, capacity) == (0, 7, 16384, 2560)
+    rc, shift, buckets, capacity = plan(1 << 28, 512 * 256 * 256)    # 256 M
+    assert (rc, shift, buckets, capacity) == (0, 9, 65536, 5120)
+    rc, shift, buckets, capacity = plan(1 << 20, 64 ** 3)            # 1 M: small groups
+    assert rc == 0 and buckets >= 2048 and 1024 <= capacity <= 2560
+    assert n_over_capacity(lib) != 0
+
+
+def n_over_capacity(lib):
+    # 100,000 particles in one cell: no bucket width keeps the average load within a block.
+    return lib.AetherSortBucketPlan(100_000, 1, None, None, None)
+
+
+def test_scaled_workload_keeps_particles_per_cell():
+    w = workloads.scaled_workload('c3_64m_hypersonic', 24)
+    full = workloads.WORKLOADS['c3_64m_hypersonic']
+    assert w.n == 1 << 24 and w.grid.cells[:2] == full.grid.cells[:2]
+    assert w.n * full.grid.num_cells == full.n * w.grid.num_cells
+    assert workloads.scaled_workload('c4_256m_512', 28) == workloads.WORKLOADS['c4_256m_512']
