@@ -285,6 +285,8 @@ def run_single(args):
     lib = _native.load_library()  # raises if the CUDA library is missing
     if not torch.cuda.is_available():
         raise RuntimeError('bench.py needs a CUDA GPU (no CPU fallback exists)')
+    if args.finish_shape == 'large':
+        _native.check(lib.AetherSortSetSmallShapeBucketLimit(0), 'AetherSortSetSmallShapeBucketLimit')
     device = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
     torch.cuda.set_device(device)
     workload, w = select_workload(args)
@@ -338,7 +340,6 @@ def run_single(args):
     assert pa.last_sort_status(device) == 0
 
     # ---- device-resident timing (inputs 1.6 GB+ per call, far larger than L2) ----
-    lib.AetherSortSetStageTiming(0 if args.no_stage_events else 1)
     launches0 = lib.AetherSortKernelLaunches()
     sampler = ClockSampler(device.index)
     sampler.start()
@@ -351,10 +352,19 @@ def run_single(args):
     torch.cuda.synchronize()
     launches = int(lib.AetherSortKernelLaunches() - launches0)
     ms = begin.elapsed_time(end) / args.steps
-    stages = {} if args.no_stage_events else stage_times(lib, _native)
-    lib.AetherSortSetStageTiming(0)
     assert pa.last_sort_status(device) == 0
     value = n / (ms * 1e-3)
+    # Per-stage times from a few more steps with the library's stage events switched on (two
+    # event records per stage and call: kept out of the timed steps above).
+    stages = {}
+    if not args.no_stage_events:
+        lib.AetherSortSetStageTiming(1)
+        for s in range(max(1, min(args.steps, 8))):
+            out = step(300 + s)
+        torch.cuda.synchronize()
+        stages = stage_times(lib, _native)
+        lib.AetherSortSetStageTiming(0)
+        assert pa.last_sort_status(device) == 0
     if args.kernels_only:  # a short run for a profiler: no end-to-end leg, no CPU leg
         clocks = sampler.stop()
         print(json.dumps({'metric': 'sorted particles/s', 'value': value, 'ms_per_step': ms,
@@ -497,6 +507,93 @@ def run_single(args):
         sys.exit(3)
 
 
+def run_exchange_alone(args):
+    """The multi-GPU step's kernels on ONE GPU, for profiler captures and stage timing: a
+    single rank "exchanges" its whole input with itself (every particle goes through the
+    fused partition + exchange kernel into the rank's own receive buffer, slice by slice,
+    flags and waits included) and sorts the received arrays with the sliced local sort.  The
+    result is checked against the ordinary sort of the same input."""
+    import torch
+    import project_aether_b200 as pa
+    from project_aether_b200 import _native, slab_sort, workloads
+    from project_aether_b200.particle_sort import native_grid
+    lib = _native.load_library()
+    device = torch.device('cuda', 0)
+    torch.cuda.set_device(device)
+    workload, w = select_workload(args)
+    n, cells, g = w.n, w.grid.num_cells, native_grid(w.grid)
+    slices = slab_sort.slices_for(n)
+    x, y, z, v = workloads.make_particles(w, device, seed=0)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    part_ws = torch.empty(lib.AetherSlabPartitionWorkspaceBytes(n, 1), dtype=torch.uint8, device=device)
+    totals = torch.zeros(1, dtype=torch.int64, device=device)
+    per_slice = torch.zeros(slices, dtype=torch.int64, device=device)
+    capacity, flag_words = n + 8, slab_sort.FLAG_WORDS
+    buffer = torch.zeros(flag_words + 6 * capacity, dtype=torch.float32, device=device)
+    flags = (ctypes.c_void_p * 1)(buffer.data_ptr())
+    arrays = (ctypes.c_void_p * 1)(buffer.data_ptr() + 4 * flag_words)
+    data = buffer[flag_words:]
+    error = torch.zeros(1, dtype=torch.int32, device=device)
+    segments = torch.empty(lib.AetherSlabSegmentsBytes(), dtype=torch.uint8, device=device)
+    totals2d = torch.empty((1, 1), dtype=torch.int64, device=device)
+    sort_ws = torch.empty(lib.AetherSortSlicedWorkspaceBytes(capacity, n, cells, slices),
+                          dtype=torch.uint8, device=device)
+    keys, index = (torch.empty(capacity, dtype=torch.int32, device=device) for _ in range(2))
+    counts = torch.empty(cells, dtype=torch.int32, device=device)
+    start = torch.empty(cells + 1, dtype=torch.int32, device=device)
+    xs, ys, zs = (torch.empty(capacity, device=device) for _ in range(3))
+    vs = torch.empty((3, capacity), device=device)
+    _native.check(lib.AetherSlabExchangeSetResidentBlocks(4), 'AetherSlabExchangeSetResidentBlocks')
+
+    def step(epoch, seed):
+        ck = _native.check
+        ck(lib.AetherSlabExchangeCount(x.data_ptr(), n, ctypes.byref(g), 1, totals.data_ptr(),
+                                       part_ws.data_ptr(), part_ws.numel(), stream), 'count')
+        ck(lib.AetherSlabExchangeSliceCounts(n, 1, slices, per_slice.data_ptr(), part_ws.data_ptr(),
+                                             part_ws.numel(), stream), 'slice counts')
+        ck(lib.AetherSlabExchangePrepare(per_slice.data_ptr(), 1, slices, 0, totals2d.data_ptr(),
+                                         segments.data_ptr(), stream), 'prepare')
+        for k in range(slices):
+            ck(lib.AetherSlabExchangeScatterSliced(
+                x.data_ptr(), y.data_ptr(), z.data_ptr(), v.data_ptr(), v.stride(0), n, 0.0, None,
+                None, ctypes.byref(g), 1, 0, arrays, capacity, totals2d.data_ptr(), error.data_ptr(),
+                slices, k, epoch, flags, part_ws.data_ptr(), part_ws.numel(), stream), 'exchange')
+        ck(lib.AetherSortSlicedBegin(capacity, n, ctypes.byref(g), slices, sort_ws.data_ptr(),
+                                     sort_ws.numel(), stream), 'begin')
+        for k in range(slices):
+            ck(lib.AetherSlabExchangeWait(buffer.data_ptr(), 1, slices, k, epoch, 4,
+                                          error.data_ptr(), stream), 'wait')
+            ck(lib.AetherSortSlicedSlice(
+                data.data_ptr(), data[capacity:].data_ptr(), data[2 * capacity:].data_ptr(),
+                data[3 * capacity:].data_ptr(), capacity, capacity, n, ctypes.byref(g), seed,
+                segments.data_ptr(), slices, k, sort_ws.data_ptr(), sort_ws.numel(), stream), 'slice')
+        ck(lib.AetherSortSlicedFinish(
+            capacity, n, ctypes.byref(g), segments.data_ptr(), slices, keys.data_ptr(),
+            index.data_ptr(), counts.data_ptr(), start.data_ptr(), xs.data_ptr(), ys.data_ptr(),
+            zs.data_ptr(), vs.data_ptr(), capacity, sort_ws.data_ptr(), sort_ws.numel(), stream),
+            'finish')
+
+    for s in range(max(1, args.warmup)):
+        step(s + 1, workloads.step_seed(1234, s))
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for s in range(args.steps):
+        step(100 + s, workloads.step_seed(1234, 100 + s))
+    end.record()
+    torch.cuda.synchronize()
+    want = pa.sort_and_gather_particles(x, y, z, v, w.grid, workloads.step_seed(1234, 100 + args.steps - 1))
+    same = (torch.equal(want.order.particle_index, index[:n]) and torch.equal(want.order.keys, keys[:n])
+            and torch.equal(want.order.cell_start, start) and torch.equal(want.positions[2], zs[:n])
+            and torch.equal(want.velocity[:, :n], vs[:, :n]))
+    print(json.dumps({'mode': 'exchange and sliced sort of one rank on one GPU', 'slices': slices,
+                      'ms_per_step': begin.elapsed_time(end) / args.steps,
+                      'config': workload_config(workload, w, 1), 'device_status': int(error),
+                      'equal_to_ordinary_sort': bool(same)}))
+    if not same or int(error) != 0:
+        sys.exit(3)
+
+
 # --------------------------------------------------------------------------------------
 # N > 1: one rank per GPU, x-slab decomposition.
 # --------------------------------------------------------------------------------------
@@ -615,7 +712,6 @@ def run_multi(args):
 
     assert device_status() == 0
 
-    lib.AetherSortSetStageTiming(1)
     launches0 = lib.AetherSortKernelLaunches()
     sampler = ClockSampler(device.index)
     if rank == 0:
@@ -638,10 +734,11 @@ def run_multi(args):
     dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     ms = float(elapsed) / args.steps
     launches = int(lib.AetherSortKernelLaunches() - launches0)
-    stages = stage_times(lib, _native)
-    lib.AetherSortSetStageTiming(0)
-    # Phase times of one more step (events on the stream), and of its exchange kernels, which
-    # run on a stream of their own beside the local sort's count and scatter kernels.
+    # Stage and phase times of one more step, kept out of the timed steps: the library's stage
+    # events, phase events on the caller's stream, and the exchange kernels (all slices) on the
+    # stream of their own on which they run beside the local sort's count and scatter kernels.
+    # With the sliced exchange a stage's figure is that of the last slice's launch.
+    lib.AetherSortSetStageTiming(1)
     marks = []
     if exchange == 'peer':
         slab_sort.time_exchange(device, True)
@@ -649,6 +746,8 @@ def run_multi(args):
                                workloads.step_seed(1234, 999), marks=marks, exchange=exchange,
                                push=move)
     torch.cuda.synchronize()
+    stages = stage_times(lib, _native)
+    lib.AetherSortSetStageTiming(0)
     phases = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) for i in range(1, len(marks))}
     exchange_ms = slab_sort.last_exchange_ms(device) if exchange == 'peer' else None
     slab_sort.time_exchange(device, False)
@@ -837,16 +936,24 @@ def main():
                     help='stop after the device-resident timing (no end-to-end leg, no CPU '
                          'baseline, no parity check); for profiler captures and sweeps')
     ap.add_argument('--no-stage-events', action='store_true',
-                    help='single GPU: do not record per-stage events inside the timed steps')
+                    help='single GPU: skip the extra steps that collect per-stage event times')
     ap.add_argument('--separate-push', action='store_true',
                     help='steady-state workload only: run the move stage as its own kernel '
                          'instead of inside the sort kernels')
     ap.add_argument('--collide', action='store_true',
                     help='steady-state workload only: run the collision stage after every sort')
+    ap.add_argument('--exchange-alone', action='store_true',
+                    help='one GPU: run the multi-GPU step\'s kernels (partition + exchange into the '
+                         'rank\'s own buffer, sliced local sort) for one rank; for profiler captures')
     ap.add_argument('--path', default='auto', choices=['auto', 'digits', 'bucketed'])
+    ap.add_argument('--finish-shape', default='auto', choices=['auto', 'large'],
+                    help='single GPU: plan the large shape of the finish kernel whatever the size '
+                         '(to capture the 64 M configuration\'s kernel on a scaled-down case)')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)
+    elif args.exchange_alone:
+        run_exchange_alone(args)
     elif args.gpus == 1:
         run_single(args)
     else:

@@ -66,6 +66,13 @@ size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload);
 int AetherSortBucketPlan(int64_t n, int64_t num_cells, int32_t* cells_per_bucket_log2,
                          int64_t* buckets, int32_t* group_capacity);
 
+/* Tuning knob of the bucketed path (process-wide; no counterpart in the reference): the
+ * finish kernel runs in its small shape (two 512-thread blocks per multiprocessor, 2560
+ * records each) while the plan needs at most `buckets` buckets of about a thousand records,
+ * and in its large shape (one 1024-thread block, 5120 records) beyond.  Default and maximum
+ * 32,768; 0 plans the large shape always.  Results do not depend on it. */
+int AetherSortSetSmallShapeBucketLimit(int64_t buckets);
+
 /* sort_particles_by_cell (fused_radix_sort.py:221-280): sorted keys,
  * permutation (original index of every sorted particle), per-cell counts (C)
  * and exclusive starts (C+1).  Inputs are not modified. */

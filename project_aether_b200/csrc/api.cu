@@ -225,6 +225,12 @@ extern "C" int AetherSortBucketPlan(int64_t n, int64_t num_cells, int32_t* cells
   return plan.usable ? 0 : cudaErrorInvalidValue;
 }
 
+extern "C" int AetherSortSetSmallShapeBucketLimit(int64_t buckets) {
+  if (buckets < 0) return cudaErrorInvalidValue;
+  set_small_shape_buckets(buckets);
+  return 0;
+}
+
 extern "C" int AetherSortParticlesByCell(const float* x, const float* y, const float* z,
                                          int64_t n, const AetherGrid* grid, uint64_t seed,
                                          uint32_t* keys_out, int32_t* index_out,

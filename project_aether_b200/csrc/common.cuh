@@ -258,6 +258,8 @@ struct BucketPlan {
   bool small_blocks;  // finish kernel shape: two small blocks per multiprocessor, or one large
 };
 BucketPlan plan_buckets(int64_t n, int64_t num_cells);
+// Most buckets for which the small finish shape is planned (at most 32,768; 0: never).
+void set_small_shape_buckets(int64_t buckets);
 // Most records of a group of buckets (what one block of the finish kernel sorts at a time).
 uint32_t bucket_group_capacity(int64_t n, const BucketPlan& p);
 size_t bucketed_workspace_bytes(int64_t n, int64_t num_cells);

@@ -1299,6 +1299,7 @@ BucketLayout bucket_layout(int64_t n, int64_t buckets) {
 // scans and the scatter pay more for the many small buckets than the finish kernel gains
 // (measured at 64 M particles: 65,536 buckets of 1,024 against 16,384 of 4,096).
 constexpr int64_t kMaxSmallShapeBuckets = 32 * 1024;
+int64_t g_small_shape_buckets = kMaxSmallShapeBuckets;  // tuning knob, see set_small_shape_buckets
 
 // Largest bucket width 2^s, s <= max_shift, whose average load stays at or below `target`,
 // with at least 2048 buckets (fewer make the slot counters of the scatter contend: measured
@@ -1328,7 +1329,7 @@ BucketPlan plan_buckets_shape(int64_t n, int64_t num_cells, bool allow_small) {
   p.small_blocks = true;
   p.shift = shift_for(n, num_cells, 1100, log2_floor(FinishSmall::kMaxCells));
   p.buckets = (num_cells + (int64_t{1} << p.shift) - 1) >> p.shift;
-  p.usable = allow_small && n > 0 && n <= 1100 * p.buckets && p.buckets <= kMaxSmallShapeBuckets;
+  p.usable = allow_small && n > 0 && n <= 1100 * p.buckets && p.buckets <= g_small_shape_buckets;
   if (p.usable) return p;
   p.small_blocks = false;
   p.shift = shift_for(n, num_cells, 4160, log2_floor(FinishLarge::kMaxCells));
@@ -1340,6 +1341,10 @@ BucketPlan plan_buckets_shape(int64_t n, int64_t num_cells, bool allow_small) {
 
 BucketPlan plan_buckets(int64_t n, int64_t num_cells) {
   return plan_buckets_shape(n, num_cells, true);
+}
+
+void set_small_shape_buckets(int64_t buckets) {
+  g_small_shape_buckets = std::max<int64_t>(0, std::min<int64_t>(buckets, kMaxSmallShapeBuckets));
 }
 
 uint32_t bucket_group_capacity(int64_t n, const BucketPlan& p) {
