@@ -670,8 +670,13 @@ def run_multi(args):
     x, y, z, v = workloads.make_particles(w, device, seed=rank, n=n_local)
 
     exchange = os.environ.get('AETHER_EXCHANGE', 'peer')  # 'peer' (NVLink stores) or 'nccl'
-    if os.environ.get('AETHER_EXCHANGE_BLOCKS'):  # resident exchange blocks per multiprocessor
-        slab_sort._state_for(device, None).resident_blocks = int(os.environ['AETHER_EXCHANGE_BLOCKS'])
+    # Tuning of the sliced exchange from the environment (for sweeps): overlap 0/1, resident
+    # exchange blocks per multiprocessor 0..4, local sort on a stream of its own 0/1.
+    knobs = {key: os.environ.get(name) for key, name in (
+        ('overlap', 'AETHER_EXCHANGE_OVERLAP'), ('resident_blocks', 'AETHER_EXCHANGE_BLOCKS'),
+        ('sort_stream', 'AETHER_EXCHANGE_SORT_STREAM'))}
+    slab_sort.configure(**{key: (None if value is None else int(value))
+                           for key, value in knobs.items()})
     steady = w.name.startswith('c5')
     state = {'x': x, 'y': y, 'z': z, 'v': v}
 

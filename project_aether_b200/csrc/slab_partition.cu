@@ -165,7 +165,11 @@ struct SlabTargets {
 // Stages the tile in shared memory grouped by destination (stable inside a
 // destination), then writes every destination's run with coalesced stores:
 // plain stores, to local memory or straight into a peer GPU's memory.
-__global__ void __launch_bounds__(kSlabThreads, 4)
+// EAGER: all six arrays of the tile are requested before anything waits (one memory latency
+// per tile instead of three, at twice the registers: two blocks per multiprocessor); otherwise
+// one axis at a time passes through the registers and four blocks fit.
+template <bool EAGER>
+__global__ void __launch_bounds__(kSlabThreads, EAGER ? 2 : 4)
 slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                     int64_t n, AetherGrid g, int slab_width, int world, bool vec, int tiles,
@@ -206,13 +210,18 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     }
     out_base[tid] = base;
   }
-  // One axis at a time (a coordinate and its velocity component) passes through the
-  // registers, so that four blocks fit an SM; the x pair comes first because the
-  // destination depends on it.
+  // The x pair comes first because the destination depends on it.
   const bool vec_v = vec && padded % 4 == 0;
   float pc[kSlabItems], pw[kSlabItems];
+  float later[EAGER ? 4 : 1][kSlabItems];  // EAGER: y, vy, z, vz
   load8(x, i0, n, vec, pc);
   load8(v, i0, n, vec_v, pw);
+  if (EAGER) {
+    load8(y, i0, n, vec, later[0]);
+    load8(v + padded, i0, n, vec_v, later[1]);
+    load8(z, i0, n, vec, later[EAGER ? 2 : 0]);
+    load8(v + 2 * padded, i0, n, vec_v, later[EAGER ? 3 : 0]);
+  }
   if (push.enabled) {  // fused move stage: the particle travels as it is after the move
 #pragma unroll
     for (int k = 0; k < kSlabItems; ++k) push_axis(pc[k], pw[k], push.dt, push.lo[0], push.hi[0]);
@@ -272,8 +281,16 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     }
 #pragma unroll
   for (int axis = 1; axis < 3; ++axis) {
-    load8(axis == 1 ? y : z, i0, n, vec, pc);
-    load8(v + axis * padded, i0, n, vec_v, pw);
+    if (EAGER) {
+#pragma unroll
+      for (int k = 0; k < kSlabItems; ++k) {
+        pc[k] = later[EAGER ? 2 * axis - 2 : 0][k];
+        pw[k] = later[EAGER ? 2 * axis - 1 : 0][k];
+      }
+    } else {
+      load8(axis == 1 ? y : z, i0, n, vec, pc);
+      load8(v + axis * padded, i0, n, vec_v, pw);
+    }
     if (push.enabled) {
 #pragma unroll
       for (int k = 0; k < kSlabItems; ++k)
@@ -450,8 +467,12 @@ cudaError_t slab_scatter(const float* x, const float* y, const float* z, const f
   uint32_t* block_sum = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) +
                                                     align_up(entries * sizeof(uint32_t), 256));
   constexpr int kStageBytes = 6 * kSlabTile * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(slab_scatter_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+  // Alone on the GPU (the one-piece exchange, or a plain partition) the kernel wants every
+  // load of a tile in flight at once; beside the local sort it keeps to few registers.
+  const bool eager = slices <= 1;
+  auto kernel = eager ? slab_scatter_kernel<true> : slab_scatter_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kStageBytes);
   if (e != cudaSuccess) return e;
   // The whole input, or the tiles of one slice.  Blocks per multiprocessor: all four that fit
   // when the kernel runs alone; fewer in the sliced exchange, where the local sort's kernels
@@ -463,12 +484,12 @@ cudaError_t slab_scatter(const float* x, const float* y, const float* z, const f
     tile_end = std::min(tiles, tile_begin + tiles_per_slice);
   }
   if (tile_end == tile_begin) return cudaSuccess;  // a slice without tiles
-  const int per_sm = slices > 0 ? exchange_blocks_per_sm() : 4;
+  const int per_sm = eager ? 2 : exchange_blocks_per_sm();
   // per_sm 0: one block per tile (blocks come and go, so that a kernel of higher priority
   // takes the multiprocessors over as they retire).
   const int grid = per_sm > 0 ? std::min(tile_end - tile_begin, sm_count() * per_sm)
                               : tile_end - tile_begin;
-  slab_scatter_kernel<<<grid, kSlabThreads, kStageBytes, stream>>>(
+  kernel<<<grid, kSlabThreads, kStageBytes, stream>>>(
       x, y, z, v, padded, n, g, g.nx / world, world, vec, tiles, tile_begin, tile_end, tile_count,
       block_sum, tg, push);
   count_launches(1);

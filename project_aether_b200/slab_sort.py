@@ -102,18 +102,40 @@ MAX_SLICES = 32            # kMaxSlices of the library
 WAIT_POLLS = 1 << 22       # polls (256 ns apart: about a second) before a slice wait gives up
 
 
+# How the sliced exchange shares the GPU with the local sort (set with `configure`).
+_settings = {
+    'overlap': None,          # None: from four ranks on
+    'resident_blocks': None,  # exchange blocks per multiprocessor beside the sort; None: 0
+    'sort_stream': None,      # None: a high-priority stream of its own when overlapping
+}
+
+
+def configure(overlap: Optional[bool] = None, resident_blocks: Optional[int] = None,
+              sort_stream: Optional[bool] = None) -> None:
+    """Tuning of `distributed_sort(exchange='peer')`; None restores a default.
+
+    overlap: run the local sort's count and scatter kernels beside the exchange kernels, slice
+      by slice.  Default: from four ranks on.  Both sides stream through the same
+      multiprocessors; with two ranks half of every rank's particles also pass through local
+      memory and the two slow each other down by more than the overlap gains (measured on the
+      256 M configuration: 9.5 ms overlapped, 8.9 ms one after the other), so there the
+      exchange runs in one piece and the ordinary local sort follows it.
+    resident_blocks: thread blocks of the exchange kernel per multiprocessor while it runs
+      beside the sort (1..4), or 0 for one block per tile, which lets the sort's kernels take
+      the multiprocessors over as the exchange's blocks retire.  Default 0.
+    sort_stream: run the sliced local sort on a high-priority stream of its own (so that its
+      short kernels are scheduled ahead of the exchange kernel's remaining blocks) instead of
+      the caller's stream.  Default: yes when overlapping.
+    Measured at four ranks (256 M particles, ms per step): 5.46 with the defaults, 5.75 with
+    two resident blocks and the sort on the caller's stream, 6.63 with one, 6.32 without overlap."""
+    _settings.update(overlap=overlap, resident_blocks=resident_blocks, sort_stream=sort_stream)
+    for state in _states.values():
+        state.sort_stream = None
+
+
 def overlap_default(world: int) -> bool:
-    """Whether the local sort's count and scatter kernels run beside the exchange kernels.
-    Both stream through L2; with two ranks the exchange moves half of every rank's particles
-    through local memory as well and the two slow each other down by more than the overlap
-    gains, so the step runs them one after the other.  From four ranks on the exchange is
-    bound by NVLink, touches little local memory, and hides the local work.
-    AETHER_EXCHANGE_OVERLAP=0/1 overrides."""
-    import os
-    forced = os.environ.get('AETHER_EXCHANGE_OVERLAP')
-    if forced in ('0', '1'):
-        return forced == '1'
-    return world >= 4
+    """Whether the local sort runs beside the exchange (see `configure`)."""
+    return world >= 4 if _settings['overlap'] is None else bool(_settings['overlap'])
 
 
 class PeerBuffers:
@@ -151,13 +173,11 @@ class _ExchangeState:
         self.epoch = 0
         self.slices = 0            # slices agreed for the next step (0: not yet known)
         self.plan_n = 0            # particle count the next local sort is planned for
-        import os
-        low = os.environ.get('AETHER_EXCHANGE_PRIORITY') == 'low'
-        self.exchange_stream = torch.cuda.Stream(device=device, priority=0 if low else -1)
-        self.sort_stream = torch.cuda.Stream(device=device, priority=-1) if low else None
+        self.device = device
+        self.exchange_stream = torch.cuda.Stream(device=device)
+        self.sort_stream = None      # created on demand (high priority)
         self.side_stream = torch.cuda.Stream(device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
-        self.resident_blocks = None  # exchange blocks per multiprocessor; None: 2 beside the sort, else 4
         self.exchange_events = None  # (begin, end) of the last exchange, when timing is on
         self.time_exchange = False
 
@@ -275,9 +295,9 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             epoch = state.epoch
             pointers = (ctypes.c_void_p * world)(*buffers.pointers)
             flag_pointers = (ctypes.c_void_p * world)(*buffers.flag_pointers)
-            _native.check(lib.AetherSlabExchangeSetResidentBlocks(
-                state.resident_blocks if state.resident_blocks is not None
-                else (2 if overlap else 4)), 'AetherSlabExchangeSetResidentBlocks')
+            resident = _settings['resident_blocks']
+            _native.check(lib.AetherSlabExchangeSetResidentBlocks(0 if resident is None else resident),
+                          'AetherSlabExchangeSetResidentBlocks')
             state.exchange_stream.wait_event(gathered)
             with torch.cuda.stream(state.exchange_stream):
                 if state.time_exchange:
@@ -328,10 +348,13 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
                 mark('sort')
                 return out
             # The local sort, slice by slice as the slices arrive (or, without overlap, once
-            # this rank's own exchange kernels are through).  It runs on the caller's stream,
-            # or (AETHER_EXCHANGE_PRIORITY=low) on a high-priority stream of its own, so that
-            # its short kernels take the multiprocessors over from the exchange kernel's blocks.
-            sort_on = state.sort_stream if state.sort_stream is not None else current
+            # this rank's own exchange kernels are through).  It runs on a high-priority stream
+            # of its own, so that its short kernels take the multiprocessors over from the
+            # exchange kernel's blocks, or on the caller's stream (see `configure`).
+            own_stream = overlap if _settings['sort_stream'] is None else _settings['sort_stream']
+            if own_stream and state.sort_stream is None:
+                state.sort_stream = torch.cuda.Stream(device=device, priority=-1)
+            sort_on = state.sort_stream if own_stream else current
             handle = ctypes.c_void_p(sort_on.cuda_stream)
             if sort_on is not current:
                 sort_on.wait_event(gathered)
