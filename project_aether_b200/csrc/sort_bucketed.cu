@@ -725,6 +725,7 @@ struct FinishShape {
   static constexpr int kMaxCells = 1 << (LOW_BITS + 2 - kShuffleBits);
   static constexpr uint32_t kLargestBucket = static_cast<uint32_t>(kMaxSegments) * CAPACITY;
   static_assert(kWordsPerThread == 8, "the counter scan reads eight words per thread");
+  static_assert(kHistWords >= CAPACITY, "the tie step lays one word per record over the counters");
 };
 using FinishSmall = FinishShape<512, 2560, 14>;
 using FinishLarge = FinishShape<1024, 5120, 15>;
@@ -827,7 +828,7 @@ __device__ __forceinline__ int drop_for(int cells) {
 // first_cell + cells_here - 1 (at most Shape::kMaxCells).  The low key of a record is
 // its key minus the key of the first cell's first shuffle value; the counters resolve
 // all but its `drop` lowest bits, which the tie step orders together with the index.
-// s.hist must be zero over the counters used.
+// s.hist must be zero over the counters used; the call leaves it overwritten.
 // Returns false if a byte counter wrapped (more than 255 records on one counter).
 template <class Shape>
 __device__ __forceinline__ bool sort_staged(FinishSmem<Shape>& s, const FinishOut& out, int count,
@@ -929,56 +930,58 @@ __device__ __forceinline__ bool sort_staged(FinishSmem<Shape>& s, const FinishOu
       const int sh = 8 * (low & 3);
       const uint32_t start = s.word_prefix[low >> 2] + byte_sum(word & ((1u << sh) - 1u));
       const uint32_t length = (word >> sh) & 0xffu;
-      s.order[start + rank] = static_cast<uint16_t>(r);
       if (length > 1) run[k] = start | (length << 16);
+      else s.order[start] = static_cast<uint16_t>(r);
     }
   }
   __syncthreads();
 
   // Records that share a counter must appear in ascending (dropped key bits,
-  // original index): a record inside such a run moves to (run start + number of
+  // original index): a record inside such a run goes to (run start + number of
   // smaller records in the run).  Indices stay below 2^30, so the dropped bits
-  // ride above them in one word.
-  uint32_t moved[kItems];
+  // ride above them in one word.  The words to compare are laid out run by run
+  // over the counters, which nobody reads any more: a run is then a few
+  // neighbouring words instead of as many records scattered over s.raw.
+  uint32_t* tie = s.hist;
 #pragma unroll
-  for (int k = 0; k < kItems; ++k) {
-    moved[k] = 0xffffffffu;
+  for (int k = 0; k < kItems; ++k)
     if (run[k]) {
       const int r = tid + k * kThreads;
-      const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
-      const uint32_t mine = ((s.raw[r * kRecordWords] & drop_mask) << 30) | s.raw[r * kRecordWords + 1];
-      uint32_t smaller = 0;
-      for (uint32_t j = 0; j < length; ++j) {
-        const uint32_t* other = &s.raw[s.order[start + j] * kRecordWords];
-        smaller += (((other[0] & drop_mask) << 30) | other[1]) < mine;
-      }
-      moved[k] = start + smaller;
+      tie[(run[k] & 0xffffu) + (packed[k] >> 16)] =
+          ((s.raw[r * kRecordWords] & drop_mask) << 30) | s.raw[r * kRecordWords + 1];
     }
-  }
   __syncthreads();
 #pragma unroll
   for (int k = 0; k < kItems; ++k)
-    if (moved[k] != 0xffffffffu) s.order[moved[k]] = static_cast<uint16_t>(tid + k * kThreads);
+    if (run[k]) {
+      const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
+      const uint32_t mine = tie[start + (packed[k] >> 16)];
+      uint32_t smaller = 0;
+      for (uint32_t j = 0; j < length; ++j) smaller += tie[start + j] < mine;
+      s.order[start + smaller] = static_cast<uint16_t>(tid + k * kThreads);
+    }
   __syncthreads();
 
-  // Coalesced output: each lane pulls one whole record out of shared memory
-  // and writes its eight words to the eight output arrays.
-  for (int d = tid; d < count; d += kThreads) {
-    const int rec = s.order[d];
-    const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords]);
-    const uint4 c = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4]);
-    const size_t o = static_cast<size_t>(begin) + d;
-    __stcs(out.keys + o, a.x);
-    __stcs(out.index + o, static_cast<int32_t>(a.y));
-    if (out.xs) {  // keys-only calls leave the payload out
-      __stcs(out.xs + o, __uint_as_float(a.z));
-      __stcs(out.ys + o, __uint_as_float(a.w));
-      __stcs(out.zs + o, __uint_as_float(c.x));
-    }
-    if (out.vs) {
-      __stcs(out.vs + o, __uint_as_float(c.y));
-      __stcs(out.vs + out.padded_sorted + o, __uint_as_float(c.z));
-      __stcs(out.vs + 2 * out.padded_sorted + o, __uint_as_float(c.w));
+  // Coalesced output.  Two neighbouring lanes pull one record out of shared memory, a half
+  // each (a quarter warp then reads four whole records: fewer bank conflicts than eight
+  // halves of eight records), and write their four words to four of the eight output arrays.
+  {
+    const int half = tid & 1;
+    uint32_t* const o0 = half ? reinterpret_cast<uint32_t*>(out.zs) : out.keys;
+    uint32_t* const o1 = half ? reinterpret_cast<uint32_t*>(out.vs)
+                              : reinterpret_cast<uint32_t*>(out.index);
+    uint32_t* const o2 = half ? (out.vs ? reinterpret_cast<uint32_t*>(out.vs + out.padded_sorted) : nullptr)
+                              : reinterpret_cast<uint32_t*>(out.xs);
+    uint32_t* const o3 = half ? (out.vs ? reinterpret_cast<uint32_t*>(out.vs + 2 * out.padded_sorted) : nullptr)
+                              : reinterpret_cast<uint32_t*>(out.ys);
+    for (int d = tid >> 1; d < count; d += kThreads / 2) {
+      const int rec = s.order[d];
+      const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4 * half]);
+      const size_t o = static_cast<size_t>(begin) + d;
+      if (o0) __stcs(o0 + o, a.x);  // keys-only calls leave the payload out
+      if (o1) __stcs(o1 + o, a.y);
+      if (o2) __stcs(o2 + o, a.z);
+      if (o3) __stcs(o3 + o, a.w);
     }
   }
   __syncthreads();
