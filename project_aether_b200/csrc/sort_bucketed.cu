@@ -943,21 +943,26 @@ __device__ __forceinline__ bool sort_staged(FinishSmem<Shape>& s, const FinishOu
   // over the counters, which nobody reads any more: a run is then a few
   // neighbouring words instead of as many records scattered over s.raw.
   uint32_t* tie = s.hist;
+  uint32_t mine[kItems];
 #pragma unroll
   for (int k = 0; k < kItems; ++k)
     if (run[k]) {
       const int r = tid + k * kThreads;
-      tie[(run[k] & 0xffffu) + (packed[k] >> 16)] =
-          ((s.raw[r * kRecordWords] & drop_mask) << 30) | s.raw[r * kRecordWords + 1];
+      const uint2 key_index = *reinterpret_cast<const uint2*>(&s.raw[r * kRecordWords]);
+      mine[k] = ((key_index.x & drop_mask) << 30) | key_index.y;
+      tie[(run[k] & 0xffffu) + (packed[k] >> 16)] = mine[k];
     }
   __syncthreads();
 #pragma unroll
   for (int k = 0; k < kItems; ++k)
     if (run[k]) {
       const uint32_t start = run[k] & 0xffffu, length = run[k] >> 16;
-      const uint32_t mine = tie[start + (packed[k] >> 16)];
       uint32_t smaller = 0;
-      for (uint32_t j = 0; j < length; ++j) smaller += tie[start + j] < mine;
+      // Most runs are two or three records: four independent loads, then the rare rest.
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j)
+        if (j < length) smaller += tie[start + j] < mine[k];
+      for (uint32_t j = 4; j < length; ++j) smaller += tie[start + j] < mine[k];
       s.order[start + smaller] = static_cast<uint16_t>(tid + k * kThreads);
     }
   __syncthreads();
