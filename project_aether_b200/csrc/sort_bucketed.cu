@@ -845,15 +845,20 @@ __device__ __forceinline__ bool sort_staged(FinishSmem<Shape>& s, const FinishOu
   // Count the low key bits with byte-wide counters; the value an add returns
   // is the record's rank among the records of its counter.
   uint32_t packed[kItems];  // counter id | rank << 16
+  uint32_t mine[kItems];    // what orders the records of one counter: dropped key bits, index
 #pragma unroll
   for (int k = 0; k < kItems; ++k) {
     const int r = tid + k * kThreads;
     packed[k] = 0;
+    mine[k] = 0;
     if (r < count) {
-      const uint32_t low = (s.raw[r * kRecordWords] - key_base) >> drop;
+      // Key and index in one access: it costs the same bank conflicts as the key alone.
+      const uint2 key_index = *reinterpret_cast<const uint2*>(&s.raw[r * kRecordWords]);
+      const uint32_t low = (key_index.x - key_base) >> drop;
       const int sh = 8 * (low & 3);
       const uint32_t old = atomicAdd(&s.hist[low >> 2], 1u << sh);
       packed[k] = low | (((old >> sh) & 0xffu) << 16);
+      mine[k] = ((key_index.x & drop_mask) << 30) | key_index.y;
     }
   }
   __syncthreads();
@@ -943,15 +948,9 @@ __device__ __forceinline__ bool sort_staged(FinishSmem<Shape>& s, const FinishOu
   // over the counters, which nobody reads any more: a run is then a few
   // neighbouring words instead of as many records scattered over s.raw.
   uint32_t* tie = s.hist;
-  uint32_t mine[kItems];
 #pragma unroll
   for (int k = 0; k < kItems; ++k)
-    if (run[k]) {
-      const int r = tid + k * kThreads;
-      const uint2 key_index = *reinterpret_cast<const uint2*>(&s.raw[r * kRecordWords]);
-      mine[k] = ((key_index.x & drop_mask) << 30) | key_index.y;
-      tie[(run[k] & 0xffffu) + (packed[k] >> 16)] = mine[k];
-    }
+    if (run[k]) tie[(run[k] & 0xffffu) + (packed[k] >> 16)] = mine[k];
   __syncthreads();
 #pragma unroll
   for (int k = 0; k < kItems; ++k)
@@ -979,8 +978,10 @@ __device__ __forceinline__ bool sort_staged(FinishSmem<Shape>& s, const FinishOu
                               : reinterpret_cast<uint32_t*>(out.xs);
     uint32_t* const o3 = half ? (out.vs ? reinterpret_cast<uint32_t*>(out.vs + 2 * out.padded_sorted) : nullptr)
                               : reinterpret_cast<uint32_t*>(out.ys);
+    int next = tid >> 1 < count ? s.order[tid >> 1] : 0;  // one round ahead of its use
     for (int d = tid >> 1; d < count; d += kThreads / 2) {
-      const int rec = s.order[d];
+      const int rec = next;
+      if (d + kThreads / 2 < count) next = s.order[d + kThreads / 2];
       const uint4 a = *reinterpret_cast<const uint4*>(&s.raw[rec * kRecordWords + 4 * half]);
       const size_t o = static_cast<size_t>(begin) + d;
       if (o0) __stcs(o0 + o, a.x);  // keys-only calls leave the payload out
