@@ -57,7 +57,7 @@ STAGE_BYTES_PER_PARTICLE = {
 # kernel, from one ncu capture at 2^24 particles of the same density; traffic grows in
 # proportion to the particle count, so a launch's traffic is this figure times its particles.
 NCU_DRAM_BYTES_PER_PARTICLE = {'bucket_count': 12.2, 'bucket_scatter': 52.9,
-                               'bucket_finish': 62.4}
+                               'bucket_finish': 62.1}
 
 
 def measured_peak():
