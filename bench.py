@@ -671,12 +671,14 @@ def run_multi(args):
 
     exchange = os.environ.get('AETHER_EXCHANGE', 'peer')  # 'peer' (NVLink stores) or 'nccl'
     # Tuning of the sliced exchange from the environment (for sweeps): overlap 0/1, resident
-    # exchange blocks per multiprocessor 0..4, local sort on a stream of its own 0/1.
+    # exchange blocks per multiprocessor 0..4, local sort on a stream of its own 0/1, transport
+    # 'stores' or 'copies'.
     knobs = {key: os.environ.get(name) for key, name in (
         ('overlap', 'AETHER_EXCHANGE_OVERLAP'), ('resident_blocks', 'AETHER_EXCHANGE_BLOCKS'),
         ('sort_stream', 'AETHER_EXCHANGE_SORT_STREAM'))}
     slab_sort.configure(**{key: (None if value is None else int(value))
-                           for key, value in knobs.items()})
+                           for key, value in knobs.items()},
+                        transport=os.environ.get('AETHER_EXCHANGE_TRANSPORT'))
     steady = w.name.startswith('c5')
     state = {'x': x, 'y': y, 'z': z, 'v': v}
 

@@ -500,6 +500,21 @@ extern "C" int AetherSlabExchangeScatterSliced(
                           workspace_bytes, stream, &signal);
 }
 
+extern "C" int AetherSlabExchangeSignal(int world, int rank, int slices, int slice,
+                                        uint32_t epoch, uint32_t* const* peer_flags,
+                                        void* stream) {
+  return slab_signal_slice(world, rank, slices, slice, epoch, peer_flags,
+                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int AetherSlabExchangeCopy(void* destination, const void* source, size_t bytes,
+                                      void* stream) {
+  if (bytes == 0) return cudaSuccess;
+  if (!destination || !source) return cudaErrorInvalidValue;
+  return cudaMemcpyAsync(destination, source, bytes, cudaMemcpyDeviceToDevice,
+                         static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int AetherSlabExchangeWait(const uint32_t* flags, int world, int slices, int slice,
                                       uint32_t epoch, uint32_t poll_limit, int32_t* error_out,
                                       void* stream) {

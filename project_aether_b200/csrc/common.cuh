@@ -319,6 +319,8 @@ void slab_exchange_set_blocks_per_sm(int blocks);
 cudaError_t slab_exchange_slice_counts(int64_t n, int world, int slices, int64_t* slice_counts,
                                        void* workspace, size_t workspace_bytes,
                                        cudaStream_t stream);
+cudaError_t slab_signal_slice(int world, int rank, int slices, int slice, uint32_t epoch,
+                              uint32_t* const* peer_flags, cudaStream_t stream);
 cudaError_t slab_wait_slice(const uint32_t* flags, int world, int slices, int slice, uint32_t epoch,
                             uint32_t poll_limit, int32_t* error, cudaStream_t stream);
 cudaError_t particle_push(float* x, float* y, float* z, float* vx, float* vy, float* vz, int64_t n,

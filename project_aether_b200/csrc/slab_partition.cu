@@ -618,6 +618,21 @@ cudaError_t slab_wait_slice(const uint32_t* flags, int world, int slices, int sl
   return cudaGetLastError();
 }
 
+cudaError_t slab_signal_slice(int world, int rank, int slices, int slice, uint32_t epoch,
+                              uint32_t* const* peer_flags, cudaStream_t stream) {
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || slices < 1 ||
+      slices > kMaxSlices || slice < 0 || slice >= slices || !peer_flags)
+    return cudaErrorInvalidValue;
+  SliceFlags flags{};
+  for (int d = 0; d < world; ++d) {
+    if (!peer_flags[d]) return cudaErrorInvalidValue;
+    flags.peer[d] = peer_flags[d];
+  }
+  slab_signal_kernel<<<1, 32, 0, stream>>>(flags, world, rank, slices, slice, epoch);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
 cudaError_t slab_exchange_scatter(const float* x, const float* y, const float* z, const float* v,
                                   int64_t padded, int64_t n, const AetherGrid& g, int world,
                                   int rank, float* const* peer_buffers, int64_t capacity,

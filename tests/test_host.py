@@ -174,3 +174,35 @@ def test_scaled_workload_keeps_particles_per_cell():
     assert w.n == 1 << 24 and w.grid.cells[:2] == full.grid.cells[:2]
     assert w.n * full.grid.num_cells == full.n * w.grid.num_cells
     assert workloads.scaled_workload('c4_256m_512', 28) == workloads.WORKLOADS['c4_256m_512']
+
+
+def test_copy_plan_tiles_every_destination_without_gaps_or_overlap():
+    """The copies planned by all sources for one destination cover [0, received) exactly once,
+    source by source and, within a source, slice by slice (the ordering rule of the exchange)."""
+    import numpy as np
+    from project_aether_b200 import slab_sort
+    rng = np.random.default_rng(5)
+    for world, slices in ((2, 1), (3, 4), (8, 32)):
+        counts = rng.integers(0, 50, size=(world, slices, world))
+        counts[rng.integers(0, world), :, :] = 0  # a source with nothing to send
+        received = counts.sum(axis=(0, 1))
+        for d in range(world):
+            pieces = []
+            for s in range(world):
+                if s == d:
+                    # A rank's own share is stored by the partition kernel: same rule.
+                    first = counts[:s, :, d].sum()
+                    pieces += [(first + counts[s, :k, d].sum(), counts[s, k, d], s, k)
+                               for k in range(slices)]
+                    continue
+                plan = slab_sort.copy_plan(counts, s)
+                assert [len(row) for row in plan] == [world - 1] * slices
+                assert [row[0][0] for row in plan] == [(s + 1) % world] * slices
+                for k, row in enumerate(plan):
+                    pieces += [(first, count, s, k) for dest, first, count in row if dest == d]
+            pieces.sort(key=lambda piece: (piece[2], piece[3]))
+            at = 0
+            for first, count, _, _ in pieces:
+                assert first == at
+                at += count
+            assert at == received[d]

@@ -285,6 +285,34 @@ def _nccl_worker(rank, world, port, result_dir):
                     got.velocity.cpu().numpy()[k, :shares_now[rank][0].size], shares_now[rank][3 + k])
             state = (*got.positions, got.velocity)
         assert slab_sort.exchange_status(device) == 0
+        # The same loop with the copy engines as transport, one after the other and overlapped.
+        for overlap in (False, True):
+            slab_sort.configure(transport='copies', overlap=overlap)
+            state = (x, y, z, v)
+            shares_now = host
+            for step in range(3):
+                moved = []
+                for h in shares_now:
+                    p, w = so.push_particles(list(h[:3]), list(h[3:]), dt, grid.lo, grid.hi)
+                    moved.append(tuple(p) + tuple(w))
+                received = so.exchange_replay(moved, ogrid, world)
+                shares_now = []
+                for r, rec in enumerate(received):
+                    o, wd = slab_sort.slab_range(grid, world, r)
+                    perm = so.sort_particles(*rec[:3], ogrid, 700 + step, ix_offset=o,
+                                             nx_local=wd).particle_index
+                    shares_now.append(tuple(a[perm] for a in rec))
+                got = slab_sort.distributed_sort(*state, grid, 700 + step,
+                                                 push=(dt, grid.lo, grid.hi))
+                for k in range(3):
+                    np.testing.assert_array_equal(got.positions[k].cpu().numpy(),
+                                                  shares_now[rank][k])
+                    np.testing.assert_array_equal(
+                        got.velocity.cpu().numpy()[k, :shares_now[rank][0].size],
+                        shares_now[rank][3 + k])
+                state = (*got.positions, got.velocity)
+            assert slab_sort.exchange_status(device) == 0
+        slab_sort.configure()
         open(os.path.join(result_dir, f'ok{rank}'), 'w').close()
     finally:
         dist.destroy_process_group()
@@ -300,13 +328,18 @@ def test_distributed_sort_over_nccl(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize('world,slices,n', [(2, 1, 30_000), (4, 3, 50_000), (8, 8, 200_000),
-                                            (3, 32, 70_001)])
-def test_sliced_exchange_and_sliced_sort_emulated_on_one_gpu(cuda, world, slices, n):
+@pytest.mark.parametrize('world,slices,n,transport', [
+    (2, 1, 30_000, 'stores'), (4, 3, 50_000, 'stores'), (8, 8, 200_000, 'stores'),
+    (3, 32, 70_001, 'stores'), (2, 4, 30_000, 'copies'), (8, 3, 100_000, 'copies'),
+    (3, 1, 70_001, 'copies')])
+def test_sliced_exchange_and_sliced_sort_emulated_on_one_gpu(cuda, world, slices, n, transport):
     """The sliced pipeline through the C ABI with all ranks on one GPU, one after another:
     counts per (slice, destination), the gathered matrix, every rank's exchange kernel storing
     into the ranks' receive buffers and setting their arrival flags, then per rank the slice
     waits (the flags are set by then, so no wait polls twice) and the sort slice by slice.
+    With transport 'copies' the exchange kernel partitions into staging rows laid out like the
+    receive buffers (a rank's own share goes straight into its buffer) and device-to-device
+    copies, planned by slab_sort.copy_plan, carry the rest; the signal follows the copies.
     Every rank's result equals the oracle's replay of exchange + slab-local sort."""
     import ctypes
     from project_aether_b200 import _native
@@ -355,12 +388,32 @@ def test_sliced_exchange_and_sliced_sort_emulated_on_one_gpu(cuda, world, slices
                 'prepare')
             assert torch.equal(totals2d, matrix.sum(dim=1))
             segments.append(seg)
+            if transport == 'copies':
+                staging = torch.zeros((world, 6 * capacity), dtype=torch.float32, device=cuda)
+                scratch = torch.zeros(flag_words, dtype=torch.int32, device=cuda)
+                rows_r = [buffers[r].data_ptr() + 4 * flag_words if d == r else staging[d].data_ptr()
+                          for d in range(world)]
+                targets = (ctypes.c_void_p * world)(*rows_r)
+                flags_r = (ctypes.c_void_p * world)(*([scratch.data_ptr()] * world))
+                plan = slab_sort.copy_plan(matrix.cpu().numpy(), r)
+            else:
+                targets, flags_r = data_pointers, flag_pointers
             for k in range(slices):
                 _native.check(lib.AetherSlabExchangeScatterSliced(
                     x.data_ptr(), y.data_ptr(), z.data_ptr(), v.data_ptr(), v.stride(0), x.numel(),
-                    move[0], move[1], move[2], ctypes.byref(g), world, r, data_pointers, capacity,
-                    totals2d.data_ptr(), error.data_ptr(), slices, k, epoch, flag_pointers,
+                    move[0], move[1], move[2], ctypes.byref(g), world, r, targets, capacity,
+                    totals2d.data_ptr(), error.data_ptr(), slices, k, epoch, flags_r,
                     spaces[r].data_ptr(), spaces[r].numel(), stream), 'exchange')
+                if transport == 'copies':
+                    for d, first, count in plan[k]:
+                        for a in range(6):
+                            at = 4 * (a * capacity + first)
+                            _native.check(lib.AetherSlabExchangeCopy(
+                                ctypes.c_void_p(buffers[d].data_ptr() + 4 * flag_words + at),
+                                ctypes.c_void_p(rows_r[d] + at), 4 * count, stream), 'copy')
+                    _native.check(lib.AetherSlabExchangeSignal(world, r, slices, k, epoch,
+                                                               flag_pointers, stream), 'signal')
+            torch.cuda.synchronize()  # the staging rows of this rank go out of scope
         torch.cuda.synchronize()
         assert int(error) == 0
         for b in buffers:  # every (source, slice) flag carries the epoch
