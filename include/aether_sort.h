@@ -205,13 +205,15 @@ int AetherSlabExchangeScatterMoved(const float* x, const float* y, const float* 
  *       the flag cannot overtake the data.  Called once per slice, in order; epochs must
  *       grow from step to step.
  *   AetherSlabExchangeSignal        the one-warp kernel alone, and
- *   AetherSlabExchangeCopy          one cudaMemcpyAsync, device to device: the transport of the
- *       exchange by copy engine.  There AetherSlabExchangeScatterSliced partitions slice
- *       `slice` into staging buffers in this GPU's own memory (peer_buffers[d] = the staging
- *       buffer for destination d, laid out like d's receive buffer; peer_flags[d] = a
- *       scratch flag array), one copy per destination and array then carries the slice's
- *       share into the destination's receive buffer without occupying a multiprocessor, and
- *       the signal follows the copies in stream order.
+ *   AetherSlabExchangeCopy          one device-to-device copy of `rows` rows of row_bytes
+ *       bytes, pitch_bytes apart on both sides (cudaMemcpy2DAsync; cudaMemcpyAsync for one
+ *       row): the transport of the exchange by copy engine.  There
+ *       AetherSlabExchangeScatterSliced partitions slice `slice` into staging buffers in this
+ *       GPU's own memory (peer_buffers[d] = the staging buffer for destination d, laid out
+ *       like d's receive buffer; peer_flags[d] = a scratch flag array), one copy per
+ *       destination (six rows: the six arrays, `capacity` floats apart) then carries the
+ *       slice's share into the destination's receive buffer without occupying a
+ *       multiprocessor, and the signal follows the copies in stream order.
  *   AetherSlabExchangeWait          enqueues a one-warp kernel that polls this rank's flag
  *       array until every source has signalled `slice` of `epoch`.  The wait is bounded:
  *       after poll_limit polls (256 ns apart) it stores 6 in *error_out (device) and
@@ -245,7 +247,8 @@ int AetherSlabExchangeScatterSliced(const float* x, const float* y, const float*
                                     size_t workspace_bytes, void* stream);
 int AetherSlabExchangeSignal(int world, int rank, int slices, int slice, uint32_t epoch,
                              uint32_t* const* peer_flags, void* stream);
-int AetherSlabExchangeCopy(void* destination, const void* source, size_t bytes, void* stream);
+int AetherSlabExchangeCopy(void* destination, const void* source, size_t row_bytes, int rows,
+                           size_t pitch_bytes, void* stream);
 int AetherSlabExchangeWait(const uint32_t* flags, int world, int slices, int slice,
                            uint32_t epoch, uint32_t poll_limit, int32_t* error_out, void* stream);
 size_t AetherSortSlicedWorkspaceBytes(int64_t capacity, int64_t plan_n, int64_t num_cells,

@@ -90,7 +90,8 @@ _SIGNATURES = {
     'AetherSlabExchangeSignal': (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                 ctypes.c_uint32, ctypes.POINTER(ctypes.c_void_p),
                                                 _P]),
-    'AetherSlabExchangeCopy': (ctypes.c_int, [_P, _P, ctypes.c_size_t, _P]),
+    'AetherSlabExchangeCopy': (ctypes.c_int, [_P, _P, ctypes.c_size_t, ctypes.c_int,
+                                              ctypes.c_size_t, _P]),
     'AetherSlabExchangeWait': (ctypes.c_int, [_P, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                               ctypes.c_uint32, ctypes.c_uint32, _P, _P]),
     'AetherSortSlicedWorkspaceBytes': (ctypes.c_size_t, [_I64, _I64, _I64, ctypes.c_int]),

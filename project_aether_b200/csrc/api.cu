@@ -507,12 +507,16 @@ extern "C" int AetherSlabExchangeSignal(int world, int rank, int slices, int sli
                            static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int AetherSlabExchangeCopy(void* destination, const void* source, size_t bytes,
-                                      void* stream) {
-  if (bytes == 0) return cudaSuccess;
-  if (!destination || !source) return cudaErrorInvalidValue;
-  return cudaMemcpyAsync(destination, source, bytes, cudaMemcpyDeviceToDevice,
-                         static_cast<cudaStream_t>(stream));
+extern "C" int AetherSlabExchangeCopy(void* destination, const void* source, size_t row_bytes,
+                                      int rows, size_t pitch_bytes, void* stream) {
+  if (row_bytes == 0 || rows == 0) return cudaSuccess;
+  if (!destination || !source || rows < 0 || pitch_bytes < row_bytes) return cudaErrorInvalidValue;
+  if (rows == 1)
+    return cudaMemcpyAsync(destination, source, row_bytes, cudaMemcpyDeviceToDevice,
+                           static_cast<cudaStream_t>(stream));
+  return cudaMemcpy2DAsync(destination, pitch_bytes, source, pitch_bytes, row_bytes,
+                           static_cast<size_t>(rows), cudaMemcpyDeviceToDevice,
+                           static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int AetherSlabExchangeWait(const uint32_t* flags, int world, int slices, int slice,

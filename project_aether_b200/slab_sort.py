@@ -105,10 +105,10 @@ WAIT_POLLS = 1 << 22       # polls (256 ns apart: about a second) before a slice
 
 # How the sliced exchange shares the GPU with the local sort (set with `configure`).
 _settings = {
-    'overlap': None,          # None: from four ranks on
+    'overlap': None,          # None: yes
     'resident_blocks': None,  # exchange blocks per multiprocessor beside the sort; None: 0
-    'sort_stream': None,      # None: a high-priority stream of its own when overlapping
-    'transport': None,        # None: 'stores'
+    'sort_stream': None,      # None: a high-priority stream of its own from four ranks on
+    'transport': None,        # None: 'copies'
 }
 
 
@@ -116,27 +116,28 @@ def configure(overlap: Optional[bool] = None, resident_blocks: Optional[int] = N
               sort_stream: Optional[bool] = None, transport: Optional[str] = None) -> None:
     """Tuning of `distributed_sort(exchange='peer')`; None restores a default.
 
-    overlap: run the local sort's count and scatter kernels beside the exchange kernels, slice
-      by slice.  Default: from four ranks on.  Both sides stream through the same
-      multiprocessors; with two ranks half of every rank's particles also pass through local
-      memory and the two slow each other down by more than the overlap gains (measured on the
-      256 M configuration: 9.5 ms overlapped, 8.9 ms one after the other), so there the
-      exchange runs in one piece and the ordinary local sort follows it.
-    resident_blocks: thread blocks of the exchange kernel per multiprocessor while it runs
-      beside the sort (1..4), or 0 for one block per tile, which lets the sort's kernels take
-      the multiprocessors over as the exchange's blocks retire.  Default 0.
-    sort_stream: run the sliced local sort on a high-priority stream of its own (so that its
-      short kernels are scheduled ahead of the exchange kernel's remaining blocks) instead of
-      the caller's stream.  Default: yes when overlapping.
-    transport: 'stores' — the exchange kernel stores every particle straight into its
-      destination GPU's receive buffer over NVLink; 'copies' — the same kernel partitions into
-      staging buffers in this GPU's own memory, laid out like the destinations' receive
-      buffers, and one device-to-device copy per destination, slice and array carries the
-      data over NVLink on the copy engines, so that the multiprocessors are free for the local
-      sort while the links are busy.  The host then has to know the counts before it can
-      enqueue the copies (one wait per step for the count all-gather).
-    Measured at four ranks (256 M particles, ms per step): 5.46 with the defaults, 5.75 with
-    two resident blocks and the sort on the caller's stream, 6.63 with one, 6.32 without overlap."""
+    transport: 'copies' (default) — the exchange kernel partitions into staging buffers in
+      this GPU's own memory, laid out like the destinations' receive buffers (a rank's own
+      share goes straight into its receive buffer), and one device-to-device copy per
+      destination and slice (six rows, one per array) carries the data over NVLink on the copy
+      engines, so that the multiprocessors are free for the local sort while the links are
+      busy.  The host has to know the counts before it can enqueue the copies (one wait per
+      step for the count all-gather).  'stores' — the exchange kernel stores every particle
+      straight into its destination GPU's receive buffer over NVLink (no staging memory, no
+      host wait), and occupies multiprocessors for as long as the links take.
+    overlap: run the local sort's count and scatter kernels beside the exchange, slice by
+      slice.  Default: yes.  (With 'stores' on two ranks the two slow each other down by more
+      than the overlap gains: 9.5 ms overlapped, 8.9 ms one after the other.)
+    resident_blocks ('stores' only): thread blocks of the exchange kernel per multiprocessor
+      while it runs beside the sort (1..4), or 0 for one block per tile, which lets the sort's
+      kernels take the multiprocessors over as the exchange's blocks retire.  Default 0.
+    sort_stream: run the sliced local sort on a high-priority stream of its own instead of the
+      caller's stream.  Default: from four ranks on.
+    Measured on the 256 M configuration, ms per step.  Two ranks: 'stores' one after the other
+    8.8–9.9, 'copies' one after the other 9.7, overlapped 8.2 (caller's stream) and 8.5 (own
+    stream).  Four ranks: 'stores' overlapped 5.36–5.46, one after the other 6.32; 'copies'
+    overlapped 4.74 (own stream) and 4.85 (caller's), one after the other 5.42.  Either way
+    about 500 GB/s per direction cross the links while all ranks send and receive at once."""
     if transport not in (None, 'stores', 'copies'):
         raise ValueError(f'unknown transport {transport!r}')
     _settings.update(overlap=overlap, resident_blocks=resident_blocks, sort_stream=sort_stream,
@@ -147,7 +148,7 @@ def configure(overlap: Optional[bool] = None, resident_blocks: Optional[int] = N
 
 def overlap_default(world: int) -> bool:
     """Whether the local sort runs beside the exchange (see `configure`)."""
-    return world >= 4 if _settings['overlap'] is None else bool(_settings['overlap'])
+    return True if _settings['overlap'] is None else bool(_settings['overlap'])
 
 
 class PeerBuffers:
@@ -243,8 +244,8 @@ def _exchange_by_copies(lib, state, buffers, matrix, x, y, z, velocity, n, move,
     """The exchange with the copy engines as transport (see `configure`): the partition kernel
     writes slice by slice into staging rows in local memory (this rank's own share goes
     straight into its receive buffer), and as soon as the host knows the counts it enqueues,
-    per slice and destination, six device-to-device copies into the destination's receive
-    buffer and behind them the slice's signal.  Returns the event behind the last signal, or
+    per slice and destination, one device-to-device copy (six rows, one per array) into the
+    destination's receive buffer and behind them the slice's signal.  Returns the event behind the last signal, or
     None (nothing copied) when the counts say that some rank's buffer would overflow."""
     device, capacity = state.device, buffers.capacity
     if state.staging is None or state.staging.shape[1] != 6 * capacity:
@@ -292,12 +293,10 @@ def _exchange_by_copies(lib, state, buffers, matrix, x, y, z, velocity, n, move,
             copy_stream.wait_event(part_done[k])
             if count:
                 handle = ctypes.c_void_p(copy_stream.cuda_stream)
-                for a in range(6):
-                    at = 4 * (a * capacity + first)
-                    _native.check(lib.AetherSlabExchangeCopy(
-                        ctypes.c_void_p(buffers.pointers[d] + at),
-                        ctypes.c_void_p(rows[d] + at), 4 * count, handle),
-                        'AetherSlabExchangeCopy')
+                _native.check(lib.AetherSlabExchangeCopy(  # six rows: x, y, z, vx, vy, vz
+                    ctypes.c_void_p(buffers.pointers[d] + 4 * first),
+                    ctypes.c_void_p(rows[d] + 4 * first), 4 * count, 6, 4 * capacity, handle),
+                    'AetherSlabExchangeCopy')
             copied = torch.cuda.Event()
             copied.record(copy_stream)
             signal.wait_event(copied)
@@ -315,14 +314,16 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
                        path: int = PATH_AUTO, mark=lambda name: None,
                        push: Optional[tuple] = None) -> SortedParticles:
     """distributed_sort with the partition and the exchange fused, and the exchange
-    overlapped with the local sort.  One kernel reads the rank's particles once and stores
-    each into its destination GPU's receive buffer over NVLink, on a stream of its own; it
-    works through the input in slices and tells the destinations when a slice is complete.
-    Meanwhile the local sort counts and scatters, slice by slice, what has arrived; only its
-    finish kernels wait for the last slice.  The count all-gather before the exchange is the
-    only collective of a step.  From the second step on the host waits for nothing until
-    everything is enqueued: buffer capacity, slice count and bucket widths come from the
-    previous step's counts (a step whose counts outgrow the buffers is repeated).
+    overlapped with the local sort.  One kernel reads the rank's particles once, slice by
+    slice, on a stream of its own, and puts each where its destination GPU's receive buffer
+    wants it: in staging rows that the copy engines then carry over NVLink, or (transport
+    'stores') straight into the destination's memory; behind every slice the destinations are
+    told that it is complete.  Meanwhile the local sort counts and scatters, slice by slice,
+    what has arrived; only its finish kernels wait for the last slice.  The count all-gather
+    before the exchange is the only collective of a step.  Buffer capacity, slice count and
+    bucket widths come from the previous step's counts (a step whose counts outgrow the
+    buffers is repeated); with 'stores' the host therefore waits for nothing until everything
+    is enqueued, with 'copies' it waits once, for the gathered counts.
     With `push` = (dt, lo, hi) the count and exchange kernels take every particle as it is
     after the move stage, so the particles arrive moved and the inputs stay untouched."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -407,7 +408,7 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             _native.check(lib.AetherSlabExchangeSetResidentBlocks(0 if resident is None else resident),
                           'AetherSlabExchangeSetResidentBlocks')
             state.exchange_stream.wait_event(gathered)
-            by_copies = (_settings['transport'] == 'copies') and world > 1
+            by_copies = _settings['transport'] != 'stores' and world > 1
             if by_copies:
                 sent = _exchange_by_copies(lib, state, buffers, matrix, x, y, z, velocity, n, move,
                                            g, world, rank, totals, slices, epoch, part_ws)
@@ -472,7 +473,8 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             # this rank's own exchange kernels are through).  It runs on a high-priority stream
             # of its own, so that its short kernels take the multiprocessors over from the
             # exchange kernel's blocks, or on the caller's stream (see `configure`).
-            own_stream = overlap if _settings['sort_stream'] is None else _settings['sort_stream']
+            own_stream = ((overlap and world >= 4) if _settings['sort_stream'] is None
+                          else _settings['sort_stream'])
             if own_stream and state.sort_stream is None:
                 state.sort_stream = torch.cuda.Stream(device=device, priority=-1)
             sort_on = state.sort_stream if own_stream else current

@@ -285,9 +285,10 @@ def _nccl_worker(rank, world, port, result_dir):
                     got.velocity.cpu().numpy()[k, :shares_now[rank][0].size], shares_now[rank][3 + k])
             state = (*got.positions, got.velocity)
         assert slab_sort.exchange_status(device) == 0
-        # The same loop with the copy engines as transport, one after the other and overlapped.
-        for overlap in (False, True):
-            slab_sort.configure(transport='copies', overlap=overlap)
+        # The same loop with the other transport and without overlap (the loop above ran the
+        # defaults: copy engines, overlapped).
+        for transport, overlap in (('stores', True), ('stores', False), ('copies', False)):
+            slab_sort.configure(transport=transport, overlap=overlap)
             state = (x, y, z, v)
             shares_now = host
             for step in range(3):
@@ -406,11 +407,10 @@ def test_sliced_exchange_and_sliced_sort_emulated_on_one_gpu(cuda, world, slices
                     spaces[r].data_ptr(), spaces[r].numel(), stream), 'exchange')
                 if transport == 'copies':
                     for d, first, count in plan[k]:
-                        for a in range(6):
-                            at = 4 * (a * capacity + first)
-                            _native.check(lib.AetherSlabExchangeCopy(
-                                ctypes.c_void_p(buffers[d].data_ptr() + 4 * flag_words + at),
-                                ctypes.c_void_p(rows_r[d] + at), 4 * count, stream), 'copy')
+                        _native.check(lib.AetherSlabExchangeCopy(
+                            ctypes.c_void_p(buffers[d].data_ptr() + 4 * (flag_words + first)),
+                            ctypes.c_void_p(rows_r[d] + 4 * first), 4 * count, 6, 4 * capacity,
+                            stream), 'copy')
                     _native.check(lib.AetherSlabExchangeSignal(world, r, slices, k, epoch,
                                                                flag_pointers, stream), 'signal')
             torch.cuda.synchronize()  # the staging rows of this rank go out of scope
