@@ -886,12 +886,16 @@ def run_multi(args):
                         'bytes_per_launch': nbytes, 'ms_per_launch': stages[top]}
         nvlink = None
         if exchange_ms and not steady:
-            # The exchange kernels read 24 B per particle and store 24 B, (G-1)/G of them into
-            # the peers' memory: NVLink bounds them.  Timed over all slices of one step, while
-            # the local sort's kernels run beside them.
+            # 24 B per particle, (G-1)/G of them, cross NVLink: by device-to-device copies out
+            # of the staging rows the partition kernel fills, or by the kernel's own stores.
+            # Timed from the first slice's partition to the last slice's signal of one step,
+            # while the local sort's kernels run beside the exchange.
             crossing = 24 * n_rank * (world - 1) / world
             link = crossing / (exchange_ms * 1e-3) / 1e9
-            nvlink = {'kernel': 'slab_scatter_kernel (all slices)', 'bytes_out_per_gpu': crossing,
+            by_stores = os.environ.get('AETHER_EXCHANGE_TRANSPORT') == 'stores'
+            nvlink = {'kernel': ('slab_scatter_kernel (all slices)' if by_stores else
+                                 'slab_scatter_kernel into staging rows + copy engines (all slices)'),
+                      'bytes_out_per_gpu': crossing,
                       'achieved': link, 'peak': PEER_COPY_GBS, 'unit': 'GB/s',
                       'frac': link / PEER_COPY_GBS, 'ms': exchange_ms,
                       'peak_kind': 'peer copy measured on this pool'}
@@ -901,9 +905,13 @@ def run_multi(args):
             'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'u32',
             'data': 'synthetic',
             'config': workload_config(workload, w, world),
-            'details': {'exchange': ('partition kernel stores into the peers\' receive buffers '
-                                     'over NVLink' if exchange == 'peer'
-                                     else 'one NCCL all-to-all per payload array'),
+            'details': {'exchange': ('one NCCL all-to-all per payload array' if exchange != 'peer'
+                                     else 'partition kernel stores into the peers\' receive buffers '
+                                          'over NVLink, beside the local sort'
+                                     if os.environ.get('AETHER_EXCHANGE_TRANSPORT') == 'stores'
+                                     else 'partition kernel fills staging rows, copy engines carry '
+                                          'them into the peers\' receive buffers over NVLink, '
+                                          'beside the local sort'),
                         'initial_share': ('cell-sorted particles of the rank\'s own slab; every '
                                           'step moves them (dt %g) and re-sorts' % STEADY_DT
                                           if steady else 'random 1/G of all particles per rank')},
