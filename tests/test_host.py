@@ -206,3 +206,13 @@ def test_copy_plan_tiles_every_destination_without_gaps_or_overlap():
                 assert first == at
                 at += count
             assert at == received[d]
+
+
+def test_exchange_settings_are_checked():
+    from project_aether_b200 import slab_sort
+    with pytest.raises(ValueError):
+        slab_sort.configure(transport='carrier pigeon')
+    slab_sort.configure(transport='stores', overlap=False)
+    assert slab_sort.overlap_default(8) is False
+    slab_sort.configure()
+    assert slab_sort.overlap_default(2) is True
