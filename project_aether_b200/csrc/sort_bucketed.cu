@@ -75,16 +75,18 @@ __device__ __forceinline__ void table_add(uint32_t* table, uint32_t bin, uint32_
 
 // One count per lane into `table`; lanes that hit the same bin share one add when the whole
 // warp agrees or (through match.any) when neighbouring lanes do.
+// Returns whether lanes shared an add (the same for all lanes): on input in random order
+// they never do, and the caller then skips the votes for the rest of its round.
 template <int TABLE>
-__device__ __forceinline__ void count_add(uint32_t* table, uint32_t bin, bool valid) {
+__device__ __forceinline__ bool count_add(uint32_t* table, uint32_t bin, bool valid) {
   const uint32_t active = __ballot_sync(0xffffffffu, valid);
-  if (active == 0) return;
+  if (active == 0) return true;
   const int first = __ffs(active) - 1;
   const uint32_t first_bin = __shfl_sync(0xffffffffu, bin, first);
   const bool uniform = __all_sync(0xffffffffu, !valid || bin == first_bin);
   if (uniform) {
     if (static_cast<int>(lane_id()) == first) table_add<TABLE>(table, first_bin, __popc(active));
-    return;
+    return true;
   }
   const uint32_t next_bin = __shfl_down_sync(0xffffffffu, bin, 1);
   const bool clustered = __any_sync(0xffffffffu, valid && lane_id() < 31 && next_bin == bin);
@@ -94,6 +96,7 @@ __device__ __forceinline__ void count_add(uint32_t* table, uint32_t bin, bool va
   } else if (valid) {
     table_add<TABLE>(table, bin, 1u);
   }
+  return clustered;
 }
 
 // Work unit = one slice of one chunk; a block counts the slice into its table and adds the
@@ -161,9 +164,13 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
           push_axis(pz[k], w[2][k], push.dt, push.lo[2], push.hi[2]);
         }
       }
+      bool sharing = true;  // the round's first particle tells whether votes are worth it
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        count_add<TABLE>(target, cell_of(px[k], py[k], pz[k], g) >> shift, i0 + k < last);
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t bin = cell_of(px[k], py[k], pz[k], g) >> shift;
+        if (sharing) sharing = count_add<TABLE>(target, bin, i0 + k < last);
+        else if (i0 + k < last) table_add<TABLE>(target, bin, 1u);
+      }
     }
     if (TABLE != kTableGlobal) {
       __syncthreads();
