@@ -66,6 +66,16 @@ size_t AetherSortWorkspaceBytes(int64_t n, int64_t num_cells, int with_payload);
 int AetherSortBucketPlan(int64_t n, int64_t num_cells, int32_t* cells_per_bucket_log2,
                          int64_t* buckets, int32_t* group_capacity);
 
+/* Process-wide switch (no counterpart in the reference).  The two dozen kernels of one sort
+ * call run one after the other, and the gaps between them are most of what a small call
+ * costs.  mode 1 (default): the short kernels (scans, tables, the digit passes that return at
+ * once when the bucketed path has done the call) are launched so that each may be set up
+ * while the one before it still runs (programmatic dependent launch); mode 2: the scatter and
+ * finish kernels too (measured slower on large inputs); mode 0: ordinary launches.  Every
+ * kernel waits for the grids before it to complete before it touches anything, so the work
+ * runs in stream order in every mode and results do not depend on it. */
+int AetherSortSetChainedLaunches(int32_t mode);
+
 /* Tuning knob of the bucketed path (process-wide; no counterpart in the reference): the
  * finish kernel runs in its small shape (two 512-thread blocks per multiprocessor, 2560
  * records each) while the plan needs at most `buckets` buckets of about a thousand records,

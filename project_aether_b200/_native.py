@@ -31,6 +31,7 @@ _SIGNATURES = {
                                             ctypes.POINTER(ctypes.c_int64),
                                             ctypes.POINTER(ctypes.c_int32)]),
     'AetherSortSetSmallShapeBucketLimit': (ctypes.c_int, [_I64]),
+    'AetherSortSetChainedLaunches': (ctypes.c_int, [ctypes.c_int32]),
     'AetherSortParticlesByCell': (ctypes.c_int, [_P, _P, _P, _I64, ctypes.POINTER(AetherGrid),
                                                  ctypes.c_uint64, _P, _P, _P, _P, _P,
                                                  ctypes.c_size_t, _P]),

@@ -225,6 +225,20 @@ extern "C" int AetherSortBucketPlan(int64_t n, int64_t num_cells, int32_t* cells
   return plan.usable ? 0 : cudaErrorInvalidValue;
 }
 
+namespace aether {
+namespace {
+int g_chained_launches = 1;
+}
+int chained_launches() { return g_chained_launches; }
+void set_chained_launches(int mode) { g_chained_launches = mode; }
+}  // namespace aether
+
+extern "C" int AetherSortSetChainedLaunches(int32_t mode) {
+  if (mode < 0 || mode > 2) return cudaErrorInvalidValue;
+  aether::set_chained_launches(mode);
+  return 0;
+}
+
 extern "C" int AetherSortSetSmallShapeBucketLimit(int64_t buckets) {
   if (buckets < 0) return cudaErrorInvalidValue;
   set_small_shape_buckets(buckets);

@@ -108,6 +108,7 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     PushSpec push, int64_t n, AetherGrid g, int shift,
                     int buckets, int chunks, int chunk_log, int parts, int64_t slice,
                     uint32_t* __restrict__ bucket_count) {
+  chain_begin();
   extern __shared__ uint32_t hist[];
   const int table_words = TABLE == kTableShared16 ? (buckets + 1) / 2 : buckets;
   for (int unit = blockIdx.x; unit < chunks * parts; unit += gridDim.x) {
@@ -192,6 +193,7 @@ bucket_count_kernel(const float* __restrict__ x, const float* __restrict__ y,
 __global__ void __launch_bounds__(256)
 bucket_total_kernel(const uint32_t* __restrict__ bucket_count, int buckets, int chunks,
                     uint32_t* __restrict__ total) {
+  chain_begin();
   const int b = blockIdx.x * 256 + threadIdx.x;
   if (b >= buckets) return;
   uint32_t sum = 0;
@@ -210,6 +212,7 @@ constexpr int kFlatScanBlock = 1024;
 __global__ void __launch_bounds__(kFlatScanBlock)
 run_scan_local_kernel(const uint32_t* __restrict__ count, int64_t entries,
                       uint32_t* __restrict__ local, uint32_t* __restrict__ block_sum) {
+  chain_begin();
   __shared__ uint32_t warp_sum[32];
   __shared__ uint32_t total;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kFlatScanBlock + threadIdx.x;
@@ -221,6 +224,7 @@ run_scan_local_kernel(const uint32_t* __restrict__ count, int64_t entries,
 
 __global__ void __launch_bounds__(kFlatScanBlock)
 run_scan_blocks_kernel(uint32_t* __restrict__ block_sum, int blocks) {
+  chain_begin();
   __shared__ uint32_t warp_sum[32];
   __shared__ uint32_t total, carry;
   if (threadIdx.x == 0) carry = 0;
@@ -240,6 +244,7 @@ __global__ void __launch_bounds__(256)
 run_table_kernel(const uint32_t* __restrict__ local, const uint32_t* __restrict__ block_sum,
                  int64_t entries, uint32_t n, uint32_t* __restrict__ cursor,
                  uint32_t* __restrict__ run_begin) {
+  chain_begin();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (i > entries) return;
   const uint32_t start = i < entries ? local[i] + block_sum[i / kFlatScanBlock] : n;
@@ -257,6 +262,7 @@ bucket_scan_kernel(const uint32_t* __restrict__ bucket_count, int buckets, int64
                    const uint32_t* __restrict__ n_on_device, uint32_t capacity,
                    uint32_t* __restrict__ bucket_start, uint32_t* __restrict__ cursor,
                    Header* __restrict__ hdr) {
+  chain_begin();
   __shared__ uint32_t warp_sum[32];
   __shared__ uint32_t biggest;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -366,6 +372,7 @@ bucket_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
                       PushSpec push, int64_t n, AetherGrid g, uint32_t k0, uint32_t k1, int shift,
                       int buckets, int chunk_log, uint32_t* __restrict__ cursor,
                       uint32_t* __restrict__ records, const Header* __restrict__ hdr) {
+  chain_begin();
   if (hdr->use_standard) return;
   const int64_t groups = (n + ITEMS - 1) / ITEMS;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kScatterThreads;
@@ -622,6 +629,7 @@ bucket_scatter_segments_kernel(const float* __restrict__ x, const float* __restr
 __global__ void __launch_bounds__(256)
 group_cut_kernel(const uint32_t* __restrict__ bucket_start, int buckets, int group_shift,
                  uint32_t capacity, uint2* __restrict__ groups, uint32_t* __restrict__ group_count) {
+  chain_begin();
   const int block_of_buckets = blockIdx.x * 256 + threadIdx.x;
   const int b_first = block_of_buckets << group_shift;
   if (b_first >= buckets) return;
@@ -668,6 +676,7 @@ __global__ void __launch_bounds__(256)
 group_table_kernel(const uint2* __restrict__ groups, const uint32_t* __restrict__ group_count,
                    const uint32_t* __restrict__ bucket_start, const uint32_t* __restrict__ run_begin,
                    int chunks, int buckets, uint32_t* __restrict__ tables) {
+  chain_begin();
   const int lane = threadIdx.x & 31;
   const uint32_t total = *group_count;
   const int row_words = table_row_words(chunks);
@@ -1164,6 +1173,7 @@ template <class Shape>
 __global__ void __launch_bounds__(Shape::kThreads, Shape::kThreads <= 512 ? 2 : 1)
 bucket_finish_kernel(RunTable t, int64_t n, const uint32_t* __restrict__ n_on_device,
                      int64_t num_cells, FinishOut out, Header* __restrict__ hdr) {
+  chain_begin();
   if (hdr->use_standard) return;
   constexpr int kThreads = Shape::kThreads;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -1237,6 +1247,7 @@ template <class Shape>
 __global__ void __launch_bounds__(Shape::kThreads, 1)
 bucket_finish_large_kernel(RunTable t, int64_t num_cells, FinishOut out,
                            Header* __restrict__ hdr, uint32_t capacity) {
+  chain_begin();
   if (hdr->use_standard || hdr->max_bucket <= capacity) return;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FinishSmem<Shape>& s = *reinterpret_cast<FinishSmem<Shape>*>(smem_raw);
@@ -1393,12 +1404,13 @@ cudaError_t launch_finish(const RunTable& t, const SortArgs& a, const FinishOut&
                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem_large);
   if (e != cudaSuccess) return e;
   const int per_sm = Shape::kThreads <= 512 ? 2 : 1;
-  bucket_finish_kernel<Shape><<<std::min(t.buckets, sm_count() * per_sm), Shape::kThreads, smem,
-                                a.stream>>>(t, a.n, n_on_device, a.num_cells, out, hdr);
-  bucket_finish_large_kernel<FinishLarge><<<std::min(t.buckets, sm_count()), FinishLarge::kThreads,
-                                            smem_large, a.stream>>>(t, a.num_cells, out, hdr,
-                                                                    group_capacity);
-  return cudaGetLastError();
+  e = launch_chained<true>(bucket_finish_kernel<Shape>, std::min(t.buckets, sm_count() * per_sm),
+                     Shape::kThreads, smem, a.stream, t, a.n, n_on_device, a.num_cells, out, hdr);
+  if (e != cudaSuccess) return e;
+  e = launch_chained<true>(bucket_finish_large_kernel<FinishLarge>, std::min(t.buckets, sm_count()),
+                     FinishLarge::kThreads, smem_large, a.stream, t, a.num_cells, out, hdr,
+                     group_capacity);
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
@@ -1480,18 +1492,29 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
   const int group_shift = std::min(log2_floor(kMaxGroupBuckets),
                                    std::max(0, log2_floor(max_cells) - p.shift));
   const int blocks_of_buckets = (buckets + (1 << group_shift) - 1) >> group_shift;
-  bucket_total_kernel<<<(buckets + 255) / 256, 256, 0, a.stream>>>(count, buckets, l.chunks, total);
-  bucket_scan_kernel<<<1, kScanThreads, 0, a.stream>>>(total, buckets, a.n, nullptr, largest, start,
-                                                       nullptr, hdr);
-  group_cut_kernel<<<(blocks_of_buckets + 255) / 256, 256, 0, a.stream>>>(
-      start, buckets, group_shift, group_capacity, groups, &hdr->aux_counter[1]);
-  run_scan_local_kernel<<<l.scan_blocks, kFlatScanBlock, 0, a.stream>>>(count, l.entries, local,
-                                                                        block_sum);
-  run_scan_blocks_kernel<<<1, kFlatScanBlock, 0, a.stream>>>(block_sum, l.scan_blocks);
-  run_table_kernel<<<static_cast<int>((l.entries + 1 + 255) / 256), 256, 0, a.stream>>>(
-      local, block_sum, l.entries, static_cast<uint32_t>(a.n), cursor, run_begin);
-  group_table_kernel<<<std::max(1, std::min((buckets + 7) / 8, sm_count() * 8)), 256, 0, a.stream>>>(
-      groups, &hdr->aux_counter[1], start, run_begin, l.chunks, buckets, tables);
+  e = launch_chained(bucket_total_kernel, (buckets + 255) / 256, 256, 0, a.stream, count, buckets,
+                     l.chunks, total);
+  if (e == cudaSuccess)
+    e = launch_chained(bucket_scan_kernel, 1, kScanThreads, 0, a.stream, total, buckets, a.n,
+                       nullptr, largest, start, nullptr, hdr);
+  if (e == cudaSuccess)
+    e = launch_chained(group_cut_kernel, (blocks_of_buckets + 255) / 256, 256, 0, a.stream, start,
+                       buckets, group_shift, group_capacity, groups, &hdr->aux_counter[1]);
+  if (e == cudaSuccess)
+    e = launch_chained(run_scan_local_kernel, l.scan_blocks, kFlatScanBlock, 0, a.stream, count,
+                       l.entries, local, block_sum);
+  if (e == cudaSuccess)
+    e = launch_chained(run_scan_blocks_kernel, 1, kFlatScanBlock, 0, a.stream, block_sum,
+                       l.scan_blocks);
+  if (e == cudaSuccess)
+    e = launch_chained(run_table_kernel, static_cast<int>((l.entries + 1 + 255) / 256), 256, 0,
+                       a.stream, local, block_sum, l.entries, static_cast<uint32_t>(a.n), cursor,
+                       run_begin);
+  if (e == cudaSuccess)
+    e = launch_chained(group_table_kernel,
+                       std::max(1, std::min((buckets + 7) / 8, sm_count() * 8)), 256, 0, a.stream,
+                       groups, &hdr->aux_counter[1], start, run_begin, l.chunks, buckets, tables);
+  if (e != cudaSuccess) return e;
   count_launches(7);
   stage_end(kStageBucketScan, a.stream);
   e = cudaGetLastError();
@@ -1505,9 +1528,10 @@ cudaError_t bucketed_sort(const SortArgs& a, const BucketPlan& p) {
         1, std::min<int64_t>((groups + kScatterThreads - 1) / kScatterThreads,
                              sm_count() * (8 / kItems) * 4)));
     auto kernel = vec ? bucket_scatter_kernel<true, kItems> : bucket_scatter_kernel<false, kItems>;
-    kernel<<<grid, kScatterThreads, 0, a.stream>>>(a.x, a.y, a.z, a.velocity, a.padded, a.push,
-                                                    a.n, a.grid, k0, k1, p.shift, buckets,
-                                                    l.chunk_log, cursor, records, hdr);
+    e = launch_chained<true>(kernel, grid, kScatterThreads, 0, a.stream, a.x, a.y, a.z, a.velocity,
+                       a.padded, a.push, a.n, a.grid, k0, k1, p.shift, buckets, l.chunk_log, cursor,
+                       records, hdr);
+    if (e != cudaSuccess) return e;
   }
   stage_end(kStageBucketScatter, a.stream);
   e = cudaGetLastError();

@@ -31,6 +31,7 @@ keygen_upsweep_kernel(const float* __restrict__ x, const float* __restrict__ y,
                       const float* __restrict__ z, const float4* __restrict__ records, int64_t n,
                       AetherGrid g, uint32_t k0, uint32_t k1, uint32_t* __restrict__ keys,
                       uint32_t* __restrict__ global_hist, const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   __shared__ uint32_t hist[PASSES][kRadix];
   for (int i = threadIdx.x; i < PASSES * kRadix; i += kKeygenThreads) (&hist[0][0])[i] = 0;
@@ -131,6 +132,7 @@ onesweep_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
                      uint32_t* __restrict__ status, uint32_t* __restrict__ tile_counter,
                      uint32_t tiles, int32_t* __restrict__ error, uint32_t poll_limit,
                      const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   PassSmem& s = *reinterpret_cast<PassSmem*>(smem_raw);
@@ -293,6 +295,7 @@ constexpr int kBoundsThreads = 256;
 __global__ void __launch_bounds__(kBoundsThreads)
 cell_bounds_kernel(const uint32_t* __restrict__ keys, int64_t n, int64_t num_cells,
                    int32_t* __restrict__ cell_start, const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   const int lane = threadIdx.x & 31;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kBoundsThreads;
@@ -324,6 +327,7 @@ cell_bounds_kernel(const uint32_t* __restrict__ keys, int64_t n, int64_t num_cel
 __global__ void __launch_bounds__(kBoundsThreads)
 cell_counts_kernel(const int32_t* __restrict__ cell_start, int64_t num_cells,
                    int32_t* __restrict__ cell_counts, const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kBoundsThreads;
   for (int64_t c = static_cast<int64_t>(blockIdx.x) * kBoundsThreads + threadIdx.x; c < num_cells;
@@ -343,6 +347,7 @@ gather_kernel(const int32_t* __restrict__ index, int64_t n, const float* __restr
               const float* __restrict__ v, int64_t padded, float* __restrict__ xs,
               float* __restrict__ ys, float* __restrict__ zs, float* __restrict__ vs,
               int64_t padded_sorted, const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kGatherThreads * 4;
   for (int64_t i0 = (static_cast<int64_t>(blockIdx.x) * kGatherThreads + threadIdx.x) * 4; i0 < n;
@@ -391,6 +396,7 @@ gather_kernel(const int32_t* __restrict__ index, int64_t n, const float* __restr
 
 __global__ void __launch_bounds__(kBoundsThreads)
 clear_words_kernel(uint32_t* __restrict__ words, size_t count, const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   const size_t stride = static_cast<size_t>(gridDim.x) * kBoundsThreads;
   for (size_t i = static_cast<size_t>(blockIdx.x) * kBoundsThreads + threadIdx.x; i < count;
@@ -418,6 +424,7 @@ record_build_kernel(const float* __restrict__ x, const float* __restrict__ y,
                     const float* __restrict__ z, const float* __restrict__ v, int64_t padded,
                     PushSpec push, int64_t n, float4* __restrict__ records,
                     const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kRecordThreads;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kRecordThreads + threadIdx.x; i < n;
@@ -440,6 +447,7 @@ record_gather_kernel(const int32_t* __restrict__ index, int64_t n,
                      const float4* __restrict__ records, float* __restrict__ xs,
                      float* __restrict__ ys, float* __restrict__ zs, float* __restrict__ vs,
                      int64_t padded_sorted, const int32_t* __restrict__ run_if) {
+  chain_begin();
   if (run_if && *run_if == 0) return;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kRecordThreads;
   for (int64_t r = static_cast<int64_t>(blockIdx.x) * kRecordThreads + threadIdx.x; r < n;
@@ -504,27 +512,24 @@ cudaError_t launch_gather(const int32_t* index, int64_t n, const float* x, const
   bool vec = aligned16(index) && aligned16(xs) && aligned16(ys) && aligned16(zs);
   if (velocity) vec = vec && aligned16(vs) && padded_sorted % 4 == 0;
   const int grid = grid_for(n, kGatherThreads * 4, 8);
-  if (vec)
-    gather_kernel<true><<<grid, kGatherThreads, 0, stream>>>(
-        index, n, x, y, z, velocity, padded, xs, ys, zs, vs, padded_sorted, run_if);
-  else
-    gather_kernel<false><<<grid, kGatherThreads, 0, stream>>>(
-        index, n, x, y, z, velocity, padded, xs, ys, zs, vs, padded_sorted, run_if);
+  const cudaError_t e = launch_chained(vec ? gather_kernel<true> : gather_kernel<false>, grid,
+                                       kGatherThreads, 0, stream, index, n, x, y, z, velocity,
+                                       padded, xs, ys, zs, vs, padded_sorted, run_if);
   count_launches(1);
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t launch_cell_tables(const uint32_t* sorted_keys, int64_t n, int64_t num_cells,
                                int32_t* cell_counts, int32_t* cell_start, cudaStream_t stream,
                                const int32_t* run_if) {
-  cell_bounds_kernel<<<grid_for(n + 1, kBoundsThreads, 8), kBoundsThreads, 0, stream>>>(
-      sorted_keys, n, num_cells, cell_start, run_if);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_chained(cell_bounds_kernel, grid_for(n + 1, kBoundsThreads, 8),
+                                 kBoundsThreads, 0, stream, sorted_keys, n, num_cells, cell_start,
+                                 run_if);
   if (e != cudaSuccess) return e;
-  cell_counts_kernel<<<grid_for(num_cells, kBoundsThreads, 8), kBoundsThreads, 0, stream>>>(
-      cell_start, num_cells, cell_counts, run_if);
+  e = launch_chained(cell_counts_kernel, grid_for(num_cells, kBoundsThreads, 8), kBoundsThreads, 0,
+                     stream, cell_start, num_cells, cell_counts, run_if);
   count_launches(2);
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int PASSES>
@@ -532,12 +537,9 @@ static void launch_keygen(const SortArgs& a, bool vec, const float4* records, ui
                           Header* hdr, const int32_t* run_if) {
   const int grid = grid_for(a.n, kKeygenChunk, 8);
   const uint32_t k0 = static_cast<uint32_t>(a.seed), k1 = static_cast<uint32_t>(a.seed >> 32);
-  if (vec)
-    keygen_upsweep_kernel<PASSES, true><<<grid, kKeygenThreads, 0, a.stream>>>(
-        a.x, a.y, a.z, records, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
-  else
-    keygen_upsweep_kernel<PASSES, false><<<grid, kKeygenThreads, 0, a.stream>>>(
-        a.x, a.y, a.z, records, a.n, a.grid, k0, k1, keys, &hdr->digit_hist[0][0], run_if);
+  launch_chained(vec ? keygen_upsweep_kernel<PASSES, true> : keygen_upsweep_kernel<PASSES, false>,
+                 grid, kKeygenThreads, 0, a.stream, a.x, a.y, a.z, records, a.n, a.grid, k0, k1, keys,
+                 &hdr->digit_hist[0][0], run_if);
 }
 
 int64_t lookback_probe_particles() { return 3 * kPassTile; }
@@ -590,11 +592,11 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   cudaError_t e = cudaSuccess;
   if (run_if) {
     const size_t words = (l.keys_alt_off - 8) / sizeof(uint32_t);
-    clear_words_kernel<<<grid_for(static_cast<int64_t>(words), kBoundsThreads * 4, 8),
-                         kBoundsThreads, 0, a.stream>>>(reinterpret_cast<uint32_t*>(base + 8),
-                                                         words, run_if);
+    e = launch_chained(clear_words_kernel,
+                       grid_for(static_cast<int64_t>(words), kBoundsThreads * 4, 8), kBoundsThreads,
+                       0, a.stream, reinterpret_cast<uint32_t*>(base + 8), words, run_if);
     count_launches(1);
-    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaGetLastError();
   } else {
     e = cudaMemsetAsync(base, 0, l.keys_alt_off, a.stream);
   }
@@ -610,8 +612,8 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
   const float4* moved = nullptr;
   if (a.push.enabled && a.n > 0) {
     stage_begin(kStagePush, a.stream);
-    record_build_kernel<<<grid_for(a.n, kRecordThreads, 8), kRecordThreads, 0, a.stream>>>(
-        a.x, a.y, a.z, a.velocity, a.padded, a.push, a.n, records, run_if);
+    launch_chained(record_build_kernel, grid_for(a.n, kRecordThreads, 8), kRecordThreads, 0,
+                   a.stream, a.x, a.y, a.z, a.velocity, a.padded, a.push, a.n, records, run_if);
     stage_end(kStagePush, a.stream);
     count_launches(1);
     moved = records;
@@ -648,14 +650,15 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
       uint32_t* st = status + static_cast<size_t>(p) * l.tiles * kRadix;
       stage_begin(static_cast<Stage>(kStagePass0 + p), a.stream);
       if (p == 0)
-        onesweep_pass_kernel<true><<<pass_grid, kPassThreads, sizeof(PassSmem), a.stream>>>(
-            cur_k, nullptr, nxt_k, nxt_v, a.n, 0, hdr->digit_hist[0], st, &hdr->tile_counter[0],
-            static_cast<uint32_t>(l.tiles), &hdr->error, kPollLimit, run_if);
+        launch_chained(onesweep_pass_kernel<true>, pass_grid, kPassThreads, sizeof(PassSmem),
+                       a.stream, cur_k, nullptr, nxt_k, nxt_v, a.n, 0, hdr->digit_hist[0], st,
+                       &hdr->tile_counter[0], static_cast<uint32_t>(l.tiles), &hdr->error,
+                       kPollLimit, run_if);
       else
-        onesweep_pass_kernel<false><<<pass_grid, kPassThreads, sizeof(PassSmem), a.stream>>>(
-            cur_k, cur_v, nxt_k, nxt_v, a.n, kRadixBits * p, hdr->digit_hist[p], st,
-            &hdr->tile_counter[p], static_cast<uint32_t>(l.tiles), &hdr->error, kPollLimit,
-            run_if);
+        launch_chained(onesweep_pass_kernel<false>, pass_grid, kPassThreads, sizeof(PassSmem),
+                       a.stream, cur_k, cur_v, nxt_k, nxt_v, a.n, kRadixBits * p,
+                       hdr->digit_hist[p], st, &hdr->tile_counter[p],
+                       static_cast<uint32_t>(l.tiles), &hdr->error, kPollLimit, run_if);
       stage_end(static_cast<Stage>(kStagePass0 + p), a.stream);
       count_launches(1);
       e = cudaGetLastError();
@@ -674,12 +677,12 @@ cudaError_t standard_sort(const SortArgs& a, const int32_t* run_if) {
     if (have_records) {
       const int grid = grid_for(a.n, kRecordThreads, 8);
       if (!moved) {
-        record_build_kernel<<<grid, kRecordThreads, 0, a.stream>>>(
-            a.x, a.y, a.z, a.velocity, a.padded, a.push, a.n, records, run_if);
+        launch_chained(record_build_kernel, grid, kRecordThreads, 0, a.stream, a.x, a.y, a.z,
+                       a.velocity, a.padded, a.push, a.n, records, run_if);
         count_launches(1);
       }
-      record_gather_kernel<<<grid, kRecordThreads, 0, a.stream>>>(
-          a.index_out, a.n, records, a.xs, a.ys, a.zs, a.vs, a.padded_sorted, run_if);
+      launch_chained(record_gather_kernel, grid, kRecordThreads, 0, a.stream, a.index_out, a.n,
+                     records, a.xs, a.ys, a.zs, a.vs, a.padded_sorted, run_if);
       count_launches(1);
       e = cudaGetLastError();
     } else {
