@@ -892,7 +892,7 @@ def run_multi(args):
             # while the local sort's kernels run beside the exchange.
             crossing = 24 * n_rank * (world - 1) / world
             link = crossing / (exchange_ms * 1e-3) / 1e9
-            by_stores = os.environ.get('AETHER_EXCHANGE_TRANSPORT') == 'stores'
+            by_stores = slab_sort.transport_default(world) == 'stores'
             nvlink = {'kernel': ('slab_scatter_kernel (all slices)' if by_stores else
                                  'slab_scatter_kernel into staging rows + copy engines (all slices)'),
                       'bytes_out_per_gpu': crossing,
@@ -907,11 +907,12 @@ def run_multi(args):
             'config': workload_config(workload, w, world),
             'details': {'exchange': ('one NCCL all-to-all per payload array' if exchange != 'peer'
                                      else 'partition kernel stores into the peers\' receive buffers '
-                                          'over NVLink, beside the local sort'
-                                     if os.environ.get('AETHER_EXCHANGE_TRANSPORT') == 'stores'
+                                          'over NVLink'
+                                     if slab_sort.transport_default(world) == 'stores'
                                      else 'partition kernel fills staging rows, copy engines carry '
-                                          'them into the peers\' receive buffers over NVLink, '
-                                          'beside the local sort'),
+                                          'them into the peers\' receive buffers over NVLink'),
+                        'overlap_with_local_sort': bool(exchange == 'peer' and
+                                                        slab_sort.overlap_default(world)),
                         'initial_share': ('cell-sorted particles of the rank\'s own slab; every '
                                           'step moves them (dt %g) and re-sorts' % STEADY_DT
                                           if steady else 'random 1/G of all particles per rank')},

@@ -105,10 +105,10 @@ WAIT_POLLS = 1 << 22       # polls (256 ns apart: about a second) before a slice
 
 # How the sliced exchange shares the GPU with the local sort (set with `configure`).
 _settings = {
-    'overlap': None,          # None: yes
+    'overlap': None,          # None: up to four ranks
     'resident_blocks': None,  # exchange blocks per multiprocessor beside the sort; None: 0
     'sort_stream': None,      # None: a high-priority stream of its own from four ranks on
-    'transport': None,        # None: 'copies'
+    'transport': None,        # None: 'copies' up to four ranks, 'stores' beyond
 }
 
 
@@ -116,28 +116,32 @@ def configure(overlap: Optional[bool] = None, resident_blocks: Optional[int] = N
               sort_stream: Optional[bool] = None, transport: Optional[str] = None) -> None:
     """Tuning of `distributed_sort(exchange='peer')`; None restores a default.
 
-    transport: 'copies' (default) — the exchange kernel partitions into staging buffers in
-      this GPU's own memory, laid out like the destinations' receive buffers (a rank's own
-      share goes straight into its receive buffer), and one device-to-device copy per
-      destination and slice (six rows, one per array) carries the data over NVLink on the copy
-      engines, so that the multiprocessors are free for the local sort while the links are
-      busy.  The host has to know the counts before it can enqueue the copies (one wait per
-      step for the count all-gather).  'stores' — the exchange kernel stores every particle
-      straight into its destination GPU's receive buffer over NVLink (no staging memory, no
-      host wait), and occupies multiprocessors for as long as the links take.
+    transport: 'copies' (default up to four ranks) — the exchange kernel partitions into
+      staging buffers in this GPU's own memory, laid out like the destinations' receive buffers
+      (a rank's own share goes straight into its receive buffer), and one device-to-device
+      copy per destination and slice (six rows, one per array) carries the data over NVLink on
+      the copy engines, so that the multiprocessors are free for the local sort while the
+      links are busy.  The host has to know the counts before it can enqueue the copies (one
+      wait per step for the count all-gather).  'stores' (default beyond four ranks) — the
+      exchange kernel stores every particle straight into its destination GPU's receive
+      buffer over NVLink (no staging memory, no host wait), and occupies multiprocessors for
+      as long as the links take.
     overlap: run the local sort's count and scatter kernels beside the exchange, slice by
-      slice.  Default: yes.  (With 'stores' on two ranks the two slow each other down by more
-      than the overlap gains: 9.5 ms overlapped, 8.9 ms one after the other.)
+      slice.  Default: up to four ranks.  Beyond, a rank's share is small, the slices' many
+      short launches and copies cost more than the overlap gains, and the exchange runs in
+      one piece with the ordinary local sort behind it.
     resident_blocks ('stores' only): thread blocks of the exchange kernel per multiprocessor
       while it runs beside the sort (1..4), or 0 for one block per tile, which lets the sort's
       kernels take the multiprocessors over as the exchange's blocks retire.  Default 0.
     sort_stream: run the sliced local sort on a high-priority stream of its own instead of the
       caller's stream.  Default: from four ranks on.
     Measured on the 256 M configuration, ms per step.  Two ranks: 'stores' one after the other
-    8.8–9.9, 'copies' one after the other 9.7, overlapped 8.2 (caller's stream) and 8.5 (own
-    stream).  Four ranks: 'stores' overlapped 5.36–5.46, one after the other 6.32; 'copies'
-    overlapped 4.74 (own stream) and 4.85 (caller's), one after the other 5.42.  Either way
-    about 500 GB/s per direction cross the links while all ranks send and receive at once."""
+    8.8–9.9, overlapped 9.5; 'copies' one after the other 9.7, overlapped 8.2 (caller's stream)
+    and 8.5 (own stream).  Four ranks: 'stores' overlapped 5.36–5.46, one after the other 6.32;
+    'copies' overlapped 4.74 (own stream) and 4.85 (caller's), one after the other 5.42.  Eight
+    ranks: 'stores' one after the other 3.01, overlapped 3.54; 'copies' overlapped 3.25, one
+    after the other 3.45.  About 500 GB/s per direction cross the links while all ranks send
+    and receive at once, by stores and by copies alike."""
     if transport not in (None, 'stores', 'copies'):
         raise ValueError(f'unknown transport {transport!r}')
     _settings.update(overlap=overlap, resident_blocks=resident_blocks, sort_stream=sort_stream,
@@ -148,7 +152,13 @@ def configure(overlap: Optional[bool] = None, resident_blocks: Optional[int] = N
 
 def overlap_default(world: int) -> bool:
     """Whether the local sort runs beside the exchange (see `configure`)."""
-    return True if _settings['overlap'] is None else bool(_settings['overlap'])
+    return world <= 4 if _settings['overlap'] is None else bool(_settings['overlap'])
+
+
+def transport_default(world: int) -> str:
+    """How the particles cross NVLink (see `configure`)."""
+    return ('copies' if world <= 4 else 'stores') if _settings['transport'] is None \
+        else _settings['transport']
 
 
 class PeerBuffers:
@@ -408,7 +418,7 @@ def peer_exchange_sort(x, y, z, velocity, grid: CellGrid, seed: int, group=None,
             _native.check(lib.AetherSlabExchangeSetResidentBlocks(0 if resident is None else resident),
                           'AetherSlabExchangeSetResidentBlocks')
             state.exchange_stream.wait_event(gathered)
-            by_copies = _settings['transport'] != 'stores' and world > 1
+            by_copies = transport_default(world) == 'copies' and world > 1
             if by_copies:
                 sent = _exchange_by_copies(lib, state, buffers, matrix, x, y, z, velocity, n, move,
                                            g, world, rank, totals, slices, epoch, part_ws)

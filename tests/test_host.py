@@ -215,4 +215,5 @@ def test_exchange_settings_are_checked():
     slab_sort.configure(transport='stores', overlap=False)
     assert slab_sort.overlap_default(8) is False
     slab_sort.configure()
-    assert slab_sort.overlap_default(2) is True
+    assert slab_sort.overlap_default(2) is True and slab_sort.overlap_default(8) is False
+    assert slab_sort.transport_default(4) == 'copies' and slab_sort.transport_default(8) == 'stores'
