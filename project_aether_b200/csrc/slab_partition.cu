@@ -337,11 +337,7 @@ slab_scatter_kernel(const float* __restrict__ x, const float* __restrict__ y,
     for (int c = 0; c < 6; ++c) {
       const float4 quad = make_float4(stage[c][swizzle(j)], stage[c][swizzle(j + 1)],
                                       stage[c][swizzle(j + 2)], stage[c][swizzle(j + 3)]);
-#ifdef AETHER_TUNE_EXCHANGE_STREAMING_STORES
-      __stcs(reinterpret_cast<float4*>(tg.array[d][c] + o), quad);
-#else
-      *reinterpret_cast<float4*>(tg.array[d][c] + o) = quad;
-#endif
+      *reinterpret_cast<float4*>(tg.array[d][c] + o) = quad;  // (streaming stores: no gain)
     }
   }
   // Heads and tails: at most three elements each per destination when aligned;
